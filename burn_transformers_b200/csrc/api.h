@@ -1,0 +1,41 @@
+// C interface of the kernel library.  Every function returns 0 on success; otherwise
+// bt_last_error() holds the reason.  dtype codes: 0 = float32, 1 = bfloat16.
+#pragma once
+#include <cuda_runtime.h>
+
+extern "C" {
+const char* bt_last_error();
+int bt_abi_version();
+
+int bt_embed(const int* tokens, const int* positions, const void* wte, const void* wpe, float* out, int n_tokens,
+             int width, int vocab, int n_positions, int dtype, int* status, cudaStream_t stream);
+
+int bt_layernorm(const float* x, const int* rows, const float* gamma, const float* beta, void* out, int n_rows,
+                 int width, float eps, int out_dtype, cudaStream_t stream);
+
+int bt_linear_simt(const void* A, const void* W, const float* bias, const float* residual, void* out, int M, int N,
+                   int K, int w_is_nk, int act, int in_dtype, int out_dtype, cudaStream_t stream);
+
+int bt_kv_append(const void* proj, long long row_stride, int k_offset, int v_offset, const int* positions,
+                 const int* token_seq, const int* ctx_len, const int* table, int table_stride, int table_len,
+                 int page_size, void* k_pool, void* v_pool, int n_tokens, int n_kv_heads, int head_dim, int dtype,
+                 cudaStream_t stream);
+
+int bt_attention_prefill_simt(const void* q, long long q_row_stride, const void* k, const void* v,
+                              const int* kv_table, int table_stride, int table_len, int page_size,
+                              long long kv_row_stride, void* out, const int* seq_start, const int* past_len,
+                              int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim, float scale,
+                              int causal, int window, int dtype, cudaStream_t stream);
+
+long long bt_attention_decode_scratch_floats(int n_seqs, int n_heads, int head_dim, int n_splits);
+int bt_attention_decode(const void* q, long long q_row_stride, const void* k_pool, const void* v_pool,
+                        const int* kv_table, int table_stride, int table_len, int page_size, void* out,
+                        float* scratch, const int* ctx_len, int n_seqs, int n_heads, int n_kv_heads, int head_dim,
+                        float scale, int window, int n_splits, int dtype, cudaStream_t stream);
+
+int bt_sample(const float* logits, long long row_stride, int n_rows, int vocab, int do_sample, float temperature,
+              int top_k, float top_p, float min_p, const float* uniforms, int* out_ids, float* out_logp,
+              cudaStream_t stream);
+int bt_logit_edits(float* logits, long long row_stride, const int* rows, const int* tokens, const float* vals,
+                   int n_edits, int vocab, cudaStream_t stream);
+}

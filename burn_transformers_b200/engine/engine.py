@@ -1,0 +1,166 @@
+"""The engine: a model plan with its weights on one GPU, a cache, and the step function.
+
+`step` is the only way tokens reach the model.  A step brings, for each sequence of a batch, its
+next tokens (a whole prompt, or one token) and runs exactly those tokens against the cache that
+earlier steps left; it returns the 32-bit logits at the wanted places.  Sequences of different
+lengths are packed one after another, so there is no padding and nothing to mask out.
+
+The contract follows the reference's prefill/decode pair (src/architecture/traits.rs:110-153,
+src/models/shared/rows.rs:1-45 of NoahIsCool/burn-transformers): positions of new tokens continue
+the sequence's length, requests are validated before the cache changes, and lengths advance only
+when the step has been issued.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from .. import kernels
+from ..cache import CacheBank, CacheConfig, PAGE_SIZE
+from ..config.registry import config_from_folder
+from ..errors import CacheError, KernelError, ShapeError
+from ..weights.loader import COMPUTE_DTYPES, load_weights
+from .model import ModelPlan
+from .step import StepContext, StepEntry, Workspace
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class Engine:
+    def __init__(self, plan: ModelPlan, tensors: dict[str, torch.Tensor], dtype: str, cache_config: CacheConfig,
+                 device="cuda:0"):
+        if dtype not in COMPUTE_DTYPES:
+            raise ShapeError(f"dtype must be one of {sorted(COMPUTE_DTYPES)}, found `{dtype}`")
+        self.plan = plan
+        self.dtype_name = dtype
+        self.dtype = COMPUTE_DTYPES[dtype]
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise KernelError(f"the engine runs on a CUDA device only, not on `{device}`")
+        kernels.library()  # fail now, loudly, if the kernels cannot be built or loaded
+        plan.bind(tensors)
+        if cache_config.max_context > plan.max_context:
+            raise CacheError(f"cache.max_context {cache_config.max_context} exceeds the model's longest sequence "
+                             f"{plan.max_context}")
+        self.cache_config = cache_config
+        self.cache = CacheBank(plan.cache_needs(), cache_config, self.dtype, self.device)
+        self.ws = Workspace(self.device)
+        self._meta_host = None
+        self._meta_dev = None
+        self.steps_run = 0
+
+    # ---- construction ------------------------------------------------------------------
+    @classmethod
+    def from_folder(cls, folder, dtype: str = "bfloat16", *, max_tokens: int | None = None,
+                    max_slots: int | None = None, max_context: int | None = None, device="cuda:0") -> "Engine":
+        """Reads config.json, picks the architecture by `model_type`, loads model.safetensors strictly."""
+        from .. import models  # noqa: F401  (registers the architectures)
+        arch, config = config_from_folder(Path(folder))
+        plan = arch.build(config)
+        tensors, report = load_weights(folder, plan.weights, dtype, torch.device(device))
+        max_context = min(max_context or plan.max_context, plan.max_context)
+        max_tokens = max_tokens or max_context
+        cache_config = CacheConfig(max_tokens=max_tokens, max_slots=max_slots or max(1, -(-max_tokens // PAGE_SIZE)),
+                                   max_context=max_context)
+        engine = cls(plan, tensors, dtype, cache_config, device)
+        engine.load_report = report
+        return engine
+
+    # ---- sequences ---------------------------------------------------------------------
+    def new_sequence(self) -> int:
+        return self.cache.acquire()
+
+    def release(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step ----------------------------------------------------------------------
+    def _validate(self, entries: list[StepEntry]) -> None:
+        if not entries:
+            raise ShapeError("a step needs at least one sequence")
+        seen = set()
+        vocab = self.plan.vocab
+        for e in entries:
+            if e.slot in seen:
+                raise ShapeError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            past = self.cache.length(e.slot)
+            if len(e.tokens) == 0:
+                raise ShapeError(f"slot {e.slot}: a step must bring at least one token per sequence")
+            if past + len(e.tokens) > self.cache_config.max_context:
+                raise CacheError(f"slot {e.slot}: {past} + {len(e.tokens)} tokens exceed the longest sequence of "
+                                 f"{self.cache_config.max_context}")
+            for t in e.tokens:
+                if not (0 <= int(t) < vocab):
+                    raise ShapeError(f"slot {e.slot}: token id {t} is outside the vocabulary of {vocab}")
+            for w in e.want:
+                if not (0 <= int(w) < len(e.tokens)):
+                    raise ShapeError(f"slot {e.slot}: wanted place {w} is outside the {len(e.tokens)} tokens of the step")
+
+    def _build_context(self, entries: list[StepEntry]) -> StepContext:
+        cache = self.cache
+        n_seqs = len(entries)
+        pasts = [cache.length(e.slot) for e in entries]
+        news = [len(e.tokens) for e in entries]
+        n_tokens = sum(news)
+        tokens, positions, token_seq, seq_start, want_rows = [], [], [], [0], []
+        for i, e in enumerate(entries):
+            base = seq_start[-1]
+            tokens.extend(int(t) for t in e.tokens)
+            positions.extend(range(pasts[i], pasts[i] + news[i]))
+            token_seq.extend([i] * news[i])
+            want_rows.extend(base + int(w) for w in e.want)
+            seq_start.append(base + news[i])
+        ctx_len = [p + n for p, n in zip(pasts, news)]
+        slots = [e.slot for e in entries]
+        width = cache.table_width
+        sections = [tokens, positions, token_seq, seq_start, pasts, ctx_len, slots, want_rows]
+        for g in range(len(cache.groups)):
+            flat = []
+            for e in entries:
+                row = cache.table_row(g, e.slot)
+                flat.extend(row)
+                flat.extend([0] * (width - len(row)))
+            sections.append(flat)
+        offsets, total = [], 0
+        for s in sections:
+            offsets.append(total)
+            total += _align4(max(1, len(s)))
+        if self._meta_host is None or self._meta_host.numel() < total:
+            cap = max(total, 4096)
+            self._meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        host = self._meta_host
+        for off, s in zip(offsets, sections):
+            if s:
+                host[off:off + len(s)] = torch.tensor(s, dtype=torch.int32)
+        self._meta_dev[:total].copy_(host[:total], non_blocking=True)
+        dev = self._meta_dev
+        view = lambda i: dev[offsets[i]:offsets[i] + max(1, len(sections[i]))]
+        tables = [view(8 + g).view(n_seqs, width) for g in range(len(cache.groups))]
+        self.h2d_bytes_last = total * 4
+        return StepContext(
+            dtype=self.dtype, cache=cache, ws=self.ws, n_tokens=n_tokens, n_seqs=n_seqs, n_want=len(want_rows),
+            max_new=max(news), is_decode=all(n == 1 for n in news), fresh=all(p == 0 for p in pasts),
+            ctx_bound=max(ctx_len), tokens=view(0), positions=view(1), token_seq=view(2), seq_start=view(3),
+            past_len=view(4), ctx_len=view(5), slots=view(6), want_rows=view(7), tables=tables, host_slots=slots)
+
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Runs the entries' tokens as one batch and returns logits [wanted, vocab] (float32, on the device),
+        in the order of the entries and of their `want` lists; None when nothing is wanted.
+
+        The returned tensor lies in the step's scratch memory: read it before the next step."""
+        self._validate(entries)
+        self.cache.reserve([(e.slot, self.cache.length(e.slot) + len(e.tokens)) for e in entries])
+        self.ws.reset()
+        ctx = self._build_context(entries)
+        logits = self.plan.forward(ctx)
+        for e in entries:
+            self.cache.commit(e.slot, self.cache.length(e.slot) + len(e.tokens))
+        self.steps_run += 1
+        return logits

@@ -1,0 +1,223 @@
+"""Python face of the CUDA kernel library: loads it, checks arguments, launches on torch's stream.
+
+There is no fallback: if the library cannot be built or loaded, or a tensor lies on the host,
+the call raises.  Tensors are passed as raw device pointers; shapes and dtypes are checked here
+so that a kernel never sees a size it was not written for.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .errors import KernelError, ShapeError
+
+_LIB = None
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+ACTIVATIONS = {None: 0, "none": 0, "gelu_new": 1, "gelu_tanh": 1, "gelu": 2, "gelu_erf": 2}
+PAGE_SIZE = 64
+
+
+def library() -> ctypes.CDLL:
+    """The loaded kernel library; builds it on first use."""
+    global _LIB
+    if _LIB is None:
+        from .csrc.build import build
+        path = build()
+        try:
+            lib = ctypes.CDLL(str(path))
+        except OSError as error:
+            raise KernelError(f"cannot load the CUDA kernel library {path}: {error}") from None
+        lib.bt_last_error.restype = ctypes.c_char_p
+        lib.bt_attention_decode_scratch_floats.restype = c_longlong
+        if lib.bt_abi_version() != 1:
+            raise KernelError(f"{path} has an unexpected interface version")
+        _LIB = lib
+    return _LIB
+
+
+def _check(code: int) -> None:
+    if code != 0:
+        raise KernelError(library().bt_last_error().decode(errors="replace"))
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise ShapeError(f"{name}: expected a tensor, found {type(t).__name__}")
+    if not t.is_cuda:
+        raise KernelError(f"{name}: lies on {t.device}; the kernels of this library run on a CUDA device only")
+    if not t.is_contiguous():
+        raise ShapeError(f"{name}: must be contiguous")
+    if dtype is not None:
+        allowed = dtype if isinstance(dtype, (tuple, list)) else (dtype,)
+        if t.dtype not in allowed:
+            raise ShapeError(f"{name}: expected dtype {allowed}, found {t.dtype}")
+    if shape is not None:
+        if len(shape) != t.dim() or any(w is not None and w != g for w, g in zip(shape, t.shape)):
+            raise ShapeError(f"{name}: expected shape {list(shape)}, found {list(t.shape)}")
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_CODE[dtype]
+    except KeyError:
+        raise ShapeError(f"unsupported element type {dtype}") from None
+
+
+# --------------------------------------------------------------------------------------------
+
+def embed(tokens, positions, wte, wpe, out, status=None):
+    """out[t] = wte[tokens[t]] (+ wpe[positions[t]]) into the 32-bit residual stream."""
+    n = tokens.shape[0]
+    vocab, width = wte.shape
+    _need(tokens, "tokens", torch.int32, (n,))
+    _need(wte, "wte", (torch.float32, torch.bfloat16))
+    _need(out, "out", torch.float32, (None, width))
+    n_pos = 0
+    if wpe is not None:
+        _need(positions, "positions", torch.int32, (n,))
+        _need(wpe, "wpe", wte.dtype, (None, width))
+        n_pos = wpe.shape[0]
+    if out.shape[0] < n:
+        raise ShapeError(f"out: {out.shape[0]} rows for {n} tokens")
+    _check(library().bt_embed(_ptr(tokens), _ptr(positions if wpe is not None else None), _ptr(wte), _ptr(wpe), _ptr(out),
+                              c_int(n), c_int(width), c_int(vocab), c_int(n_pos), c_int(_code(wte.dtype)),
+                              _ptr(status), _stream()))
+
+
+def layernorm(x, gamma, beta, out, eps: float, rows=None, n_rows=None):
+    """out[r] = LayerNorm(x[rows[r]] or x[r]); x is 32-bit, out is 32-bit or bfloat16."""
+    width = x.shape[-1]
+    _need(x, "x", torch.float32, (None, width))
+    _need(gamma, "gamma", torch.float32, (width,))
+    if beta is not None:
+        _need(beta, "beta", torch.float32, (width,))
+    n = n_rows if n_rows is not None else (rows.shape[0] if rows is not None else x.shape[0])
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    _need(out, "out", (torch.float32, torch.bfloat16), (None, width))
+    if out.shape[0] < n:
+        raise ShapeError(f"out: {out.shape[0]} rows for {n} rows")
+    _check(library().bt_layernorm(_ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), c_int(n), c_int(width),
+                                  c_float(eps), c_int(_code(out.dtype)), _stream()))
+
+
+def linear_simt(a, w, bias, out, *, m=None, w_is_nk=False, activation=None, residual=None):
+    """out = act(a @ w + bias) (+ residual) with 32-bit fused multiply-adds.
+
+    a: [M, K]; w: [K, N] (or [N, K] when w_is_nk); bias: [N] float32 or None; residual: [M, N]
+    float32 (may be `out` itself); out: [M, N] float32 or a's dtype.
+    """
+    k = a.shape[1]
+    n = w.shape[0] if w_is_nk else w.shape[1]
+    m = a.shape[0] if m is None else m
+    _need(a, "a", (torch.float32, torch.bfloat16), (None, k))
+    _need(w, "w", a.dtype, (n, k) if w_is_nk else (k, n))
+    _need(out, "out", (torch.float32, a.dtype), (None, n))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (n,))
+    if residual is not None:
+        _need(residual, "residual", torch.float32, (None, n))
+    if a.shape[0] < m or out.shape[0] < m:
+        raise ShapeError(f"linear: {m} rows asked of a[{a.shape[0]}] and out[{out.shape[0]}]")
+    if activation not in ACTIVATIONS:
+        raise ShapeError(f"linear: unknown activation {activation!r}")
+    _check(library().bt_linear_simt(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), c_int(m), c_int(n), c_int(k),
+                                    c_int(1 if w_is_nk else 0), c_int(ACTIVATIONS[activation]), c_int(_code(a.dtype)),
+                                    c_int(_code(out.dtype)), _stream()))
+
+
+def kv_append(proj, k_offset, v_offset, positions, token_seq, ctx_len, table, table_len, k_pool, v_pool,
+              n_tokens, n_kv_heads, head_dim):
+    """Copies the new tokens' key and value channels of `proj` rows into the layer's pages."""
+    _need(proj, "proj", (torch.float32, torch.bfloat16))
+    _need(k_pool, "k_pool", proj.dtype)
+    _need(v_pool, "v_pool", proj.dtype)
+    _need(table, "table", torch.int32)
+    _check(library().bt_kv_append(_ptr(proj), c_longlong(proj.shape[1]), c_int(k_offset), c_int(v_offset),
+                                  _ptr(positions), _ptr(token_seq), _ptr(ctx_len), _ptr(table), c_int(table.shape[1]),
+                                  c_int(table_len), c_int(PAGE_SIZE), _ptr(k_pool), _ptr(v_pool), c_int(n_tokens),
+                                  c_int(n_kv_heads), c_int(head_dim), c_int(_code(proj.dtype)), _stream()))
+
+
+def attention_prefill_simt(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale,
+                           *, causal=True, window=0, k_pool=None, v_pool=None, table=None, table_len=0,
+                           k_offset=None, v_offset=None):
+    """Attention of several new tokens per sequence.
+
+    Queries are the first n_heads*head_dim channels of `q_proj` rows.  Keys and values come either
+    from the pages (`k_pool`, `v_pool`, `table`) or, when `table` is None, from the channels
+    `k_offset`, `v_offset` of the same rows (sequences that start at position 0).
+    """
+    _need(q_proj, "q_proj", (torch.float32, torch.bfloat16))
+    _need(out, "out", q_proj.dtype, (None, n_heads * head_dim))
+    stride = q_proj.shape[1]
+    es = q_proj.element_size()
+    if table is None:
+        k_ptr = c_void_p(q_proj.data_ptr() + k_offset * es)
+        v_ptr = c_void_p(q_proj.data_ptr() + v_offset * es)
+        t_ptr, t_stride = c_void_p(0), 0
+    else:
+        _need(k_pool, "k_pool", q_proj.dtype)
+        _need(v_pool, "v_pool", q_proj.dtype)
+        _need(table, "table", torch.int32)
+        k_ptr, v_ptr, t_ptr, t_stride = _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1]
+    _check(library().bt_attention_prefill_simt(
+        _ptr(q_proj), c_longlong(stride), k_ptr, v_ptr, t_ptr, c_int(t_stride), c_int(table_len), c_int(PAGE_SIZE),
+        c_longlong(stride), _ptr(out), _ptr(seq_start), _ptr(past_len), c_int(n_seqs), c_int(max_new), c_int(n_heads),
+        c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(1 if causal else 0), c_int(window),
+        c_int(_code(q_proj.dtype)), _stream()))
+
+
+def attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits) -> int:
+    return int(library().bt_attention_decode_scratch_floats(c_int(n_seqs), c_int(n_heads), c_int(head_dim), c_int(n_splits)))
+
+
+def attention_decode(q_proj, out, k_pool, v_pool, table, table_len, ctx_len, n_seqs, n_heads, n_kv_heads, head_dim,
+                     scale, *, window=0, n_splits=1, scratch=None):
+    """Attention of one new token per sequence over that sequence's pages."""
+    _need(q_proj, "q_proj", (torch.float32, torch.bfloat16))
+    _need(out, "out", q_proj.dtype, (None, n_heads * head_dim))
+    _need(k_pool, "k_pool", q_proj.dtype)
+    _need(v_pool, "v_pool", q_proj.dtype)
+    _need(table, "table", torch.int32)
+    if n_splits > 1:
+        need = attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise ShapeError(f"attention_decode: {n_splits} splits need {need} floats of scratch")
+    _check(library().bt_attention_decode(
+        _ptr(q_proj), c_longlong(q_proj.shape[1]), _ptr(k_pool), _ptr(v_pool), _ptr(table), c_int(table.shape[1]),
+        c_int(table_len), c_int(PAGE_SIZE), _ptr(out), _ptr(scratch), _ptr(ctx_len), c_int(n_seqs), c_int(n_heads),
+        c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(n_splits), c_int(_code(q_proj.dtype)),
+        _stream()))
+
+
+def sample(logits, n_rows, *, do_sample, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0, uniforms=None,
+           out_ids=None, out_logp=None):
+    """Selects one token per row of 32-bit logits; writes ids (int32) and log-probabilities (float32)."""
+    _need(logits, "logits", torch.float32)
+    vocab = logits.shape[1]
+    _need(out_ids, "out_ids", torch.int32)
+    _need(out_logp, "out_logp", torch.float32)
+    if do_sample:
+        _need(uniforms, "uniforms", torch.float32)
+    _check(library().bt_sample(_ptr(logits), c_longlong(logits.stride(0)), c_int(n_rows), c_int(vocab),
+                               c_int(1 if do_sample else 0), c_float(temperature), c_int(top_k or 0),
+                               c_float(1.0 if top_p is None else top_p), c_float(0.0 if min_p is None else min_p),
+                               _ptr(uniforms), _ptr(out_ids), _ptr(out_logp), _stream()))
+
+
+def logit_edits(logits, rows, tokens, vals, n_edits):
+    """Applies sparse edits (row, token, [add, repetition, subtract, ban]) to 32-bit logits in place."""
+    _need(logits, "logits", torch.float32)
+    _check(library().bt_logit_edits(_ptr(logits), c_longlong(logits.stride(0)), _ptr(rows), _ptr(tokens), _ptr(vals),
+                                    c_int(n_edits), c_int(logits.shape[1]), _stream()))

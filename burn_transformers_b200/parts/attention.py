@@ -1,0 +1,96 @@
+"""Self-attention over the cache."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache.spec import CacheNeed, KvSpec
+from ..errors import CacheError
+from ..weights.spec import MATRIX, VECTOR, TensorSpec
+from .base import Mixer
+from .linear import linear
+
+_SM_COUNT = 148
+
+
+class CausalSelfAttention(Mixer):
+    """Multi-head (or grouped) attention with one fused query|key|value projection.
+
+    [q|k|v] = x @ qkv.weight + qkv.bias with the weight stored [in, out]; head h owns channels
+    h*head_dim..(h+1)*head_dim of its block; scores are (q . k) * scale, masked causally (and by
+    `window` if given), softmax in 32-bit, then the value mix and the output projection, whose
+    result is added to the residual stream (src/models/gpt2/model.rs:114-142, 218-261;
+    src/attention/dispatch.rs:277-430 of the reference).  `n_kv_heads` < `n_heads` shares each key
+    head among consecutive query heads.
+    """
+
+    def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, *,
+                 causal: bool = True, window: int | None = None, bias: bool = True,
+                 init_std: float = 0.02, out_init_std: float | None = None):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} query heads cannot share {n_kv_heads} key heads")
+        if head_dim % 16 or head_dim > 256:
+            raise ValueError(f"head_dim {head_dim} must be a multiple of 16 and at most 256")
+        self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
+        self.scale, self.causal, self.window, self.has_bias = float(scale), causal, window, bias
+        self.q_width = n_heads * head_dim
+        self.kv_width = n_kv_heads * head_dim
+        self.proj_width = self.q_width + 2 * self.kv_width
+        self.init_std = init_std
+        self.out_init_std = init_std if out_init_std is None else out_init_std
+
+    def specs(self):
+        specs = {"qkv.weight": TensorSpec((self.width, self.proj_width), MATRIX, ("normal", self.init_std)),
+                 "out.weight": TensorSpec((self.q_width, self.width), MATRIX, ("normal", self.out_init_std))}
+        if self.has_bias:
+            specs["qkv.bias"] = TensorSpec((self.proj_width,), VECTOR, ("zeros",))
+            specs["out.bias"] = TensorSpec((self.width,), VECTOR, ("zeros",))
+        return specs
+
+    def cache_need(self):
+        return CacheNeed(kv=KvSpec(self.n_kv_heads, self.head_dim, self.window))
+
+    def _splits(self, ctx) -> int:
+        units = max(1, ctx.n_seqs * self.n_heads)
+        span = ctx.ctx_bound if self.window is None else min(ctx.ctx_bound, self.window)
+        by_work = max(1, (span + 127) // 128)           # at least 128 keys per split
+        by_fill = max(1, (2 * _SM_COUNT + units - 1) // units)
+        return int(min(by_work, by_fill, 64))
+
+    def forward(self, ctx, x, residual, entry, owns_cache=True):
+        n = ctx.n_tokens
+        dtype = x.dtype
+        proj = ctx.ws.take((n, self.proj_width), dtype)
+        linear(ctx, x, self.t_qkv_weight, self.t_qkv_bias if self.has_bias else None, proj, m=n)
+        k_pool, v_pool, group, g = ctx.cache.layer_pools(entry)
+        table = ctx.tables[g]
+        window = self.window or 0
+        if owns_cache:
+            kernels.kv_append(proj, self.q_width, self.q_width + self.kv_width, ctx.positions, ctx.token_seq,
+                              ctx.ctx_len, table, group.table_len, k_pool, v_pool, n, self.n_kv_heads, self.head_dim)
+        mixed = ctx.ws.take((n, self.q_width), dtype)
+        if ctx.is_decode:
+            splits = self._splits(ctx)
+            scratch = None
+            if splits > 1:
+                need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.n_heads, self.head_dim, splits)
+                scratch = ctx.ws.take((need,), torch.float32)
+            kernels.attention_decode(proj, mixed, k_pool, v_pool, table, group.table_len, ctx.ctx_len, ctx.n_seqs,
+                                     self.n_heads, self.n_kv_heads, self.head_dim, self.scale, window=window,
+                                     n_splits=splits, scratch=scratch)
+        elif ctx.fresh and owns_cache:
+            # every sequence starts at position 0: keys and values are the step's own projections
+            kernels.attention_prefill_simt(proj, mixed, ctx.seq_start, ctx.past_len, ctx.n_seqs, ctx.max_new,
+                                           self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+                                           causal=self.causal, window=window,
+                                           k_offset=self.q_width, v_offset=self.q_width + self.kv_width)
+        else:
+            if group.is_ring:
+                raise CacheError("a step that brings several tokens to sequences that already hold some is not "
+                                 "supported for windowed layers: their ring of pages keeps one window only")
+            kernels.attention_prefill_simt(proj, mixed, ctx.seq_start, ctx.past_len, ctx.n_seqs, ctx.max_new,
+                                           self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+                                           causal=self.causal, window=window, k_pool=k_pool, v_pool=v_pool,
+                                           table=table, table_len=group.table_len)
+        linear(ctx, mixed, self.t_out_weight, self.t_out_bias if self.has_bias else None, residual, m=n,
+               residual=residual)

@@ -1,0 +1,73 @@
+"""Interfaces of the parts a model is put together from.
+
+A part owns its sizes and constants as constructor arguments and its tensors by local names; it
+does not know which model it is in.  The model plan maps checkpoint names to (part, local name).
+
+    Norm            forward(ctx, x32, out_dtype, rows=None, n_rows=None) -> normalised rows
+    PositionEncoding  `table` to add to the token embedding, and/or rotate(ctx, proj, ...) inside a mixer
+    Mixer           cache_need() -> CacheNeed;  forward(ctx, x, residual, entry, owns_cache) adds its
+                    output to the 32-bit residual stream in place
+    FeedForward     forward(ctx, x, residual) adds its output to the residual stream in place
+    Block           forward(ctx, residual, entry, owns_cache) arranges norms, mixer and feed-forward
+
+`x` holds the step's tokens as rows, packed sequence after sequence (no padding); `ctx`
+(engine.step.StepContext) says which row belongs to which sequence and position.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.spec import CacheNeed
+from ..weights.spec import TensorSpec
+
+
+class Part:
+    """Something with tensors of its own."""
+
+    def specs(self) -> dict[str, TensorSpec]:
+        return {}
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        for name in self.specs():
+            setattr(self, "t_" + name.replace(".", "_"), tensors[name])
+
+    # Parts made only of this library's kernels can be captured in a CUDA graph.
+    graph_safe = True
+
+
+class Norm(Part):
+    def forward(self, ctx, x32, out_dtype, rows=None, n_rows=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Learned tables add to the embedding; rotary kinds act on queries and keys inside a mixer."""
+    adds_to_embedding = False
+    rotates = False
+
+    def max_positions(self) -> int | None:
+        return None
+
+
+class Mixer(Part):
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed()
+
+    def forward(self, ctx, x, residual, entry: int, owns_cache: bool = True) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x, residual) -> None:
+        raise NotImplementedError
+
+
+class Block(Part):
+    def parts(self) -> dict[str, Part]:
+        raise NotImplementedError
+
+    def cache_need(self) -> CacheNeed:
+        raise NotImplementedError
+
+    def forward(self, ctx, residual, entry: int, owns_cache: bool = True) -> None:
+        raise NotImplementedError
