@@ -10,7 +10,13 @@ from .engine import Engine, StepEntry
 from .errors import (BurnTransformersError, CacheError, CheckpointError, ConfigError, GenerationError, KernelError,
                      ShapeError, UnsupportedArchitecture)
 from .weights import write_random_model
+from .sampling import GenerationConfig, GeneratedSequence, FinishReason
+from .auto import (AutoCausalLm, AutoLoadOptions, CausalGenerationOutput, CausalGenerationRequest, LoadedModel,
+                   generate_causal, generate_causal_streaming)
+from .engine.generate import generate, plan_batches
 
 __all__ = ["CacheConfig", "Gpt2Config", "config_from_folder", "register_architecture", "supported_model_types",
            "Engine", "StepEntry", "BurnTransformersError", "CacheError", "CheckpointError", "ConfigError",
-           "GenerationError", "KernelError", "ShapeError", "UnsupportedArchitecture", "write_random_model"]
+           "GenerationError", "KernelError", "ShapeError", "UnsupportedArchitecture", "write_random_model", "GenerationConfig", "GeneratedSequence", "FinishReason",
+           "AutoCausalLm", "AutoLoadOptions", "CausalGenerationOutput", "CausalGenerationRequest", "LoadedModel",
+           "generate_causal", "generate_causal_streaming", "generate", "plan_batches"]

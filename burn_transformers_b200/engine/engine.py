@@ -22,11 +22,7 @@ from ..config.registry import config_from_folder
 from ..errors import CacheError, KernelError, ShapeError
 from ..weights.loader import COMPUTE_DTYPES, load_weights
 from .model import ModelPlan
-from .step import StepContext, StepEntry, Workspace
-
-
-def _align4(n: int) -> int:
-    return (n + 3) & ~3
+from .step import StepBuilder, StepContext, StepEntry
 
 
 class Engine:
@@ -47,9 +43,8 @@ class Engine:
                              f"{plan.max_context}")
         self.cache_config = cache_config
         self.cache = CacheBank(plan.cache_needs(), cache_config, self.dtype, self.device)
-        self.ws = Workspace(self.device)
-        self._meta_host = None
-        self._meta_dev = None
+        self.builder = StepBuilder(self.cache, self.dtype, self.device)
+        self.ws = self.builder.ws
         self.steps_run = 0
 
     # ---- construction ------------------------------------------------------------------
@@ -102,54 +97,6 @@ class Engine:
                 if not (0 <= int(w) < len(e.tokens)):
                     raise ShapeError(f"slot {e.slot}: wanted place {w} is outside the {len(e.tokens)} tokens of the step")
 
-    def _build_context(self, entries: list[StepEntry]) -> StepContext:
-        cache = self.cache
-        n_seqs = len(entries)
-        pasts = [cache.length(e.slot) for e in entries]
-        news = [len(e.tokens) for e in entries]
-        n_tokens = sum(news)
-        tokens, positions, token_seq, seq_start, want_rows = [], [], [], [0], []
-        for i, e in enumerate(entries):
-            base = seq_start[-1]
-            tokens.extend(int(t) for t in e.tokens)
-            positions.extend(range(pasts[i], pasts[i] + news[i]))
-            token_seq.extend([i] * news[i])
-            want_rows.extend(base + int(w) for w in e.want)
-            seq_start.append(base + news[i])
-        ctx_len = [p + n for p, n in zip(pasts, news)]
-        slots = [e.slot for e in entries]
-        width = cache.table_width
-        sections = [tokens, positions, token_seq, seq_start, pasts, ctx_len, slots, want_rows]
-        for g in range(len(cache.groups)):
-            flat = []
-            for e in entries:
-                row = cache.table_row(g, e.slot)
-                flat.extend(row)
-                flat.extend([0] * (width - len(row)))
-            sections.append(flat)
-        offsets, total = [], 0
-        for s in sections:
-            offsets.append(total)
-            total += _align4(max(1, len(s)))
-        if self._meta_host is None or self._meta_host.numel() < total:
-            cap = max(total, 4096)
-            self._meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
-            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
-        host = self._meta_host
-        for off, s in zip(offsets, sections):
-            if s:
-                host[off:off + len(s)] = torch.tensor(s, dtype=torch.int32)
-        self._meta_dev[:total].copy_(host[:total], non_blocking=True)
-        dev = self._meta_dev
-        view = lambda i: dev[offsets[i]:offsets[i] + max(1, len(sections[i]))]
-        tables = [view(8 + g).view(n_seqs, width) for g in range(len(cache.groups))]
-        self.h2d_bytes_last = total * 4
-        return StepContext(
-            dtype=self.dtype, cache=cache, ws=self.ws, n_tokens=n_tokens, n_seqs=n_seqs, n_want=len(want_rows),
-            max_new=max(news), is_decode=all(n == 1 for n in news), fresh=all(p == 0 for p in pasts),
-            ctx_bound=max(ctx_len), tokens=view(0), positions=view(1), token_seq=view(2), seq_start=view(3),
-            past_len=view(4), ctx_len=view(5), slots=view(6), want_rows=view(7), tables=tables, host_slots=slots)
-
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Runs the entries' tokens as one batch and returns logits [wanted, vocab] (float32, on the device),
         in the order of the entries and of their `want` lists; None when nothing is wanted.
@@ -158,7 +105,7 @@ class Engine:
         self._validate(entries)
         self.cache.reserve([(e.slot, self.cache.length(e.slot) + len(e.tokens)) for e in entries])
         self.ws.reset()
-        ctx = self._build_context(entries)
+        ctx = self.builder.build(entries)
         logits = self.plan.forward(ctx)
         for e in entries:
             self.cache.commit(e.slot, self.cache.length(e.slot) + len(e.tokens))

@@ -1,0 +1,121 @@
+"""The generation loop above the step function.
+
+Requests are served in batches that start together: all prompts of a batch run in one step,
+then every unfinished sequence gets one token per step; a sequence that stops leaves the
+batch and neither emits nor touches the cache again (src/generation/causal.rs:16-20, 118-211 of
+NoahIsCool/burn-transformers).  When a batch has ended its slots are given back and the next
+batch starts, until every request is served.
+
+The loop only decides; it asks an engine for logits and a sampler for ids, so its decisions can
+be tested with stand-ins for both.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+from typing import Callable
+
+from ..cache.spec import PAGE_SIZE
+from ..errors import GenerationError
+from ..sampling.config import GenerationConfig
+from ..sampling.tracker import FinishReason, GeneratedSequence, SequenceTracker
+from .step import StepEntry
+
+
+@dataclasses.dataclass
+class GenerationToken:
+    """One emitted token, as handed to a streaming callback (src/generation/causal.rs:64-77)."""
+    sequence: int
+    step: int
+    token_id: int
+    log_probability: float
+    finish_reason: FinishReason | None
+
+
+def pages(tokens: int) -> int:
+    return -(-tokens // PAGE_SIZE)
+
+
+def plan_batches(prompt_lengths: list[int], max_new_tokens: int, *, max_tokens: int, max_slots: int,
+                 max_context: int, max_batch: int | None = None) -> list[list[int]]:
+    """Cuts the requests, in order, into batches that fit the cache.
+
+    A sequence may grow to prompt + max_new_tokens - 1 cached tokens (the last emitted token is
+    never fed back; src/generation/bookkeeping.rs:742-747); a batch fits when the sum of those
+    lengths, each rounded up to a whole page, stays within max_tokens and its size within
+    max_slots (and max_batch)."""
+    limit = min(max_slots, max_batch) if max_batch else max_slots
+    if limit <= 0:
+        raise GenerationError("max_batch must be greater than zero")
+    batches: list[list[int]] = []
+    current: list[int] = []
+    used = 0
+    for index, n in enumerate(prompt_lengths):
+        if n <= 0:
+            raise GenerationError(f"prompt {index} is empty: every sequence needs at least one token")
+        longest = n + max_new_tokens - 1
+        if longest > max_context:
+            raise GenerationError(f"prompt {index}: {n} prompt tokens + {max_new_tokens} new tokens need "
+                                  f"{longest} positions, the cache allows {max_context}")
+        need = pages(longest) * PAGE_SIZE
+        if need > max_tokens:
+            raise GenerationError(f"prompt {index}: needs {need} cached tokens, the cache holds {max_tokens}")
+        if current and (used + need > max_tokens or len(current) >= limit):
+            batches.append(current)
+            current, used = [], 0
+        current.append(index)
+        used += need
+    if current:
+        batches.append(current)
+    return batches
+
+
+def run_batch(engine, sampler, trackers: list[SequenceTracker], on_token: Callable | None = None) -> None:
+    """Serves one batch to its end.  `engine` needs new_sequence/step/release; `sampler` needs select."""
+    slots = {}
+    try:
+        for t in trackers:
+            slots[t.request] = engine.new_sequence()
+        for row, t in enumerate(trackers):
+            t.row_in_batch = row
+        logits = engine.step([StepEntry(slots[t.request], t.prompt, [len(t.prompt) - 1]) for t in trackers])
+        active = list(trackers)
+        batch_rows = len(trackers)
+        while active:
+            ids, logps = sampler.select(logits, active, batch_rows)
+            going = []
+            for t, token, logp in zip(active, ids, logps):
+                if not math.isfinite(logp):
+                    raise GenerationError(f"sequence {t.request}: the selected token {token} has a non-finite "
+                                          f"log-probability {logp}; generation stops before emitting it")
+                reason = t.push(int(token), float(logp))
+                if on_token is not None:
+                    on_token(GenerationToken(t.request, t.emitted - 1, int(token), float(logp), reason))
+                if reason is None:
+                    going.append(t)
+            active = going
+            if not active:
+                break
+            logits = engine.step([StepEntry(slots[t.request], [t.output.token_ids[-1]], [0]) for t in active])
+    finally:
+        for slot in slots.values():
+            engine.release(slot)
+
+
+def generate(engine, prompts: list[list[int]], config: GenerationConfig, *, max_batch: int | None = None,
+             on_token: Callable | None = None, sampler=None) -> list[GeneratedSequence]:
+    """Generates a continuation for every prompt; results come in the order of the prompts."""
+    vocab = engine.plan.vocab
+    config.validate(vocab)
+    if not prompts:
+        raise GenerationError("generation needs at least one prompt")
+    cache = engine.cache_config
+    batches = plan_batches([len(p) for p in prompts], config.max_new_tokens, max_tokens=cache.max_tokens,
+                           max_slots=cache.max_slots, max_context=cache.max_context, max_batch=max_batch)
+    if sampler is None:
+        from ..sampling.sampler import DeviceSampler
+        sampler = DeviceSampler(config, vocab, engine.device, max(len(b) for b in batches))
+    trackers = [SequenceTracker(i, p, config) for i, p in enumerate(prompts)]
+    for batch in batches:
+        run_batch(engine, sampler, [trackers[i] for i in batch], on_token)
+    return [t.output for t in trackers]

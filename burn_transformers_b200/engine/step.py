@@ -54,7 +54,7 @@ class StepContext:
 
     def __init__(self, *, dtype, cache, ws, n_tokens, n_seqs, n_want, max_new, is_decode, fresh, ctx_bound,
                  tokens, positions, token_seq, seq_start, past_len, ctx_len, slots, want_rows, tables,
-                 host_slots=None):
+                 host_slots=None, host_seq_start=None, host_past_len=None):
         self.dtype = dtype
         self.cache, self.ws = cache, ws
         self.n_tokens, self.n_seqs, self.n_want, self.max_new = n_tokens, n_seqs, n_want, max_new
@@ -66,4 +66,71 @@ class StepContext:
         self.seq_start, self.past_len, self.ctx_len, self.slots = seq_start, past_len, ctx_len, slots
         self.want_rows = want_rows
         self.tables = tables            # per cache group: [n_seqs, table_width] page ids
-        self.host_slots = host_slots    # the slots as a Python list, for parts that index state on the host
+        # the same facts as Python lists, for parts that plan on the host
+        self.host_slots, self.host_seq_start, self.host_past_len = host_slots, host_seq_start, host_past_len
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class StepBuilder:
+    """Turns a step's entries into a StepContext: packs the tokens, computes positions from the cache's
+    lengths, and sends all integer tables of the step to the device in one copy from pinned memory."""
+
+    def __init__(self, cache, dtype, device):
+        self.cache, self.dtype, self.device = cache, dtype, torch.device(device)
+        self.ws = Workspace(self.device)
+        self._host = None
+        self._dev = None
+        self.h2d_bytes_last = 0
+
+    def build(self, entries: list[StepEntry]) -> StepContext:
+        cache = self.cache
+        n_seqs = len(entries)
+        pasts = [cache.length(e.slot) for e in entries]
+        news = [len(e.tokens) for e in entries]
+        tokens, positions, token_seq, seq_start, want_rows = [], [], [], [0], []
+        for i, e in enumerate(entries):
+            base = seq_start[-1]
+            tokens.extend(int(t) for t in e.tokens)
+            positions.extend(range(pasts[i], pasts[i] + news[i]))
+            token_seq.extend([i] * news[i])
+            want_rows.extend(base + int(w) for w in e.want)
+            seq_start.append(base + news[i])
+        ctx_len = [p + n for p, n in zip(pasts, news)]
+        slots = [e.slot for e in entries]
+        width = cache.table_width
+        sections = [tokens, positions, token_seq, seq_start, pasts, ctx_len, slots, want_rows]
+        for g in range(len(cache.groups)):
+            flat = []
+            for e in entries:
+                row = cache.table_row(g, e.slot)
+                flat.extend(row)
+                flat.extend([0] * (width - len(row)))
+            sections.append(flat)
+        offsets, total = [], 0
+        for s in sections:
+            offsets.append(total)
+            total += _align4(max(1, len(s)))
+        if self._host is None or self._host.numel() < total:
+            cap = max(total, 4096)
+            self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        flat_all = []
+        for off, s in zip(offsets, sections):
+            flat_all.extend([0] * (off - len(flat_all)))
+            flat_all.extend(s)
+        flat_all.extend([0] * (total - len(flat_all)))
+        self._host[:total] = torch.tensor(flat_all, dtype=torch.int32)
+        self._dev[:total].copy_(self._host[:total], non_blocking=True)
+        self.h2d_bytes_last = total * 4
+        dev = self._dev
+        view = lambda i: dev[offsets[i]:offsets[i] + max(1, len(sections[i]))]
+        tables = [view(8 + g).view(n_seqs, width) for g in range(len(cache.groups))]
+        return StepContext(
+            dtype=self.dtype, cache=cache, ws=self.ws, n_tokens=len(tokens), n_seqs=n_seqs, n_want=len(want_rows),
+            max_new=max(news), is_decode=all(n == 1 for n in news), fresh=all(p == 0 for p in pasts),
+            ctx_bound=max(ctx_len), tokens=view(0), positions=view(1), token_seq=view(2), seq_start=view(3),
+            past_len=view(4), ctx_len=view(5), slots=view(6), want_rows=view(7), tables=tables, host_slots=slots,
+            host_seq_start=seq_start, host_past_len=pasts)

@@ -97,6 +97,7 @@ def check(plan: WeightPlan, entries: dict[str, st.TensorEntry]) -> tuple[str, di
                               f"not {list(other.shape)} {other.dtype}")
         else:
             tied_entries[alias] = (entry, other)
+    mismatched.sort()
     if missing or unexpected or mismatched:
         parts = []
         if missing:

@@ -1,0 +1,362 @@
+"""Each CUDA kernel alone against a plain float64 formula, at sizes other than the engine's."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2 as plain
+from burn_transformers_b200 import kernels
+from burn_transformers_b200.errors import KernelError, ShapeError
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+PAGE = kernels.PAGE_SIZE
+# a kernel's own error: 32-bit sums of a few hundred terms; bfloat16 outputs are rounded to 8 bits once
+TOL = {torch.float32: 2e-6, torch.bfloat16: 4e-3}
+
+
+def rel(got, want):
+    got, want = got.double().cpu(), want.double().cpu()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+@pytest.fixture(autouse=True)
+def _seed():
+    torch.manual_seed(1234)
+
+
+def test_library_is_the_built_one():
+    lib = kernels.library()
+    assert lib.bt_abi_version() == 1
+    with pytest.raises(KernelError, match="CUDA device only"):
+        kernels.layernorm(torch.zeros(2, 8), torch.ones(8), None, torch.zeros(2, 8), 1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width, vocab, n_pos", [(40, 33, 17), (1000, 129, 70)])
+def test_embed(dtype, width, vocab, n_pos):
+    wte = torch.randn(vocab, width, device=DEV).to(dtype)
+    wpe = torch.randn(n_pos, width, device=DEV).to(dtype)
+    tok = torch.randint(0, vocab, (23,), device=DEV, dtype=torch.int32)
+    pos = torch.randint(0, n_pos, (23,), device=DEV, dtype=torch.int32)
+    out = torch.empty(23, width, device=DEV)
+    kernels.embed(tok, pos, wte, wpe, out)
+    assert rel(out, wte.double()[tok.long()] + wpe.double()[pos.long()]) < 2e-7   # one 32-bit add
+    kernels.embed(tok, pos, wte, None, out)
+    assert torch.equal(out, wte.float()[tok.long()])
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    tok[5] = vocab
+    kernels.embed(tok, pos, wte, wpe, out, status=status)
+    assert int(status) == 6 and float(out[5].abs().max()) == 0.0     # reported, nothing read outside the table
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width, eps", [(24, 1e-5), (770, 1e-6), (4099, 1e-3)])
+def test_layernorm(out_dtype, width, eps):
+    x = torch.randn(13, width, device=DEV) * 5 + 100.0        # a large mean: E[x^2]-E[x]^2 would lose it
+    g, b = torch.randn(width, device=DEV), torch.randn(width, device=DEV)
+    out = torch.empty(13, width, device=DEV, dtype=out_dtype)
+    kernels.layernorm(x, g, b, out, eps)
+    want = torch.nn.functional.layer_norm(x.double(), (width,), g.double(), b.double(), eps)
+    assert rel(out, want) < (1e-5 if out_dtype == torch.float32 else 4e-3)
+    rows = torch.tensor([12, 0, 0, 7], dtype=torch.int32, device=DEV)
+    picked = torch.empty(4, width, device=DEV, dtype=out_dtype)
+    kernels.layernorm(x, g, None, picked, eps, rows=rows)
+    want = torch.nn.functional.layer_norm(x.double()[rows.long()], (width,), g.double(), None, eps)
+    assert rel(picked, want) < (1e-5 if out_dtype == torch.float32 else 4e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m, n, k", [(1, 50, 24), (7, 777, 240), (65, 64, 17), (200, 130, 1000)])
+@pytest.mark.parametrize("nk", [False, True])
+def test_linear_simt(dtype, m, n, k, nk):
+    a = torch.randn(m, k, device=DEV).to(dtype)
+    w = torch.randn(k, n, device=DEV).to(dtype)
+    bias, res = torch.randn(n, device=DEV), torch.randn(m, n, device=DEV)
+    w_arg = w.t().contiguous() if nk else w
+    plain_product = a.double() @ w.double()
+    out = torch.empty(m, n, device=DEV)
+    kernels.linear_simt(a, w_arg, None, out, w_is_nk=nk)
+    assert rel(out, plain_product) < 2e-6
+    for act, fn in (("gelu_new", lambda t: torch.nn.functional.gelu(t, approximate="tanh")),
+                    ("gelu", torch.nn.functional.gelu)):
+        out = res.clone()
+        kernels.linear_simt(a, w_arg, bias, out, w_is_nk=nk, activation=act, residual=out)     # in place
+        assert rel(out, fn(plain_product + bias.double()) + res.double()) < 2e-6
+    if dtype == torch.bfloat16:
+        low = torch.empty(m, n, device=DEV, dtype=dtype)
+        kernels.linear_simt(a, w_arg, bias, low, w_is_nk=nk)
+        assert rel(low, plain_product + bias.double()) < 4e-3
+    # rows beyond m are not touched
+    big = torch.full((m + 3, n), 7.0, device=DEV)
+    kernels.linear_simt(a, w_arg, None, big, m=m, w_is_nk=nk)
+    assert float((big[m:] - 7.0).abs().max()) == 0.0
+    with pytest.raises(ShapeError):
+        kernels.linear_simt(a, w_arg, None, torch.empty(m, n + 1, device=DEV), w_is_nk=nk)
+
+
+# ---- attention ---------------------------------------------------------------------------------
+
+def make_paged(lengths, n_kv_heads, head_dim, dtype, table_len=None, extra_pages=3):
+    """Random keys and values in shuffled pages.  Returns pools, table and the dense [seq][pos] copies."""
+    n = len(lengths)
+    width = max(-(-max(lengths) // PAGE), 1) if table_len is None else table_len
+    n_pages = n * width + extra_pages
+    order = torch.randperm(n_pages).tolist()
+    table = torch.zeros(n, width, dtype=torch.int32)
+    k_pool = torch.randn(n_pages, n_kv_heads, PAGE, head_dim).to(dtype)
+    v_pool = torch.randn(n_pages, n_kv_heads, PAGE, head_dim).to(dtype)
+    for s in range(n):
+        for i in range(width):
+            table[s, i] = order.pop()
+    dense_k, dense_v = [], []
+    for s, length in enumerate(lengths):
+        pos = torch.arange(length)
+        pages = table[s, (pos // PAGE) % width].long()
+        dense_k.append(k_pool[pages, :, pos % PAGE].double())      # [L, H, hd]
+        dense_v.append(v_pool[pages, :, pos % PAGE].double())
+    return k_pool.to(DEV), v_pool.to(DEV), table.to(DEV), dense_k, dense_v
+
+
+def attend(q, k, v, scale, q_pos, window=0, causal=True):
+    """q: [Q, Hq, hd]; k, v: [L, Hkv, hd] float64; q_pos: position of each query."""
+    hq, hkv = q.shape[1], k.shape[1]
+    out = torch.zeros_like(q)
+    pos = torch.arange(k.shape[0])
+    for h in range(hq):
+        s = (q[:, h] @ k[:, h // (hq // hkv)].T) * scale
+        hidden = torch.zeros_like(s, dtype=torch.bool)
+        if causal:
+            hidden |= pos[None, :] > q_pos[:, None]
+        if window:
+            hidden |= pos[None, :] <= q_pos[:, None] - window
+        s = s.masked_fill(hidden, -math.inf)
+        p = torch.softmax(s, dim=-1).nan_to_num(0.0)
+        out[:, h] = p @ v[:, h // (hq // hkv)]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hq, hkv, hd, window, splits", [
+    (4, 4, 16, 0, 1), (5, 5, 48, 0, 3), (6, 2, 80, 0, 2), (8, 1, 128, 100, 4), (2, 2, 256, 0, 1), (3, 3, 32, 64, 7)])
+def test_attention_decode(dtype, hq, hkv, hd, window, splits):
+    lengths = [1, 63, 64, 65, 300, 129]
+    k_pool, v_pool, table, dk, dv = make_paged(lengths, hkv, hd, dtype)
+    n = len(lengths)
+    q = torch.randn(n, (hq + 2 * hkv) * hd, device=DEV).to(dtype)     # queries inside a wider projection row
+    ctx_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    out = torch.empty(n, hq * hd, device=DEV, dtype=dtype)
+    scratch = torch.empty(max(1, kernels.attention_decode_scratch_floats(n, hq, hd, splits)), device=DEV)
+    scale = 0.37
+    kernels.attention_decode(q, out, k_pool, v_pool, table, table.shape[1], ctx_len, n, hq, hkv, hd, scale,
+                             window=window, n_splits=splits, scratch=scratch)
+    for s, length in enumerate(lengths):
+        qs = q[s, :hq * hd].double().cpu().view(1, hq, hd)
+        want = attend(qs, dk[s], dv[s], scale, torch.tensor([length - 1]), window)
+        assert rel(out[s].view(1, hq, hd), want) < TOL[dtype] * 2, f"sequence {s} of length {length}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("target", [0, 63, 64, 437, 699])
+@pytest.mark.parametrize("splits", [1, 5])
+def test_attention_decode_finds_one_far_key_among_hundreds(dtype, target, splits):
+    """With near-uniform random scores a lost key changes the result by 1/700, less than a bfloat16 rounding.
+    Here one key matches the query and carries a value of its own, so losing it changes everything."""
+    hq = hkv = 2
+    hd, length = 64, 700
+    k_pool, v_pool, table, dk, dv = make_paged([length], hkv, hd, dtype)
+    q = torch.randn(1, hq * hd, device=DEV).to(dtype)
+    page, row = int(table[0, target // PAGE]), target % PAGE
+    for h in range(hq):
+        k_pool[page, h, row] = (q[0, h * hd:(h + 1) * hd].float() * 4.0).to(dtype)      # score ~ 4 |q|^2 >> the rest
+        v_pool[page, h, row] = 50.0 + h
+    ctx_len = torch.tensor([length], dtype=torch.int32, device=DEV)
+    out = torch.empty(1, hq * hd, device=DEV, dtype=dtype)
+    scratch = torch.empty(max(1, kernels.attention_decode_scratch_floats(1, hq, hd, splits)), device=DEV)
+    kernels.attention_decode(q, out, k_pool, v_pool, table, table.shape[1], ctx_len, 1, hq, hkv, hd, 1.0,
+                             n_splits=splits, scratch=scratch)
+    got = out.float().view(hq, hd)
+    for h in range(hq):
+        assert float((got[h] - (50.0 + h)).abs().max()) < 0.5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_decode_window_edge(dtype):
+    """The key just outside the window would win the softmax if it were seen; the key just inside must be seen."""
+    hd, length, window = 32, 200, 70
+    for inside in (True, False):
+        k_pool, v_pool, table, _, _ = make_paged([length], 1, hd, dtype)
+        q = torch.randn(1, hd, device=DEV).to(dtype)
+        target = length - window if inside else length - window - 1
+        page, row = int(table[0, target // PAGE]), target % PAGE
+        k_pool[page, 0, row] = (q[0].float() * 4.0).to(dtype)
+        v_pool[page, 0, row] = 90.0
+        out = torch.empty(1, hd, device=DEV, dtype=dtype)
+        scratch = torch.empty(kernels.attention_decode_scratch_floats(1, 1, hd, 2), device=DEV)
+        kernels.attention_decode(q, out, k_pool, v_pool, table, table.shape[1],
+                                 torch.tensor([length], dtype=torch.int32, device=DEV), 1, 1, 1, hd, 1.0,
+                                 window=window, n_splits=2, scratch=scratch)
+        assert (float(out.float().mean()) > 80.0) == inside
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hq, hkv, hd, window, causal", [
+    (4, 4, 16, 0, True), (5, 5, 48, 0, True), (6, 3, 80, 0, True), (2, 1, 128, 40, True), (2, 2, 256, 0, True),
+    (3, 3, 64, 0, False)])
+def test_attention_prefill_packed_and_paged(dtype, hq, hkv, hd, window, causal):
+    """Several new tokens per sequence: from the step's own projections (sequences that start at 0) and from
+    the pages (sequences that already hold tokens), with unequal lengths."""
+    news, pasts = [1, 17, 64, 100], [0, 0, 0, 0]
+    width = (hq + 2 * hkv) * hd
+    n_tok = sum(news)
+    proj = torch.randn(n_tok, width, device=DEV).to(dtype)
+    seq_start = torch.tensor([0] + list(np.cumsum(news)), dtype=torch.int32, device=DEV)
+    out = torch.empty(n_tok, hq * hd, device=DEV, dtype=dtype)
+    scale = 0.3
+    kernels.attention_prefill_simt(proj, out, seq_start, torch.tensor(pasts, dtype=torch.int32, device=DEV),
+                                   len(news), max(news), hq, hkv, hd, scale, causal=causal, window=window,
+                                   k_offset=hq * hd, v_offset=(hq + hkv) * hd)
+    p64 = proj.double().cpu()
+    for s, n in enumerate(news):
+        rows = p64[int(seq_start[s]):int(seq_start[s]) + n]
+        q = rows[:, :hq * hd].view(n, hq, hd)
+        k = rows[:, hq * hd:(hq + hkv) * hd].view(n, hkv, hd)
+        v = rows[:, (hq + hkv) * hd:].view(n, hkv, hd)
+        want = attend(q, k, v, scale, torch.arange(n), window, causal)
+        got = out[int(seq_start[s]):int(seq_start[s]) + n].view(n, hq, hd)
+        assert rel(got, want) < TOL[dtype] * 2, f"packed, sequence {s}"
+    if not causal:
+        return
+    # paged: sequences hold `past` tokens already; the new tokens' keys are appended first
+    pasts = [0, 5, 64, 130]
+    lengths = [p + n for p, n in zip(pasts, news)]
+    k_pool, v_pool, table, dk, dv = make_paged(lengths, hkv, hd, dtype)
+    positions = torch.cat([torch.arange(p, p + n) for p, n in zip(pasts, news)]).to(torch.int32).to(DEV)
+    token_seq = torch.cat([torch.full((n,), s) for s, n in enumerate(news)]).to(torch.int32).to(DEV)
+    ctx_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    kernels.kv_append(proj, hq * hd, (hq + hkv) * hd, positions, token_seq, ctx_len, table, table.shape[1], k_pool,
+                      v_pool, n_tok, hkv, hd)
+    kernels.attention_prefill_simt(proj, out, seq_start, torch.tensor(pasts, dtype=torch.int32, device=DEV),
+                                   len(news), max(news), hq, hkv, hd, scale, causal=True, window=window,
+                                   k_pool=k_pool, v_pool=v_pool, table=table, table_len=table.shape[1])
+    for s, n in enumerate(news):
+        rows = p64[int(seq_start[s]):int(seq_start[s]) + n]
+        k = torch.cat([dk[s][:pasts[s]], rows[:, hq * hd:(hq + hkv) * hd].view(n, hkv, hd)])
+        v = torch.cat([dv[s][:pasts[s]], rows[:, (hq + hkv) * hd:].view(n, hkv, hd)])
+        want = attend(rows[:, :hq * hd].view(n, hq, hd), k, v, scale, torch.arange(pasts[s], pasts[s] + n), window)
+        got = out[int(seq_start[s]):int(seq_start[s]) + n].view(n, hq, hd)
+        assert rel(got, want) < TOL[dtype] * 2, f"paged, sequence {s}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_prefill_never_looks_ahead(dtype):
+    """A future key that matches the query perfectly must not be seen; the same key in the past must."""
+    hd, n = 32, 90
+    proj = (torch.randn(n, 3 * hd, device=DEV) * 0.1).to(dtype)
+    seq_start = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    past = torch.zeros(1, dtype=torch.int32, device=DEV)
+    query, key = 40, 41
+    proj[query, :hd] = 3.0
+    proj[key, hd:2 * hd] = 3.0
+    proj[key, 2 * hd:] = 70.0
+    out = torch.empty(n, hd, device=DEV, dtype=dtype)
+    kernels.attention_prefill_simt(proj, out, seq_start, past, 1, n, 1, 1, hd, 1.0, k_offset=hd, v_offset=2 * hd)
+    assert float(out[query].float().abs().max()) < 5.0          # key 41 is in query 40's future
+    proj[query + 2, :hd] = 3.0
+    kernels.attention_prefill_simt(proj, out, seq_start, past, 1, n, 1, 1, hd, 1.0, k_offset=hd, v_offset=2 * hd)
+    assert float(out[query + 2].float().min()) > 60.0           # and in query 42's past
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_kv_append_pages_and_ring(dtype):
+    hkv, hd = 3, 16
+    news, pasts = [70, 1], [60, 127]
+    lengths = [p + n for p, n in zip(pasts, news)]
+    n_tok = sum(news)
+    proj = torch.randn(n_tok, 5 * hkv * hd, device=DEV).to(dtype)
+    k_off, v_off = hkv * hd, 3 * hkv * hd
+    positions = torch.cat([torch.arange(p, p + n) for p, n in zip(pasts, news)]).to(torch.int32).to(DEV)
+    token_seq = torch.cat([torch.full((n,), s) for s, n in enumerate(news)]).to(torch.int32).to(DEV)
+    ctx_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    table = torch.tensor([[5, 2, 7], [1, 4, 0]], dtype=torch.int32, device=DEV)
+    k_pool = torch.zeros(8, hkv, PAGE, hd, device=DEV, dtype=dtype)
+    v_pool = torch.zeros_like(k_pool)
+    kernels.kv_append(proj, k_off, v_off, positions, token_seq, ctx_len, table, 3, k_pool, v_pool, n_tok, hkv, hd)
+    for t in range(n_tok):
+        s, pos = int(token_seq[t]), int(positions[t])
+        page = int(table[s, pos // PAGE])
+        assert torch.equal(k_pool[page, :, pos % PAGE].reshape(-1), proj[t, k_off:k_off + hkv * hd])
+        assert torch.equal(v_pool[page, :, pos % PAGE].reshape(-1), proj[t, v_off:v_off + hkv * hd])
+    assert int((k_pool.float().abs().sum(dim=(1, 3)) > 0).sum()) == n_tok           # nothing else was written
+    # a ring of one page keeps the last 64 positions only
+    k_pool.zero_(); v_pool.zero_()
+    kernels.kv_append(proj, k_off, v_off, positions, token_seq, ctx_len, table, 1, k_pool, v_pool, n_tok, hkv, hd)
+    for t in range(n_tok):
+        s, pos = int(token_seq[t]), int(positions[t])
+        kept = pos >= lengths[s] - PAGE
+        same = torch.equal(k_pool[int(table[s, 0]), :, pos % PAGE].reshape(-1), proj[t, k_off:k_off + hkv * hd])
+        assert same == kept
+
+
+# ---- selection ---------------------------------------------------------------------------------
+
+def run_sample(logits, **kw):
+    n = logits.shape[0]
+    ids = torch.empty(n, dtype=torch.int32, device=DEV)
+    logp = torch.empty(n, dtype=torch.float32, device=DEV)
+    kernels.sample(logits, n, out_ids=ids, out_logp=logp, **kw)
+    return ids.cpu().tolist(), logp.cpu().tolist()
+
+
+@pytest.mark.parametrize("vocab", [19, 777, 50257])
+def test_greedy_selection(vocab):
+    z = torch.randn(5, vocab, device=DEV) * 3
+    z[1, 7] = z[1, vocab - 1] = 50.0              # a tie: the lower index wins
+    z[2, vocab - 1] = 60.0
+    ids, logp = run_sample(z, do_sample=False)
+    want = torch.log_softmax(z.double(), dim=-1)
+    assert ids[1] == 7 and ids[2] == vocab - 1
+    for r in range(5):
+        assert ids[r] == int(torch.argmax(z[r]))
+        assert abs(logp[r] - float(want[r, ids[r]])) < 1e-4
+
+
+@pytest.mark.parametrize("vocab", [19, 1000, 50257])
+@pytest.mark.parametrize("options", [dict(), dict(top_k=5), dict(top_p=0.7), dict(min_p=0.05),
+                                     dict(top_k=40, top_p=0.9, min_p=0.01)])
+def test_sampling_follows_the_inverse_cdf(vocab, options):
+    temperature = 0.8
+    if "top_k" in options:
+        options = dict(options, top_k=min(options["top_k"], vocab - 1))
+    row = (torch.randn(vocab) * 2.5).float()
+    rows = 64
+    z = row.repeat(rows, 1).contiguous().to(DEV)
+    u = ((torch.arange(rows, dtype=torch.float64) + 0.5) / rows).float()
+    u[0], u[-1] = 2.0 ** -24, 1 - 2.0 ** -24
+    ids, logp = run_sample(z, do_sample=True, temperature=temperature, uniforms=u.to(DEV),
+                           top_k=options.get("top_k", 0), top_p=options.get("top_p", 1.0), min_p=options.get("min_p", 0.0))
+    processed = plain.process(row.double().numpy(), sample=True, temperature=temperature, **options)
+    kept = np.isfinite(processed)
+    assert all(kept[i] for i in ids), "a filtered token was drawn"
+    assert ids[0] == int(np.argmax(kept)) and ids[-1] == int(len(kept) - 1 - np.argmax(kept[::-1]))
+    e = np.where(kept, np.exp(processed - processed[kept].max()), 0.0)
+    c = np.cumsum(e / e.sum())
+    lsm = plain.log_softmax(np.where(kept, processed, -1e300))
+    for r in range(rows):
+        k = ids[r]
+        below = c[k - 1] if k > 0 else 0.0
+        assert below - 1e-5 <= float(u[r]) <= c[k] + 1e-5, f"row {r}: u={float(u[r])} outside [{below}, {c[k]}]"
+        assert abs(logp[r] - lsm[k]) < 2e-4
+
+
+def test_logit_edits():
+    z = torch.tensor([[1.0, -2.0, 3.0, 4.0, 0.5], [1.0, 1.0, 1.0, 1.0, 1.0]], device=DEV)
+    rows = torch.tensor([0, 0, 0, 1], dtype=torch.int32, device=DEV)
+    toks = torch.tensor([0, 1, 3, 4], dtype=torch.int32, device=DEV)
+    vals = torch.tensor([0.5, 2.0, 0.25, 0.0,      # (1 + .5) / 2 - .25 = 0.5
+                         0.0, 2.0, 0.0, 0.0,       # -2 * 2 = -4
+                         0.0, 1.0, 0.0, 1.0,       # banned
+                         1.0, 1.0, 3.0, 0.0], device=DEV)
+    kernels.logit_edits(z, rows, toks, vals, 4)
+    assert z.cpu().tolist() == [[0.5, -4.0, 3.0, -math.inf, 0.5], [1.0, 1.0, 1.0, 1.0, -1.0]]
