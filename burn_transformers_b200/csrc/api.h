@@ -6,6 +6,7 @@
 extern "C" {
 const char* bt_last_error();
 int bt_abi_version();
+long long bt_launch_count();
 
 int bt_embed(const int* tokens, const int* positions, const void* wte, const void* wpe, float* out, int n_tokens,
              int width, int vocab, int n_positions, int dtype, int* status, cudaStream_t stream);

@@ -1,4 +1,5 @@
 #include "common.cuh"
+#include <atomic>
 #include <cstdarg>
 
 namespace bt {
@@ -13,8 +14,12 @@ int fail(const char* fmt, ...) {
   va_end(args);
   return 1;
 }
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+long long launches() { return g_launches.load(std::memory_order_relaxed); }
 }  // namespace bt
 
+extern "C" long long bt_launch_count() { return bt::launches(); }
 extern "C" const char* bt_last_error() { return bt::error_buffer(); }
 
 // Compile-time facts a caller can check after loading the library.

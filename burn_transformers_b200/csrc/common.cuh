@@ -12,6 +12,9 @@ enum DType : int { kF32 = 0, kBF16 = 1 };
 // Last error text of the calling thread, read by bt_last_error().
 char* error_buffer();
 int fail(const char* fmt, ...);
+// Kernel launches issued through this library since it was loaded (launches recorded into a CUDA
+// graph count once, at capture).
+void count_launch();
 
 #define BT_CHECK(cond, ...)                                   \
   do {                                                        \
@@ -22,6 +25,7 @@ int fail(const char* fmt, ...);
   do {                                                                                       \
     cudaError_t e_ = cudaGetLastError();                                                     \
     if (e_ != cudaSuccess) return ::bt::fail("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
+    ::bt::count_launch();                                                                    \
   } while (0)
 
 __device__ __forceinline__ float to_float(float v) { return v; }

@@ -31,10 +31,16 @@ def library() -> ctypes.CDLL:
             raise KernelError(f"cannot load the CUDA kernel library {path}: {error}") from None
         lib.bt_last_error.restype = ctypes.c_char_p
         lib.bt_attention_decode_scratch_floats.restype = c_longlong
+        lib.bt_launch_count.restype = c_longlong
         if lib.bt_abi_version() != 1:
             raise KernelError(f"{path} has an unexpected interface version")
         _LIB = lib
     return _LIB
+
+
+def launch_count() -> int:
+    """Kernel launches issued through the library so far (a launch recorded into a CUDA graph counts once)."""
+    return int(library().bt_launch_count())
 
 
 def _check(code: int) -> None:
