@@ -252,3 +252,58 @@ extern "C" int bt_attention_decode(const void* q, long long q_row_stride, const 
                                         n_kv_heads, head_dim, scale, window, n_splits, stream);
   return fail("attention_decode: unknown dtype %d", dtype);
 }
+
+// ---------------------------------------------------------------------------------------------
+// The variant that allocates nothing (see attention_decode_static.h for who it is for and its rules).
+// ---------------------------------------------------------------------------------------------
+#include "attention_decode_static.h"
+#include <mutex>
+
+namespace bt {
+
+// The scratch of bt_attention_decode_static.  In host code this name is only a handle for the runtime:
+// the address a kernel may use is looked up per device with cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_decode_static_scratch[BT_DECODE_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+static float* g_decode_static_ptr[kMaxDevices] = {nullptr};
+static std::mutex g_decode_static_mutex;
+
+// Device address of the scratch array on the current device; looked up once per device.
+static int decode_static_scratch(float** ptr) {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  BT_CHECK(e == cudaSuccess, "attention_decode_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+  BT_CHECK(device >= 0 && device < kMaxDevices, "attention_decode_static: device %d is beyond the %d this library tracks",
+           device, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_decode_static_mutex);
+  if (g_decode_static_ptr[device] == nullptr) {
+    float* found = nullptr;
+    e = cudaGetSymbolAddress((void**)&found, g_decode_static_scratch);
+    BT_CHECK(e == cudaSuccess && found != nullptr, "attention_decode_static: cudaGetSymbolAddress failed on device %d: %s",
+             device, cudaGetErrorString(e));
+    g_decode_static_ptr[device] = found;
+  }
+  *ptr = g_decode_static_ptr[device];
+  return 0;
+}
+
+}  // namespace bt
+
+extern "C" int bt_attention_decode_static(const void* q, long long q_row_stride, const void* k_pool,
+                                          const void* v_pool, const int* kv_table, int table_stride, int table_len,
+                                          int page_size, void* out, const int* ctx_len, int n_seqs, int n_heads,
+                                          int n_kv_heads, int head_dim, float scale, int window, int n_splits,
+                                          int dtype, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_seqs >= 0 && n_heads > 0 && head_dim > 0 && n_splits >= 1, "attention_decode_static: bad sizes");
+  const long long need = (long long)n_seqs * n_heads * n_splits * (head_dim + 2);
+  BT_CHECK(need <= (long long)BT_DECODE_STATIC_SCRATCH_FLOATS,
+           "attention_decode_static: %d sequences x %d heads x %d splits x (%d + 2) = %lld floats of scratch exceed the "
+           "built-in %d; use fewer splits or bt_attention_decode with scratch of your own",
+           n_seqs, n_heads, n_splits, head_dim, need, BT_DECODE_STATIC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  if (int rc = decode_static_scratch(&scratch)) return rc;
+  return bt_attention_decode(q, q_row_stride, k_pool, v_pool, kv_table, table_stride, table_len, page_size, out, scratch,
+                             ctx_len, n_seqs, n_heads, n_kv_heads, head_dim, scale, window, n_splits, dtype, stream);
+}

@@ -1,0 +1,80 @@
+"""The decode-attention entry point that allocates nothing, called through its exported C symbol.
+
+`bt_attention_decode_static` is for callers that cannot get device memory of their own (a plug-in that is
+handed only its inputs and outputs, a serving loop that forbids cudaMalloc after start-up): it keeps the
+scratch for its splits in an array inside the library.  It must give what `bt_attention_decode` gives with
+caller-owned scratch.  Two calls in a row, with different inputs and split counts, check that nothing left
+in the shared array by the first call leaks into the second.  This file is collected last on purpose.
+"""
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import pytest
+import torch
+
+from burn_transformers_b200 import kernels
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+PAGE = kernels.PAGE_SIZE
+STATIC_FLOATS = 1 << 20
+
+
+def paged(lengths, n_kv_heads, head_dim, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    width = -(-max(lengths) // PAGE)
+    n_pages = len(lengths) * width
+    order = torch.randperm(n_pages, generator=g)
+    table = order.view(len(lengths), width).to(torch.int32)
+    k = torch.randn(n_pages, n_kv_heads, PAGE, head_dim, generator=g).to(dtype)
+    v = torch.randn(n_pages, n_kv_heads, PAGE, head_dim, generator=g).to(dtype)
+    return k.to(DEV), v.to(DEV), table.to(DEV)
+
+
+def call_static(lib, q, k, v, table, ctx_len, out, n_heads, n_kv_heads, head_dim, scale, window, splits):
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    return lib.bt_attention_decode_static(
+        c_void_p(q.data_ptr()), c_longlong(q.shape[1]), c_void_p(k.data_ptr()), c_void_p(v.data_ptr()),
+        c_void_p(table.data_ptr()), c_int(table.shape[1]), c_int(table.shape[1]), c_int(PAGE), c_void_p(out.data_ptr()),
+        c_void_p(ctx_len.data_ptr()), c_int(q.shape[0]), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
+        c_float(scale), c_int(window), c_int(splits), c_int(kernels.DTYPE_CODE[q.dtype]), stream)
+
+
+@pytest.mark.parametrize("dtype, tol", [(torch.float32, 2e-6), (torch.bfloat16, 4e-3)])
+def test_static_scratch_entry_point_matches_the_ordinary_one(dtype, tol):
+    lib = kernels.library()
+    lib.bt_attention_decode_static.restype = c_int
+    calls = [dict(lengths=[700, 65, 1, 300], hq=6, hkv=2, hd=64, window=0, splits=5, seed=1),
+             dict(lengths=[129, 500], hq=4, hkv=4, hd=48, window=100, splits=3, seed=2)]
+    for c in calls:
+        k, v, table = paged(c["lengths"], c["hkv"], c["hd"], dtype, c["seed"])
+        n = len(c["lengths"])
+        q = torch.randn(n, c["hq"] * c["hd"], generator=torch.Generator().manual_seed(c["seed"])).to(dtype).to(DEV)
+        ctx_len = torch.tensor(c["lengths"], dtype=torch.int32, device=DEV)
+        want = torch.empty(n, c["hq"] * c["hd"], device=DEV, dtype=dtype)
+        scratch = torch.empty(kernels.attention_decode_scratch_floats(n, c["hq"], c["hd"], c["splits"]), device=DEV)
+        kernels.attention_decode(q, want, k, v, table, table.shape[1], ctx_len, n, c["hq"], c["hkv"], c["hd"], 0.3,
+                                 window=c["window"], n_splits=c["splits"], scratch=scratch)
+        got = torch.full_like(want, float("nan"))
+        before = torch.cuda.memory_allocated()
+        rc = call_static(lib, q, k, v, table, ctx_len, got, c["hq"], c["hkv"], c["hd"], 0.3, c["window"], c["splits"])
+        assert rc == 0, lib.bt_last_error().decode()
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == before
+        err = float((got.double() - want.double()).abs().max() / want.double().abs().max())
+        assert err <= tol, f"{c}: {err:.3e}"
+
+
+def test_static_scratch_entry_point_refuses_what_does_not_fit():
+    lib = kernels.library()
+    lib.bt_attention_decode_static.restype = c_int
+    n, hq, hd, splits = 64, 64, 128, 2                     # 64 * 64 * 2 * 130 floats > 2^20
+    assert n * hq * splits * (hd + 2) > STATIC_FLOATS
+    k, v, table = paged([10] * n, 1, hd, torch.bfloat16, 3)
+    q = torch.zeros(n, hq * hd, device=DEV, dtype=torch.bfloat16)
+    out = torch.zeros_like(q)
+    ctx_len = torch.full((n,), 10, dtype=torch.int32, device=DEV)
+    rc = call_static(lib, q, k, v, table, ctx_len, out, hq, 1, hd, 1.0, 0, splits)
+    message = lib.bt_last_error().decode()
+    assert rc != 0 and "exceed the built-in" in message and str(STATIC_FLOATS) in message
+    torch.cuda.synchronize()
