@@ -96,5 +96,6 @@ class ModelPlan:
             self.blocks[call.block].forward(ctx, residual, entry, owns)
         if ctx.n_want == 0:
             return None
-        h = self.final_norm.forward(ctx, residual, ctx.dtype, rows=ctx.want_rows, n_rows=ctx.n_want)
+        h = self.final_norm.forward(ctx, residual, ctx.dtype, rows=ctx.want_rows, n_rows=ctx.n_want,
+                                    lazy=getattr(self.readout, "accepts_lazy_norm", False))
         return self.readout.forward(ctx, h, ctx.n_want)

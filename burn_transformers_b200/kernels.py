@@ -142,6 +142,50 @@ def linear_simt(a, w, bias, out, *, m=None, w_is_nk=False, activation=None, resi
                                     c_int(_code(out.dtype)), _stream()))
 
 
+def linear_skinny_supports(m, n, k, w_is_nk, fuse_ln) -> bool:
+    return bool(library().bt_linear_skinny_supports(c_int(m), c_int(n), c_int(k), c_int(1 if w_is_nk else 0),
+                                                    c_int(1 if fuse_ln else 0)))
+
+
+def linear_skinny(a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=None, norm=None, split=0):
+    """out[:m] = act(rows @ w + bias) (+ residual) for at most 64 bfloat16 rows.
+
+    rows are `a` (bfloat16 [M, K]) or, when `norm` = (x32, gamma, beta, eps, row_index) is given and `a` is None,
+    LayerNorm(x32[row_index]) formed inside the kernel."""
+    n = w.shape[0] if w_is_nk else w.shape[1]
+    k = w.shape[1] if w_is_nk else w.shape[0]
+    _need(w, "w", torch.bfloat16, (n, k) if w_is_nk else (k, n))
+    _need(out, "out", (torch.float32, torch.bfloat16), (None, n))
+    if out.shape[0] < m:
+        raise ShapeError(f"linear_skinny: {m} rows asked of out[{out.shape[0]}]")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (n,))
+    if residual is not None:
+        _need(residual, "residual", torch.float32, (None, n))
+    if activation not in ACTIVATIONS:
+        raise ShapeError(f"linear_skinny: unknown activation {activation!r}")
+    x32 = gamma = beta = rows = None
+    eps = 0.0
+    if norm is not None:
+        x32, gamma, beta, eps, rows = norm
+        _need(x32, "x32", torch.float32, (None, k))
+        _need(gamma, "gamma", torch.float32, (k,))
+        if beta is not None:
+            _need(beta, "beta", torch.float32, (k,))
+        if rows is not None:
+            _need(rows, "rows", torch.int32)
+        elif x32.shape[0] < m:
+            raise ShapeError(f"linear_skinny: {m} rows asked of x32[{x32.shape[0]}]")
+    else:
+        _need(a, "a", torch.bfloat16, (None, k))
+        if a.shape[0] < m:
+            raise ShapeError(f"linear_skinny: {m} rows asked of a[{a.shape[0]}]")
+    _check(library().bt_linear_skinny(_ptr(a if norm is None else None), _ptr(x32), _ptr(rows), _ptr(gamma), _ptr(beta),
+                                      c_float(eps), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), c_int(m), c_int(n),
+                                      c_int(k), c_int(1 if w_is_nk else 0), c_int(ACTIVATIONS[activation]),
+                                      c_int(1 if out.dtype == torch.float32 else 0), c_int(split), _stream()))
+
+
 def kv_append(proj, k_offset, v_offset, positions, token_seq, ctx_len, table, table_len, k_pool, v_pool,
               n_tokens, n_kv_heads, head_dim):
     """Copies the new tokens' key and value channels of `proj` rows into the layer's pages."""

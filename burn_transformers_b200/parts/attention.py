@@ -24,6 +24,8 @@ class CausalSelfAttention(Mixer):
     head among consecutive query heads.
     """
 
+    accepts_lazy_norm = True
+
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, *,
                  causal: bool = True, window: int | None = None, bias: bool = True,
                  init_std: float = 0.02, out_init_std: float | None = None):
@@ -59,7 +61,7 @@ class CausalSelfAttention(Mixer):
 
     def forward(self, ctx, x, residual, entry, owns_cache=True):
         n = ctx.n_tokens
-        dtype = x.dtype
+        dtype = ctx.dtype
         proj = ctx.ws.take((n, self.proj_width), dtype)
         linear(ctx, x, self.t_qkv_weight, self.t_qkv_bias if self.has_bias else None, proj, m=n)
         k_pool, v_pool, group, g = ctx.cache.layer_pools(entry)

@@ -36,7 +36,11 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, ctx, x32, out_dtype, rows=None, n_rows=None):
+    fusable = False
+
+    def forward(self, ctx, x32, out_dtype, rows=None, n_rows=None, lazy=False):
+        """`lazy` allows (never obliges) the norm to return a handle that the consumer's first matrix product
+        resolves inside its kernel; only consumers that set `accepts_lazy_norm` are given one."""
         raise NotImplementedError
 
 
@@ -50,6 +54,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    accepts_lazy_norm = False   # True: `x` is only ever handed to parts.linear.linear
+
     def cache_need(self) -> CacheNeed:
         return CacheNeed()
 
@@ -58,6 +64,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_lazy_norm = False
+
     def forward(self, ctx, x, residual) -> None:
         raise NotImplementedError
 

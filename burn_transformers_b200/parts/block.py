@@ -22,7 +22,7 @@ class PreNormBlock(Block):
         return all(p.graph_safe for p in self.parts().values())
 
     def forward(self, ctx, residual, entry, owns_cache=True):
-        x = self.norm1.forward(ctx, residual, ctx.dtype)
+        x = self.norm1.forward(ctx, residual, ctx.dtype, lazy=self.mixer.accepts_lazy_norm)
         self.mixer.forward(ctx, x, residual, entry, owns_cache)
-        x = self.norm2.forward(ctx, residual, ctx.dtype)
+        x = self.norm2.forward(ctx, residual, ctx.dtype, lazy=self.feed_forward.accepts_lazy_norm)
         self.feed_forward.forward(ctx, x, residual)

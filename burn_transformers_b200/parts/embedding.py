@@ -27,6 +27,8 @@ class TiedReadout(Part):
     """logits = h @ table^T with the token embedding's table, no bias, 32-bit logits
     (src/models/gpt2/model.rs:496-513).  Owns no tensor: it borrows the embedding's."""
 
+    accepts_lazy_norm = True
+
     def __init__(self, embedding: TokenEmbedding):
         self.embedding = embedding
 

@@ -13,6 +13,8 @@ class DenseFeedForward(FeedForward):
     `gelu_new` is the tanh form, `gelu` the erf form; both are evaluated in 32-bit on the
     accumulator and rounded once."""
 
+    accepts_lazy_norm = True
+
     def __init__(self, width: int, inner: int, activation: str, *, bias: bool = True, init_std: float = 0.02,
                  down_init_std: float | None = None):
         if activation not in ACTIVATIONS:
@@ -31,7 +33,7 @@ class DenseFeedForward(FeedForward):
 
     def forward(self, ctx, x, residual):
         n = ctx.n_tokens
-        hidden = ctx.ws.take((n, self.inner), x.dtype)
+        hidden = ctx.ws.take((n, self.inner), ctx.dtype)
         linear(ctx, x, self.t_up_weight, self.t_up_bias if self.has_bias else None, hidden, m=n,
                activation=self.activation)
         linear(ctx, hidden, self.t_down_weight, self.t_down_bias if self.has_bias else None, residual, m=n,

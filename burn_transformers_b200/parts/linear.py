@@ -6,10 +6,37 @@ import torch
 from .. import kernels
 
 
+class LazyNorm:
+    """Rows that are still to be normalised: (32-bit rows, the norm part, an optional row index).
+
+    A product that can normalise on the way in takes it as it is; anything else calls `materialize`."""
+
+    def __init__(self, norm, x32, rows, n_rows):
+        self.norm, self.x32, self.rows, self.n_rows = norm, x32, rows, n_rows
+        self.dtype = torch.bfloat16
+
+    def materialize(self, ctx):
+        return self.norm.apply(ctx, self.x32, torch.bfloat16, self.rows, self.n_rows)
+
+
 def linear(ctx, a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=None):
     """out[:m] = act(a[:m] @ w + bias) (+ residual[:m]).
 
     32-bit operands always take the plain fused-multiply-add kernel: the 32-bit path has no
-    reduced-precision matrix mode.
-    """
+    reduced-precision matrix mode.  bfloat16 products of at most 64 rows take the weight-streaming kernel,
+    which can also normalise its rows on the way in."""
+    lazy = isinstance(a, LazyNorm)
+    if w.dtype == torch.bfloat16 and m <= 64:
+        n = w.shape[0] if w_is_nk else w.shape[1]
+        k = w.shape[1] if w_is_nk else w.shape[0]
+        fuse = lazy and m <= 16 and a.norm.fusable
+        if kernels.linear_skinny_supports(m, n, k, w_is_nk, fuse):
+            if lazy and not fuse:
+                a, lazy = a.materialize(ctx), False
+            norm = (a.x32, a.norm.t_weight, a.norm.t_bias if a.norm.has_bias else None, a.norm.eps, a.rows) if lazy else None
+            kernels.linear_skinny(None if lazy else a, w, bias, out, m=m, w_is_nk=w_is_nk, activation=activation,
+                                  residual=residual, norm=norm)
+            return
+    if lazy:
+        a = a.materialize(ctx)
     kernels.linear_simt(a, w, bias, out, m=m, w_is_nk=w_is_nk, activation=activation, residual=residual)

@@ -96,6 +96,54 @@ def test_linear_simt(dtype, m, n, k, nk):
         kernels.linear_simt(a, w_arg, None, torch.empty(m, n + 1, device=DEV), w_is_nk=nk)
 
 
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 64])
+@pytest.mark.parametrize("n, k, nk, split", [(768, 768, False, 0), (2304, 768, False, 1), (768, 3072, False, 8),
+                                             (104, 240, False, 4), (200, 96, False, 0), (1000, 96, True, 0),
+                                             (777, 240, True, 2), (50257, 64, True, 0)])
+def test_linear_skinny(m, n, k, nk, split):
+    a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(k, n, device=DEV) * 0.1).to(torch.bfloat16)
+    w_arg = w.t().contiguous() if nk else w
+    bias, res = torch.randn(n, device=DEV), torch.randn(m, n, device=DEV)
+    assert kernels.linear_skinny_supports(m, n, k, nk, False)
+    product = a.double() @ w.double()
+    out = res.clone()
+    kernels.linear_skinny(a, w_arg, bias, out, m=m, w_is_nk=nk, activation="gelu_new", residual=out, split=split)
+    want = torch.nn.functional.gelu(product + bias.double(), approximate="tanh") + res.double()
+    assert rel(out, want) < 2e-6
+    low = torch.full((m + 2, n), 3.0, device=DEV, dtype=torch.bfloat16)
+    kernels.linear_skinny(a, w_arg, None, low, m=m, w_is_nk=nk, split=split)
+    assert rel(low[:m], product) < 4e-3 and float((low[m:].float() - 3.0).abs().max()) == 0.0
+    # the same rows give the same result whatever else is in the call
+    if m > 1:
+        alone = torch.empty(1, n, device=DEV)
+        both = torch.empty(m, n, device=DEV)
+        kernels.linear_skinny(a[m - 1:].contiguous(), w_arg, bias, alone, m=1, w_is_nk=nk, split=split)
+        kernels.linear_skinny(a, w_arg, bias, both, m=m, w_is_nk=nk, split=split)
+        assert torch.equal(alone[0], both[m - 1])
+    # LayerNorm of 32-bit rows on the way in, rows picked by an index
+    if m <= 16 and kernels.linear_skinny_supports(m, n, k, nk, True):
+        x = torch.randn(m + 3, k, device=DEV) * 2 + 3
+        g, b = torch.randn(k, device=DEV), torch.randn(k, device=DEV)
+        rows = torch.randperm(m + 3, device=DEV)[:m].to(torch.int32)
+        normed = torch.nn.functional.layer_norm(x.double()[rows.long()], (k,), g.double(), b.double(), 1e-5)
+        normed = normed.float().to(torch.bfloat16).double()          # the kernel rounds the rows once too
+        out = torch.empty(m, n, device=DEV)
+        kernels.linear_skinny(None, w_arg, bias, out, m=m, w_is_nk=nk, norm=(x, g, b, 1e-5, rows), split=split)
+        assert rel(out, normed @ w.double() + bias.double()) < 2e-3   # a row value at a rounding tie may flip
+
+
+def test_linear_skinny_refuses_what_it_cannot_do():
+    assert not kernels.linear_skinny_supports(65, 64, 64, False, False)
+    assert not kernels.linear_skinny_supports(4, 100, 64, False, False)     # [K,N] rows of 100 are not 16-byte chunks
+    assert not kernels.linear_skinny_supports(4, 64, 100, True, False)
+    assert not kernels.linear_skinny_supports(4, 64, 4096, False, True)     # too wide to normalise in registers
+    with pytest.raises(KernelError, match="not supported"):
+        kernels.linear_skinny(torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16),
+                              torch.zeros(100, 100, device=DEV, dtype=torch.bfloat16), None,
+                              torch.zeros(4, 100, device=DEV), m=4)
+
+
 # ---- attention ---------------------------------------------------------------------------------
 
 def make_paged(lengths, n_kv_heads, head_dim, dtype, table_len=None, extra_pages=3):
