@@ -35,8 +35,14 @@ int bt_attention_decode(const void* q, long long q_row_stride, const void* k_poo
                         float scale, int window, int n_splits, int dtype, cudaStream_t stream);
 
 int bt_sample(const float* logits, long long row_stride, int n_rows, int vocab, int do_sample, float temperature,
-              int top_k, float top_p, float min_p, const float* uniforms, int* out_ids, float* out_logp,
-              cudaStream_t stream);
+              int top_k, float top_p, float min_p, const float* uniforms, const unsigned long long* stream_seeds,
+              const int* counters, int* out_ids, float* out_logp, cudaStream_t stream);
+int bt_advance(const int* ids, int* tokens, int* positions, int* past_len, int* ctx_len, int* counters, int n,
+               cudaStream_t stream);
+int bt_linear_skinny_supports(int M, int N, int K, int w_is_nk, int fuse_ln);
+int bt_linear_skinny(const void* a, const float* x32, const int* rows, const float* gamma, const float* beta, float eps,
+                     const void* w, const float* bias, const float* residual, void* out, int M, int N, int K,
+                     int w_is_nk, int act, int out_is_f32, int split, cudaStream_t stream);
 int bt_logit_edits(float* logits, long long row_stride, const int* rows, const int* tokens, const float* vals,
                    int n_edits, int vocab, cudaStream_t stream);
 }

@@ -19,6 +19,15 @@ __device__ __forceinline__ unsigned ordered_key(float v) {
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
+// Draw `index` of the SplitMix64 stream `seed`, mapped to the midpoint of one of 2^23 intervals of (0, 1).
+__device__ __forceinline__ float stream_uniform(unsigned long long seed, unsigned long long index) {
+  unsigned long long v = seed + 0x9E3779B97F4A7C15ull * (index + 1ull);
+  v = (v ^ (v >> 30)) * 0xBF58476D1CE4E5B9ull;
+  v = (v ^ (v >> 27)) * 0x94D049BB133111EBull;
+  v ^= v >> 31;
+  return ((float)(v >> 41) + 0.5f) * (1.0f / 8388608.0f);
+}
+
 __device__ __forceinline__ float block_sum_f(float v, float* scratch) { return block_sum(v, scratch); }
 
 __device__ __forceinline__ int block_sum_i(int v, int* scratch) {
@@ -40,8 +49,9 @@ __device__ __forceinline__ int block_sum_i(int v, int* scratch) {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab, int do_sample, float temperature,
-              int top_k, float top_p, float min_p, const float* __restrict__ uniforms, int* __restrict__ out_ids,
-              float* __restrict__ out_logp) {
+              int top_k, float top_p, float min_p, const float* __restrict__ uniforms,
+              const unsigned long long* __restrict__ stream_seeds, const int* __restrict__ counters,
+              int* __restrict__ out_ids, float* __restrict__ out_logp) {
   __shared__ float fs[33];
   __shared__ int is[33];
   __shared__ float warp_tot[32];
@@ -160,7 +170,9 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   __syncthreads();
   const float total = fs[32];
   const float excl = warp_tot[tid >> 5] + (incl - mine);
-  const float threshold = uniforms[row] * total;
+  // the row's uniform: given, or draw `counters[row]` of the row's own SplitMix64 stream
+  const float u = stream_seeds ? stream_uniform(stream_seeds[row], (unsigned long long)counters[row]) : uniforms[row];
+  const float threshold = u * total;
   int below = 0;
   if (excl < threshold) {
     float run = excl;
@@ -197,16 +209,44 @@ __global__ void logit_edit_kernel(float* __restrict__ logits, long long row_stri
 
 }  // namespace bt
 
+// Uniforms come from `uniforms` (one per row) or, when `stream_seeds` is given, are drawn on the device:
+// row r uses draw counters[r] of the SplitMix64 stream stream_seeds[r].
 extern "C" int bt_sample(const float* logits, long long row_stride, int n_rows, int vocab, int do_sample,
-                         float temperature, int top_k, float top_p, float min_p, const float* uniforms, int* out_ids,
+                         float temperature, int top_k, float top_p, float min_p, const float* uniforms,
+                         const unsigned long long* stream_seeds, const int* counters, int* out_ids,
                          float* out_logp, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(vocab > 0 && n_rows >= 0, "sample: bad sizes rows=%d vocab=%d", n_rows, vocab);
-  BT_CHECK(!do_sample || (temperature > 0.f && uniforms != nullptr), "sample: sampling needs a positive temperature and uniforms");
+  BT_CHECK(!do_sample || (temperature > 0.f && (uniforms != nullptr || (stream_seeds != nullptr && counters != nullptr))),
+           "sample: sampling needs a positive temperature and uniforms (or stream seeds and counters)");
   if (n_rows == 0) return 0;
   sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, vocab, do_sample, temperature, top_k, top_p,
-                                                      min_p, uniforms, out_ids, out_logp);
+                                                      min_p, uniforms, stream_seeds, counters, out_ids, out_logp);
   BT_LAUNCH_OK("sample");
+  return 0;
+}
+
+namespace bt {
+// After a decode step whose tokens were selected on the device: the selected ids become the next step's
+// tokens, and every sequence moves on by one position.
+__global__ void advance_kernel(const int* __restrict__ ids, int* __restrict__ tokens, int* __restrict__ positions,
+                               int* __restrict__ past_len, int* __restrict__ ctx_len, int* __restrict__ counters, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  tokens[i] = ids[i];
+  positions[i] += 1;
+  past_len[i] += 1;
+  ctx_len[i] += 1;
+  counters[i] += 1;
+}
+}  // namespace bt
+
+extern "C" int bt_advance(const int* ids, int* tokens, int* positions, int* past_len, int* ctx_len, int* counters,
+                          int n, cudaStream_t stream) {
+  using namespace bt;
+  if (n <= 0) return 0;
+  advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, tokens, positions, past_len, ctx_len, counters, n);
+  BT_LAUNCH_OK("advance");
   return 0;
 }
 

@@ -46,6 +46,11 @@ class Engine:
         self.builder = StepBuilder(self.cache, self.dtype, self.device)
         self.ws = self.builder.ws
         self.steps_run = 0
+        # decode steps are replayed from CUDA graphs when every part is made of this library's kernels
+        self.use_graphs = plan.graph_safe
+        self.max_graph_batch = 256
+        self._graphs: dict = {}
+        self.h2d_bytes_last = 0
 
     # ---- construction ------------------------------------------------------------------
     @classmethod
@@ -97,6 +102,29 @@ class Engine:
                 if not (0 <= int(w) < len(e.tokens)):
                     raise ShapeError(f"slot {e.slot}: wanted place {w} is outside the {len(e.tokens)} tokens of the step")
 
+    def decode_graph(self, n: int, selection: dict | None = None):
+        """The recorded decode step for `n` sequences (with token selection when `selection` is given)."""
+        from .graphs import DecodeGraph
+        key = (n, None if selection is None else tuple(sorted(selection.items())))
+        if key not in self._graphs:
+            self._graphs[key] = DecodeGraph(self, n, selection)
+        return self._graphs[key]
+
+    def _graph_step(self, entries: list[StepEntry]):
+        graph = self.decode_graph(len(entries))
+        cache = self.cache
+        graph.meta.fill([e.tokens[0] for e in entries], [cache.length(e.slot) for e in entries],
+                        [e.slot for e in entries],
+                        [[cache.table_row(g, e.slot) for e in entries] for g in range(len(cache.groups))])
+        self.h2d_bytes_last = graph.meta.upload()
+        logits = graph.run()
+        wanted = [i for i, e in enumerate(entries) for _ in e.want]
+        if wanted == list(range(len(entries))):
+            return logits
+        if not wanted:
+            return None
+        return logits[torch.tensor(wanted, device=self.device)]
+
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Runs the entries' tokens as one batch and returns logits [wanted, vocab] (float32, on the device),
         in the order of the entries and of their `want` lists; None when nothing is wanted.
@@ -104,9 +132,13 @@ class Engine:
         The returned tensor lies in the step's scratch memory: read it before the next step."""
         self._validate(entries)
         self.cache.reserve([(e.slot, self.cache.length(e.slot) + len(e.tokens)) for e in entries])
-        self.ws.reset()
-        ctx = self.builder.build(entries)
-        logits = self.plan.forward(ctx)
+        if self.use_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
+            logits = self._graph_step(entries)
+        else:
+            self.ws.reset()
+            ctx = self.builder.build(entries)
+            self.h2d_bytes_last = self.builder.h2d_bytes_last
+            logits = self.plan.forward(ctx)
         for e in entries:
             self.cache.commit(e.slot, self.cache.length(e.slot) + len(e.tokens))
         self.steps_run += 1

@@ -1,0 +1,160 @@
+"""Decode steps as CUDA graphs.
+
+A step in which every sequence brings one token always launches the same kernels with the same
+arguments; only the integers they read (tokens, positions, lengths, page tables) change.  Those live
+in one device buffer with a fixed layout, so the launches are recorded once per batch size and
+replayed: one graph launch per step instead of some seventy kernel launches from Python.
+
+Two recordings exist per batch size: the forward pass alone (`Engine.step` uses it, the host sends the
+integers every step), and forward + token selection + advance (`DecodeSession` uses it: the selected
+ids become the next step's tokens on the device, so the host only launches and reads results, one
+step behind).
+"""
+from __future__ import annotations
+
+import gc
+import weakref
+
+import numpy as np
+import torch
+
+from .. import kernels
+from ..errors import GenerationError
+from .step import StepContext, Workspace
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class DecodeMeta:
+    """The integers of a decode step for `n` sequences, in pinned host memory and on the device."""
+    SECTIONS = ("tokens", "positions", "token_seq", "seq_start", "past_len", "ctx_len", "slots", "want_rows", "counters")
+
+    def __init__(self, n: int, table_width: int, n_groups: int, device):
+        self.n, self.table_width, self.n_groups = n, table_width, n_groups
+        sizes = {name: n for name in self.SECTIONS}
+        sizes["seq_start"] = n + 1
+        self.offsets, total = {}, 0
+        for name in self.SECTIONS:
+            self.offsets[name] = total
+            total += _align4(sizes[name])
+        self.table_offsets = []
+        for _ in range(n_groups):
+            self.table_offsets.append(total)
+            total += _align4(n * table_width)
+        self.total = total
+        self.sizes = sizes
+        self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=device)
+        ar = np.arange(n + 1, dtype=np.int32)
+        self._set("token_seq", ar[:n])
+        self._set("seq_start", ar)
+        self._set("want_rows", ar[:n])
+        # results of the selection kernel: ids, then the log-probabilities' bits
+        self.out = torch.zeros(2 * n, dtype=torch.int32, device=device)
+        self.seeds = torch.zeros(n, dtype=torch.int64, device=device)
+
+    def _set(self, name, values):
+        off = self.offsets[name]
+        self.host_np[off:off + len(values)] = values
+
+    def view(self, name) -> torch.Tensor:
+        off = self.offsets[name]
+        return self.dev[off:off + self.sizes[name]]
+
+    def table(self, g) -> torch.Tensor:
+        off = self.table_offsets[g]
+        return self.dev[off:off + self.n * self.table_width].view(self.n, self.table_width)
+
+    def fill(self, tokens, pasts, slots, tables, counters=None):
+        """tables: per group, a list of page lists (one per sequence)."""
+        pasts = np.asarray(pasts, dtype=np.int32)
+        self._set("tokens", np.asarray(tokens, dtype=np.int32))
+        self._set("positions", pasts)
+        self._set("past_len", pasts)
+        self._set("ctx_len", pasts + 1)
+        self._set("slots", np.asarray(slots, dtype=np.int32))
+        if counters is not None:
+            self._set("counters", np.asarray(counters, dtype=np.int32))
+        for g, rows in enumerate(tables):
+            off = self.table_offsets[g]
+            flat = np.zeros((self.n, self.table_width), dtype=np.int32)
+            for i, row in enumerate(rows):
+                flat[i, :len(row)] = row
+            self.host_np[off:off + self.n * self.table_width] = flat.reshape(-1)
+
+    def upload(self):
+        self.dev.copy_(self.host, non_blocking=True)
+        return self.total * 4
+
+
+class DecodeGraph:
+    """The recorded decode step of `n` sequences, with or without token selection."""
+
+    def __init__(self, engine, n: int, selection: dict | None = None):
+        # no strong reference back to the engine: a recording must die with its engine at once, by reference
+        # count, and never later inside the garbage collector while another recording is being made
+        self._engine = weakref.ref(engine)
+        self.n, self.selection = n, selection
+        cache = engine.cache
+        self.meta = DecodeMeta(n, cache.table_width, len(cache.groups), engine.device)
+        self.ws = Workspace(engine.device)
+        m = self.meta
+        self.ctx = StepContext(
+            dtype=engine.dtype, cache=cache, ws=self.ws, n_tokens=n, n_seqs=n, n_want=n, max_new=1, is_decode=True,
+            fresh=False, ctx_bound=engine.cache_config.max_context, tokens=m.view("tokens"),
+            positions=m.view("positions"), token_seq=m.view("token_seq"), seq_start=m.view("seq_start"),
+            past_len=m.view("past_len"), ctx_len=m.view("ctx_len"), slots=m.view("slots"),
+            want_rows=m.view("want_rows"), tables=[m.table(g) for g in range(len(cache.groups))])
+        self.graph = None
+        self.logits = None
+        self.launches = 0          # kernels inside one replay
+
+    def _issue(self):
+        """Launches the step's kernels on the current stream (eagerly, or into a recording)."""
+        self.ws.reset()
+        logits = self._engine().plan.forward(self.ctx)
+        if self.selection is not None:
+            m, s = self.meta, self.selection
+            kernels.sample(logits, self.n, do_sample=s["do_sample"], temperature=s["temperature"], top_k=s["top_k"],
+                           top_p=s["top_p"], min_p=s["min_p"], stream_seeds=m.seeds if s["do_sample"] else None,
+                           counters=m.view("counters") if s["do_sample"] else None, out_ids=m.out[:self.n],
+                           out_logp=m.out[self.n:].view(torch.float32))
+            kernels.advance(m.out[:self.n], m.view("tokens"), m.view("positions"), m.view("past_len"),
+                            m.view("ctx_len"), m.view("counters"), self.n)
+        return logits
+
+    def run(self) -> torch.Tensor:
+        """Runs the step on what the device copy of the integers holds.  The first call runs the kernels directly
+        and then records them; later calls replay the recording."""
+        if self.graph is not None:
+            self.graph.replay()
+            return self.logits
+        before = kernels.launch_count()
+        first = self._issue()
+        self.launches = kernels.launch_count() - before
+        # the recording must find every piece of scratch at a fixed address: size the workspace for a whole
+        # step before recording, and let it grow no more
+        need = self.ws.offset + (1 << 16)
+        if self.ws._retired or self.ws.buffer.numel() < need:
+            torch.cuda.current_stream().synchronize()
+            keep = first.clone()
+            self.ws.buffer = torch.empty(max(need, 2 * self.ws.buffer.numel()), dtype=torch.uint8, device=self.ws.device)
+            self.ws._retired.clear()
+            first = keep
+        self.ws.frozen = True
+        graph = torch.cuda.CUDAGraph()
+        # nothing may free device or pinned memory while the stream records: keep the collector out
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                self.logits = self._issue()
+        finally:
+            if was_enabled:
+                gc.enable()
+        self.graph = graph
+        return first

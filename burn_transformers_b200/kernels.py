@@ -252,18 +252,34 @@ def attention_decode(q_proj, out, k_pool, v_pool, table, table_len, ctx_len, n_s
 
 
 def sample(logits, n_rows, *, do_sample, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0, uniforms=None,
-           out_ids=None, out_logp=None):
-    """Selects one token per row of 32-bit logits; writes ids (int32) and log-probabilities (float32)."""
+           stream_seeds=None, counters=None, out_ids=None, out_logp=None):
+    """Selects one token per row of 32-bit logits; writes ids (int32) and log-probabilities (float32).
+
+    Sampling takes one uniform per row from `uniforms`, or draws it on the device as draw `counters[r]` of the
+    SplitMix64 stream `stream_seeds[r]` (int64 tensor holding the unsigned seeds' bits)."""
     _need(logits, "logits", torch.float32)
     vocab = logits.shape[1]
     _need(out_ids, "out_ids", torch.int32)
     _need(out_logp, "out_logp", torch.float32)
-    if do_sample:
+    if do_sample and stream_seeds is not None:
+        _need(stream_seeds, "stream_seeds", torch.int64)
+        _need(counters, "counters", torch.int32)
+    elif do_sample:
         _need(uniforms, "uniforms", torch.float32)
     _check(library().bt_sample(_ptr(logits), c_longlong(logits.stride(0)), c_int(n_rows), c_int(vocab),
                                c_int(1 if do_sample else 0), c_float(temperature), c_int(top_k or 0),
                                c_float(1.0 if top_p is None else top_p), c_float(0.0 if min_p is None else min_p),
-                               _ptr(uniforms), _ptr(out_ids), _ptr(out_logp), _stream()))
+                               _ptr(uniforms), _ptr(stream_seeds), _ptr(counters), _ptr(out_ids), _ptr(out_logp),
+                               _stream()))
+
+
+def advance(ids, tokens, positions, past_len, ctx_len, counters, n):
+    """tokens <- ids; positions, past_len, ctx_len and counters += 1 (all int32 device tensors of n entries)."""
+    for name, t in (("ids", ids), ("tokens", tokens), ("positions", positions), ("past_len", past_len),
+                    ("ctx_len", ctx_len), ("counters", counters)):
+        _need(t, name, torch.int32)
+    _check(library().bt_advance(_ptr(ids), _ptr(tokens), _ptr(positions), _ptr(past_len), _ptr(ctx_len), _ptr(counters),
+                                c_int(n), _stream()))
 
 
 def logit_edits(logits, rows, tokens, vals, n_edits):
