@@ -101,36 +101,40 @@ def prefill_flops(cfg, lengths):
 
 
 def decode_points(engine, cfg, batch, prompt_len, steps, warmup, torch, bt, rng):
-    """Runs `warmup` + `steps` decode steps of `batch` sequences after a prefill of `prompt_len` tokens each.
-    Returns (ms per step on the device, launches in the timed region, mean context of the timed steps)."""
-    from burn_transformers_b200 import kernels
+    """`warmup` + `steps` decode steps of `batch` sequences after a prefill of `prompt_len` tokens each: every
+    step is one replay of the recorded forward + greedy selection + advance, the selected tokens being fed
+    forward on the device.  Returns (ms per step on the device, kernels launched in the timed region, mean
+    context of the timed steps)."""
+    from burn_transformers_b200.engine.graphs import DecodeSession
     from burn_transformers_b200.sampling.sampler import DeviceSampler
     from burn_transformers_b200.sampling.tracker import SequenceTracker
 
-    config = bt.GenerationConfig(max_new_tokens=steps + warmup + 1)
+    config = bt.GenerationConfig(max_new_tokens=steps + warmup + 2)
     prompts = [rng.integers(0, cfg["vocab_size"], prompt_len).tolist() for _ in range(batch)]
     sampler = DeviceSampler(config, cfg["vocab_size"], engine.device, batch)
     trackers = [SequenceTracker(i, p, config) for i, p in enumerate(prompts)]
-    slots = [engine.new_sequence() for _ in prompts]
+    slots = {i: engine.new_sequence() for i in range(batch)}
     try:
-        logits = engine.step([bt.StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        logits = engine.step([bt.StepEntry(slots[i], p, [len(p) - 1]) for i, p in enumerate(prompts)])
+        ids, logps = sampler.select(logits, trackers)
+        for t, tok, lp in zip(trackers, ids, logps):
+            t.push(tok, lp)
+        engine.cache.reserve([(slots[i], prompt_len + steps + warmup + 1) for i in range(batch)])
+        session = DecodeSession(engine, config, batch)
+        graph = session._compose(trackers, slots)
+        for _ in range(warmup):
+            graph.run()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        launches = 0
-        for i in range(warmup + steps):
-            if i == warmup:
-                torch.cuda.synchronize()
-                launches = kernels.launch_count()
-                start.record()
-            ids, logps = sampler.select(logits, trackers)
-            for t, tok, lp in zip(trackers, ids, logps):
-                t.push(tok, lp)
-            logits = engine.step([bt.StepEntry(s, [tok], [0]) for s, tok in zip(slots, ids)])
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            graph.run()
         stop.record()
         torch.cuda.synchronize()
-        launches = kernels.launch_count() - launches
         ms = start.elapsed_time(stop) / steps
+        launches = graph.launches * steps
     finally:
-        for s in slots:
+        for s in slots.values():
             engine.release(s)
     mean_ctx = prompt_len + warmup + (steps + 1) / 2
     return ms, launches, mean_ctx
@@ -167,15 +171,20 @@ def run_ours(args):
     cfg = gpt2_small()
     pk = peaks()
     batch, steps, warmup = 8, args.steps, args.warmup
-    if steps + warmup > CONTEXT - 2:
+    if steps + warmup > CONTEXT - 4:
         print(json.dumps({"error": f"steps + warmup must stay below the context of {CONTEXT}"}))
         return 1
-    prompt_len = min(512, CONTEXT - steps - warmup - 1)
+    prompt_len = min(512, CONTEXT - steps - warmup - 2)
     rng = np.random.default_rng(0)
     with tempfile.TemporaryDirectory() as folder:
         bt.write_random_model(folder, cfg, seed=0, storage="bfloat16")
         engine = bt.Engine.from_folder(folder, "bfloat16", max_tokens=64 * CONTEXT, max_slots=64)
     before_all = kernels.launch_count()
+    if args.only == "decode":
+        ms, launches, mean_ctx = decode_points(engine, cfg, args.batch, prompt_len, steps, warmup, torch, bt, rng)
+        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": ms, "tokens_per_s": args.batch / ms * 1e3,
+                          "gpu_launches": launches, "mean_context": mean_ctx}))
+        return 0
     # prefill: 2 sequences x 1,024 tokens
     lengths = [PREFILL_TOKENS // 2] * 2
     prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in lengths]
@@ -192,6 +201,9 @@ def run_ours(args):
         for s in slots:
             engine.release(s)
     prefill_ms = statistics.median(times[1:])
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": prefill_ms}))
+        return 0
     prefill = {"value": PREFILL_TOKENS / prefill_ms * 1e3, "tokens": PREFILL_TOKENS, "ms": prefill_ms,
                "frac": prefill_flops(cfg, lengths) / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
     # decode at batch 1 and 64 (shorter runs), then the headline at batch 8 under the clock sampler
@@ -217,8 +229,12 @@ def run_ours(args):
                    "sampling": "greedy on device", "l2": "working set of a step exceeds L2 (weights 249 MB + cache)",
                    "peaks": pk["source"]},
         "clocks": clocks.summary(),
-        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": engine.builder.h2d_bytes_last,
-                "d2h_bytes_per_step": 8 * batch},
+        "e2e": {"value": e2e, "unit": "tokens/s",
+                "h2d_bytes_per_step": round(engine.last_session.h2d_bytes / max(1, engine.last_session.steps), 1),
+                "d2h_bytes_per_step": round(engine.last_session.d2h_bytes / max(1, engine.last_session.steps), 1),
+                "note": "generate_causal_streaming: prompts as host lists, every step's ids and log-probabilities "
+                        "read back to pinned host memory; tokens are fed forward on the device, so a step's own "
+                        "input copy is the integers of a recomposed batch only"},
         "gpu_launches": launches,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -236,6 +252,9 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+                        help="for profiling: run only the decode steps (at --batch) or only the prefill")
+    parser.add_argument("--batch", type=int, default=8, help="batch of the decode steps under --only decode")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate (Cargo.toml only): pip "

@@ -29,16 +29,20 @@ int bt_attention_prefill_simt(const void* q, long long q_row_stride, const void*
                               int causal, int window, int dtype, cudaStream_t stream);
 
 long long bt_attention_decode_scratch_floats(int n_seqs, int n_heads, int head_dim, int n_splits);
-int bt_attention_decode(const void* q, long long q_row_stride, const void* k_pool, const void* v_pool,
-                        const int* kv_table, int table_stride, int table_len, int page_size, void* out,
-                        float* scratch, const int* ctx_len, int n_seqs, int n_heads, int n_kv_heads, int head_dim,
-                        float scale, int window, int n_splits, int dtype, cudaStream_t stream);
+int bt_attention_decode(const void* q, long long q_row_stride, const void* new_k, const void* new_v, void* k_pool,
+                        void* v_pool, const int* kv_table, int table_stride, int table_len, int page_size, void* out,
+                        float* scratch, int* tickets, const int* ctx_len, int n_seqs, int n_heads, int n_kv_heads,
+                        int head_dim, float scale, int window, int n_splits, int dtype, cudaStream_t stream);
 
 int bt_sample(const float* logits, long long row_stride, int n_rows, int vocab, int do_sample, float temperature,
               int top_k, float top_p, float min_p, const float* uniforms, const unsigned long long* stream_seeds,
               const int* counters, int* out_ids, float* out_logp, cudaStream_t stream);
 int bt_advance(const int* ids, int* tokens, int* positions, int* past_len, int* ctx_len, int* counters, int n,
                cudaStream_t stream);
+int bt_linear_stream_supports(int M, int N, int K, int fuse_ln);
+int bt_linear_stream(const void* a, const float* x32, const int* rows, const float* gamma, const float* beta, float eps,
+                     const void* w, const float* bias, const float* residual, void* out, int M, int N, int K, int act,
+                     int out_is_f32, int warps_k, cudaStream_t stream);
 int bt_linear_skinny_supports(int M, int N, int K, int w_is_nk, int fuse_ln);
 int bt_linear_skinny(const void* a, const float* x32, const int* rows, const float* gamma, const float* beta, float eps,
                      const void* w, const float* bias, const float* residual, void* out, int M, int N, int K,

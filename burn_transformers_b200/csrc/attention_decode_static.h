@@ -20,9 +20,11 @@
 //    request is refused with an error (bt_last_error() says by how much) and nothing is launched.
 //  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
 //    current).  Make that first call before any stream capture begins on that device.
+//  * n_seqs * n_heads must not exceed 16384 (the built-in ticket counters the splits' merge uses).
 //  * All calls on a device share the one array, and the array keeps whatever the last call left in it.  The
-//    kernels write every partial result they later read, so nothing has to start at zero and nothing is
-//    cleared.  Two calls that overlap on the GPU (different streams, no ordering between them) race on the
+//    kernels write every partial result they later read, so the partial results need no clearing.  The ticket
+//    counters must be zero when a call starts: they are zero when the library is loaded, and the block that
+//    merges a (sequence, head) sets its counter back to zero, so a completed call leaves them zero.  Two calls that overlap on the GPU (different streams, no ordering between them) race on the
 //    array and give wrong results: order them, or use bt_attention_decode with separate scratch buffers.
 #pragma once
 #include <cuda_runtime.h>

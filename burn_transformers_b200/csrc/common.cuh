@@ -28,6 +28,46 @@ void count_launch();
     ::bt::count_launch();                                                                    \
   } while (0)
 
+// Programmatic dependent launch.  A kernel launched through launch_pdl may start while the kernel before it
+// in the stream is still running; it must call pdl_wait() before it reads or writes anything that kernel
+// touches (after the call the whole earlier grid has finished and its writes are visible).  What comes
+// before pdl_wait() may only read memory that no kernel of the step writes: weights.  pdl_trigger() lets
+// the next kernel of the stream begin its own prologue.  Both are no-ops in a kernel launched the plain way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              int cluster_x, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[n].val.programmaticStreamSerializationAllowed = 1;
+  ++n;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#define BT_PDL_OK(name, call)                                                                 \
+  do {                                                                                        \
+    cudaError_t e_ = (call);                                                                  \
+    if (e_ != cudaSuccess) return ::bt::fail("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
+    ::bt::count_launch();                                                                     \
+  } while (0)
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -8,6 +8,8 @@ template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
                              const T* __restrict__ wte, const T* __restrict__ wpe, float* __restrict__ out,
                              int width, int vocab, int n_positions, int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = tokens[t];
   const int pos = wpe ? positions[t] : 0;
@@ -36,14 +38,13 @@ extern "C" int bt_embed(const int* tokens, const int* positions, const void* wte
   if (n_tokens == 0) return 0;
   const int threads = width >= 256 ? 256 : 128;
   if (dtype == kF32)
-    embed_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, positions, (const float*)wte, (const float*)wpe, out,
-                                                          width, vocab, n_positions, status);
+    BT_PDL_OK("embed", launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, 1, tokens, positions,
+                                  (const float*)wte, (const float*)wpe, out, width, vocab, n_positions, status));
   else if (dtype == kBF16)
-    embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(tokens, positions, (const __nv_bfloat16*)wte,
-                                                                  (const __nv_bfloat16*)wpe, out, width, vocab,
-                                                                  n_positions, status);
+    BT_PDL_OK("embed", launch_pdl(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, 1, tokens,
+                                  positions, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, width, vocab,
+                                  n_positions, status));
   else
     return fail("embed: unknown dtype %d", dtype);
-  BT_LAUNCH_OK("embed");
   return 0;
 }

@@ -11,6 +11,8 @@ layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, cons
                  const float* __restrict__ beta, TOut* __restrict__ out, int width, float eps) {
   __shared__ float scratch[33];
   extern __shared__ float row_cache[];  // width floats
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* src = x + (long long)(rows ? rows[r] : r) * width;
   float s = 0.f;
@@ -46,11 +48,12 @@ extern "C" int bt_layernorm(const float* x, const int* rows, const float* gamma,
   constexpr int T = 256;
   const size_t smem = (size_t)width * sizeof(float);
   if (out_dtype == kF32)
-    layernorm_kernel<float, T><<<n_rows, T, smem, stream>>>(x, rows, gamma, beta, (float*)out, width, eps);
+    BT_PDL_OK("layernorm", launch_pdl(layernorm_kernel<float, T>, dim3(n_rows), dim3(T), smem, stream, 1, x, rows, gamma,
+                                      beta, (float*)out, width, eps));
   else if (out_dtype == kBF16)
-    layernorm_kernel<__nv_bfloat16, T><<<n_rows, T, smem, stream>>>(x, rows, gamma, beta, (__nv_bfloat16*)out, width, eps);
+    BT_PDL_OK("layernorm", launch_pdl(layernorm_kernel<__nv_bfloat16, T>, dim3(n_rows), dim3(T), smem, stream, 1, x, rows,
+                                      gamma, beta, (__nv_bfloat16*)out, width, eps));
   else
     return fail("layernorm: unknown dtype %d", out_dtype);
-  BT_LAUNCH_OK("layernorm");
   return 0;
 }

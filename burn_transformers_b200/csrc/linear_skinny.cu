@@ -6,8 +6,10 @@
 //   * the blocks that share a column tile form a thread-block cluster along K; their partial sums are added
 //     through distributed shared memory in a fixed order (rank 0, 1, ...), so the result is deterministic and
 //     needs neither atomics nor scratch memory;
-//   * optionally the rows are LayerNorm-ed on the way in (32-bit statistics over the full row, two passes),
-//     which saves a kernel and a round trip of the normalised rows;
+//   * optionally the rows (at most 16) are LayerNorm-ed on the way in (32-bit statistics over the full row,
+//     two passes), which saves a kernel and a round trip of the normalised rows;
+//   * the weight panel is requested before the kernel waits for its predecessor (programmatic dependent
+//     launch), so weights stream while the previous kernel is still finishing;
 //   * the epilogue adds the bias, applies GELU, adds the 32-bit residual and writes 32-bit or bfloat16.
 // The products themselves use mma.sync m16n8k16: with at most 64 rows the tensor pipe is idle either way.
 #include <cooperative_groups.h>
@@ -21,7 +23,6 @@ namespace bt {
 
 constexpr int SK_THREADS = 128;
 constexpr int SK_BN = 32;          // output columns per block: 4 warps x 8
-constexpr int SK_MAX_LN_PER_LANE = 64;   // fused LayerNorm keeps a row in registers: K <= 32 * 64
 
 struct SkinnyParams {
   const __nv_bfloat16* a;      // [M, K] bfloat16 rows, or null when the rows come from `x32` through LayerNorm
@@ -102,44 +103,61 @@ linear_skinny_kernel(SkinnyParams p) {
     }
   }
   asm volatile("cp.async.commit_group;\n" ::);
+  pdl_trigger();   // the next kernel may start fetching its own weights
+  pdl_wait();      // from here on the rows (and the residual) of the previous kernel are read
 
   // ---- rows ----------------------------------------------------------------------------------------
   if (FUSE_LN) {
-    // one warp per row; the row lives in registers between the passes
-    for (int r = warp; r < 16 * MT; r += SK_THREADS / 32) {
-      __nv_bfloat16* dst = As + r * a_stride;
-      if (r >= p.M) {
-        for (int c = lane; c < ks; c += 32) dst[c] = __float2bfloat16_rn(0.f);
-        continue;
-      }
-      const float* src = p.x32 + (long long)(p.rows ? p.rows[r] : r) * p.K;
-      float v[SK_MAX_LN_PER_LANE];
-      float s = 0.f;
-#pragma unroll
-      for (int i = 0; i < SK_MAX_LN_PER_LANE; ++i) {
-        const int c = lane + 32 * i;
-        v[i] = c < p.K ? src[c] : 0.f;
-        s += v[i];
-      }
-      const float mean = warp_sum(s) / (float)p.K;
-      float q = 0.f;
-#pragma unroll
-      for (int i = 0; i < SK_MAX_LN_PER_LANE; ++i) {
-        const int c = lane + 32 * i;
-        const float d = c < p.K ? v[i] - mean : 0.f;
-        q += d * d;
-      }
-      const float rstd = 1.f / sqrtf(warp_sum(q) / (float)p.K + p.eps);
-#pragma unroll
-      for (int i = 0; i < SK_MAX_LN_PER_LANE; ++i) {
-        const int c = lane + 32 * i;           // column of the full row
-        const int cs = c - k0;                 // column inside this block's slice
-        if (c < p.K && cs >= 0 && cs < ks) {
-          const float y = (v[i] - mean) * rstd * p.gamma[c] + (p.beta ? p.beta[c] : 0.f);
-          dst[cs] = __float2bfloat16_rn(y);
+    __shared__ float stats[16][2];
+    for (int r = warp; r < 16; r += SK_THREADS / 32) {
+      float mean = 0.f, rstd = 0.f;
+      if (r < p.M) {
+        const float* src = p.x32 + (long long)(p.rows ? p.rows[r] : r) * p.K;
+        float s = 0.f;
+        for (int c = lane * 4; c < p.K; c += 128) {
+          const float4 v = *reinterpret_cast<const float4*>(src + c);
+          s += (v.x + v.y) + (v.z + v.w);
         }
+        mean = warp_sum(s) / (float)p.K;
+        float d2 = 0.f;
+        for (int c = lane * 4; c < p.K; c += 128) {
+          const float4 v = *reinterpret_cast<const float4*>(src + c);
+          const float a = v.x - mean, b = v.y - mean, cc = v.z - mean, d = v.w - mean;
+          d2 += (a * a + b * b) + (cc * cc + d * d);
+        }
+        rstd = 1.f / sqrtf(warp_sum(d2) / (float)p.K + p.eps);
       }
-      for (int cs = k_len + lane; cs < ks; cs += 32) dst[cs] = __float2bfloat16_rn(0.f);
+      if (lane == 0) {
+        stats[r][0] = mean;
+        stats[r][1] = rstd;
+      }
+    }
+    __syncthreads();
+    const int chunks_per_row = ks / 8;
+    for (int i = tid; i < 16 * chunks_per_row; i += SK_THREADS) {
+      const int r = i / chunks_per_row, c = (i - r * chunks_per_row) * 8;
+      uint4 packed = make_uint4(0, 0, 0, 0);
+      if (r < p.M && c < k_len) {
+        const float* x = p.x32 + (long long)(p.rows ? p.rows[r] : r) * p.K + k0 + c;
+        const float* gm = p.gamma + k0 + c;
+        const float mean = stats[r][0], rstd = stats[r][1];
+        const float4 x0 = *reinterpret_cast<const float4*>(x), x1 = *reinterpret_cast<const float4*>(x + 4);
+        const float4 g0 = *reinterpret_cast<const float4*>(gm), g1 = *reinterpret_cast<const float4*>(gm + 4);
+        float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+        if (p.beta) {
+          b0 = *reinterpret_cast<const float4*>(p.beta + k0 + c);
+          b1 = *reinterpret_cast<const float4*>(p.beta + k0 + c + 4);
+        }
+        auto pack = [](float lo, float hi) {
+          __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+          return *reinterpret_cast<unsigned*>(&v);
+        };
+        packed.x = pack((x0.x - mean) * rstd * g0.x + b0.x, (x0.y - mean) * rstd * g0.y + b0.y);
+        packed.y = pack((x0.z - mean) * rstd * g0.z + b0.z, (x0.w - mean) * rstd * g0.w + b0.w);
+        packed.z = pack((x1.x - mean) * rstd * g1.x + b1.x, (x1.y - mean) * rstd * g1.y + b1.y);
+        packed.w = pack((x1.z - mean) * rstd * g1.z + b1.z, (x1.w - mean) * rstd * g1.w + b1.w);
+      }
+      *reinterpret_cast<uint4*>(As + r * a_stride + c) = packed;
     }
   } else {
     const int chunks_per_row = ks / 8;
@@ -214,8 +232,12 @@ linear_skinny_kernel(SkinnyParams p) {
   const int total = 16 * MT * SK_BN;
   const int per = (total + split - 1) / split;
   for (int e = rank * per + tid; e < min(total, (rank + 1) * per); e += SK_THREADS) {
+    float from[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) from[j] = j < split ? cluster.map_shared_rank(part, j)[e] : 0.f;   // all in flight
     float v = 0.f;
-    for (int j = 0; j < split; ++j) v += cluster.map_shared_rank(part, j)[e];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v += from[j];
     finish(e / SK_BN, e % SK_BN, v);
   }
   cluster.sync();    // nobody leaves while a peer may still read its partial tile
@@ -231,19 +253,7 @@ static int launch_skinny(const SkinnyParams& p, int split, cudaStream_t stream) 
   BT_CHECK(smem <= 200 * 1024, "linear_skinny: a K slice of %d needs %zu bytes of shared memory", ks, smem);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   BT_CHECK(e == cudaSuccess, "linear_skinny: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(split, (p.N + SK_BN - 1) / SK_BN, 1);
-  cfg.blockDim = dim3(SK_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = split;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kern, p);
+  e = launch_pdl(kern, dim3(split, (p.N + SK_BN - 1) / SK_BN, 1), dim3(SK_THREADS, 1, 1), smem, stream, split, p);
   BT_CHECK(e == cudaSuccess, "linear_skinny: launch failed: %s", cudaGetErrorString(e));
   count_launch();
   return 0;
@@ -254,9 +264,9 @@ static int launch_skinny_mt(const SkinnyParams& p, int split, cudaStream_t strea
   const int mt = (p.M + 15) / 16;
   switch (mt) {
     case 1: return launch_skinny<1, NK, LN>(p, split, stream);
-    case 2: return launch_skinny<2, NK, LN>(p, split, stream);
-    case 3: return launch_skinny<3, NK, LN>(p, split, stream);
-    case 4: return launch_skinny<4, NK, LN>(p, split, stream);
+    case 2: if (!LN) return launch_skinny<2, NK, false>(p, split, stream); break;
+    case 3: if (!LN) return launch_skinny<3, NK, false>(p, split, stream); break;
+    case 4: if (!LN) return launch_skinny<4, NK, false>(p, split, stream); break;
   }
   return fail("linear_skinny: %d rows exceed 64", p.M);
 }
@@ -268,7 +278,7 @@ extern "C" int bt_linear_skinny_supports(int M, int N, int K, int w_is_nk, int f
   if (M < 1 || M > 64 || N < 1 || K < 16) return 0;
   if (K % 8 != 0) return 0;                       // 16-byte chunks of rows (and of [N,K] weight rows)
   if (!w_is_nk && N % 8 != 0) return 0;           // 16-byte chunks of [K,N] weight rows
-  if (fuse_ln && K > 32 * bt::SK_MAX_LN_PER_LANE) return 0;
+  if (fuse_ln && M > 16) return 0;                // the fused LayerNorm handles one 16-row tile
   return 1;
 }
 

@@ -57,6 +57,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   __shared__ float warp_tot[32];
   __shared__ float s_max;
   __shared__ int s_arg;
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x, tid = threadIdx.x;
   const float* z = logits + (long long)row * row_stride;
   const float inv_t = do_sample ? 1.f / temperature : 1.f;
@@ -220,9 +222,9 @@ extern "C" int bt_sample(const float* logits, long long row_stride, int n_rows, 
   BT_CHECK(!do_sample || (temperature > 0.f && (uniforms != nullptr || (stream_seeds != nullptr && counters != nullptr))),
            "sample: sampling needs a positive temperature and uniforms (or stream seeds and counters)");
   if (n_rows == 0) return 0;
-  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, vocab, do_sample, temperature, top_k, top_p,
-                                                      min_p, uniforms, stream_seeds, counters, out_ids, out_logp);
-  BT_LAUNCH_OK("sample");
+  BT_PDL_OK("sample", launch_pdl(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, 1, logits, row_stride, vocab,
+                                 do_sample, temperature, top_k, top_p, min_p, uniforms, stream_seeds, counters, out_ids,
+                                 out_logp));
   return 0;
 }
 
@@ -231,6 +233,8 @@ namespace bt {
 // tokens, and every sequence moves on by one position.
 __global__ void advance_kernel(const int* __restrict__ ids, int* __restrict__ tokens, int* __restrict__ positions,
                                int* __restrict__ past_len, int* __restrict__ ctx_len, int* __restrict__ counters, int n) {
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   tokens[i] = ids[i];
@@ -245,8 +249,8 @@ extern "C" int bt_advance(const int* ids, int* tokens, int* positions, int* past
                           int n, cudaStream_t stream) {
   using namespace bt;
   if (n <= 0) return 0;
-  advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, tokens, positions, past_len, ctx_len, counters, n);
-  BT_LAUNCH_OK("advance");
+  BT_PDL_OK("advance", launch_pdl(advance_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, 1, ids, tokens, positions,
+                                  past_len, ctx_len, counters, n));
   return 0;
 }
 

@@ -70,8 +70,21 @@ def plan_batches(prompt_lengths: list[int], max_new_tokens: int, *, max_tokens: 
     return batches
 
 
-def run_batch(engine, sampler, trackers: list[SequenceTracker], on_token: Callable | None = None) -> None:
-    """Serves one batch to its end.  `engine` needs new_sequence/step/release; `sampler` needs select."""
+def _emit(t: SequenceTracker, token: int, logp: float, on_token):
+    if not math.isfinite(logp):
+        raise GenerationError(f"sequence {t.request}: the selected token {token} has a non-finite "
+                              f"log-probability {logp}; generation stops before emitting it")
+    reason = t.push(int(token), float(logp))
+    if on_token is not None:
+        on_token(GenerationToken(t.request, t.emitted - 1, int(token), float(logp), reason))
+    return reason
+
+
+def run_batch(engine, sampler, trackers: list[SequenceTracker], on_token: Callable | None = None,
+              session=None) -> None:
+    """Serves one batch to its end.  `engine` needs new_sequence/step/release; `sampler` needs select.
+    With a `session` (engine.graphs.DecodeSession) the one-token steps run from a recorded CUDA graph with
+    the selected tokens fed forward on the device."""
     slots = {}
     try:
         for t in trackers:
@@ -83,18 +96,11 @@ def run_batch(engine, sampler, trackers: list[SequenceTracker], on_token: Callab
         batch_rows = len(trackers)
         while active:
             ids, logps = sampler.select(logits, active, batch_rows)
-            going = []
-            for t, token, logp in zip(active, ids, logps):
-                if not math.isfinite(logp):
-                    raise GenerationError(f"sequence {t.request}: the selected token {token} has a non-finite "
-                                          f"log-probability {logp}; generation stops before emitting it")
-                reason = t.push(int(token), float(logp))
-                if on_token is not None:
-                    on_token(GenerationToken(t.request, t.emitted - 1, int(token), float(logp), reason))
-                if reason is None:
-                    going.append(t)
-            active = going
+            active = [t for t, token, logp in zip(active, ids, logps) if _emit(t, token, logp, on_token) is None]
             if not active:
+                break
+            if session is not None:
+                session.run(active, slots, lambda t, token, logp: _emit(t, token, logp, on_token))
                 break
             logits = engine.step([StepEntry(slots[t.request], [t.output.token_ids[-1]], [0]) for t in active])
     finally:
@@ -116,6 +122,13 @@ def generate(engine, prompts: list[list[int]], config: GenerationConfig, *, max_
         from ..sampling.sampler import DeviceSampler
         sampler = DeviceSampler(config, vocab, engine.device, max(len(b) for b in batches))
     trackers = [SequenceTracker(i, p, config) for i, p in enumerate(prompts)]
+    session = None
+    if getattr(engine, "use_graphs", False):
+        from .graphs import DecodeSession
+        if DecodeSession.usable(engine, config):
+            session = DecodeSession(engine, config, max(len(b) for b in batches))
     for batch in batches:
-        run_batch(engine, sampler, [trackers[i] for i in batch], on_token)
+        run_batch(engine, sampler, [trackers[i] for i in batch], on_token, session)
+    if session is not None:
+        engine.last_session = session
     return [t.output for t in trackers]

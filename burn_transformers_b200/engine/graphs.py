@@ -158,3 +158,85 @@ class DecodeGraph:
                 gc.enable()
         self.graph = graph
         return first
+
+
+class DecodeSession:
+    """Decodes a fixed set of sequences with the tokens fed forward on the device.
+
+    Each step is one replay of the recorded forward + selection + advance; the host launches step k+1
+    before it reads step k's ids, so the device never waits for the host.  A sequence that reaches its
+    length limit is known beforehand and leaves before the next launch; one that stops on an
+    end-of-sequence token or a stop sequence is found one step late, and that one step's result for it is
+    thrown away (its cache row lies in pages the sequence still owns, and its slot is released with it).
+    """
+
+    def __init__(self, engine, config, sampler_rows: int):
+        self.engine, self.config = engine, config
+        self.selection = dict(do_sample=config.samples, temperature=float(config.temperature),
+                              top_k=int(config.top_k) if (config.samples and config.top_k and config.top_k < engine.plan.vocab) else 0,
+                              top_p=float(config.top_p) if (config.samples and config.top_p is not None) else 1.0,
+                              min_p=float(config.min_p) if (config.samples and config.min_p is not None) else 0.0)
+        self.host_out = [torch.zeros(2 * sampler_rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.events = [torch.cuda.Event() for _ in range(2)]
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.steps = 0
+
+    @staticmethod
+    def usable(engine, config) -> bool:
+        return engine.use_graphs and not config.edits_logits and config.counter_mode == "per_sequence"
+
+    def _compose(self, trackers, slots):
+        """Uploads the state of the sequences that go on: their last token, length, pages, stream and counter."""
+        from ..sampling.random import sequence_stream
+        engine, cache = self.engine, self.engine.cache
+        graph = engine.decode_graph(len(trackers), self.selection)
+        meta = graph.meta
+        meta.fill([t.output.token_ids[-1] for t in trackers], [cache.length(slots[t.request]) for t in trackers],
+                  [slots[t.request] for t in trackers],
+                  [[cache.table_row(g, slots[t.request]) for t in trackers] for g in range(len(cache.groups))],
+                  counters=[t.emitted for t in trackers])
+        self.h2d_bytes += meta.upload()
+        if self.config.samples:
+            seeds = np.array([sequence_stream(self.config.seed, t.request) for t in trackers], dtype=np.uint64)
+            meta.seeds.copy_(torch.from_numpy(seeds.view(np.int64)), non_blocking=False)
+            self.h2d_bytes += 8 * len(trackers)
+        return graph
+
+    def run(self, trackers, slots, emit):
+        """`trackers`: unfinished sequences, each having emitted at least one token.  `emit(tracker, id, logp)`
+        records a token and returns the finish reason or None."""
+        engine, cache, cfg = self.engine, self.engine.cache, self.config
+        active = list(trackers)
+        # all pages a sequence can still need: prompt + max_new_tokens - 1 positions
+        cache.reserve([(slots[t.request], len(t.prompt) + cfg.max_new_tokens - 1) for t in active])
+        while active:
+            n = len(active)
+            graph = self._compose(active, slots)
+            # steps this composition can run before a sequence reaches its length limit
+            budget = min(cfg.max_new_tokens - t.emitted for t in active)
+            launched, processed = 0, 0
+            stop = False
+            while processed < launched or (launched < budget and not stop):
+                if launched < budget and not stop and launched - processed < 2:
+                    graph.run()
+                    buf = launched % 2
+                    self.host_out[buf][:2 * n].copy_(graph.meta.out, non_blocking=True)
+                    self.events[buf].record()
+                    launched += 1
+                    self.steps += 1
+                    self.d2h_bytes += 8 * n
+                    if launched - processed < 2 and launched < budget:
+                        continue            # keep one step in flight ahead of the host
+                buf = processed % 2
+                self.events[buf].synchronize()
+                ids = self.host_out[buf][:n].tolist()
+                logps = self.host_out[buf][n:2 * n].view(torch.float32).tolist()
+                processed += 1
+                for t, token, logp in zip(active, ids, logps):
+                    if t.finished:
+                        continue            # the step after its last one: thrown away
+                    cache.commit(slots[t.request], cache.length(slots[t.request]) + 1)
+                    if emit(t, token, logp) is not None:
+                        stop = True         # the composition changes: drain what is in flight, then recompose
+            active = [t for t in active if not t.finished]

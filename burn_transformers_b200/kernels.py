@@ -186,6 +186,48 @@ def linear_skinny(a, w, bias, out, *, m, w_is_nk=False, activation=None, residua
                                       c_int(1 if out.dtype == torch.float32 else 0), c_int(split), _stream()))
 
 
+def linear_stream_supports(m, n, k, fuse_ln) -> bool:
+    return bool(library().bt_linear_stream_supports(c_int(m), c_int(n), c_int(k), c_int(1 if fuse_ln else 0)))
+
+
+def linear_stream(a, w, bias, out, *, m, activation=None, residual=None, norm=None, warps_k=0):
+    """out[:m] = act(rows @ w^T + bias) (+ residual) for at most 64 bfloat16 rows; w is [N, K].
+
+    rows are `a` (bfloat16 [M, K]) or, when `norm` = (x32, gamma, beta, eps, row_index) is given and `a` is None,
+    LayerNorm(x32[row_index]) formed inside the kernel (at most 16 rows)."""
+    n, k = w.shape
+    _need(w, "w", torch.bfloat16, (n, k))
+    _need(out, "out", (torch.float32, torch.bfloat16), (None, n))
+    if out.shape[0] < m:
+        raise ShapeError(f"linear_stream: {m} rows asked of out[{out.shape[0]}]")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (n,))
+    if residual is not None:
+        _need(residual, "residual", torch.float32, (None, n))
+    if activation not in ACTIVATIONS:
+        raise ShapeError(f"linear_stream: unknown activation {activation!r}")
+    x32 = gamma = beta = rows = None
+    eps = 0.0
+    if norm is not None:
+        x32, gamma, beta, eps, rows = norm
+        _need(x32, "x32", torch.float32, (None, k))
+        _need(gamma, "gamma", torch.float32, (k,))
+        if beta is not None:
+            _need(beta, "beta", torch.float32, (k,))
+        if rows is not None:
+            _need(rows, "rows", torch.int32)
+        elif x32.shape[0] < m:
+            raise ShapeError(f"linear_stream: {m} rows asked of x32[{x32.shape[0]}]")
+    else:
+        _need(a, "a", torch.bfloat16, (None, k))
+        if a.shape[0] < m:
+            raise ShapeError(f"linear_stream: {m} rows asked of a[{a.shape[0]}]")
+    _check(library().bt_linear_stream(_ptr(a if norm is None else None), _ptr(x32), _ptr(rows), _ptr(gamma), _ptr(beta),
+                                      c_float(eps), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), c_int(m), c_int(n),
+                                      c_int(k), c_int(ACTIVATIONS[activation]),
+                                      c_int(1 if out.dtype == torch.float32 else 0), c_int(warps_k), _stream()))
+
+
 def kv_append(proj, k_offset, v_offset, positions, token_seq, ctx_len, table, table_len, k_pool, v_pool,
               n_tokens, n_kv_heads, head_dim):
     """Copies the new tokens' key and value channels of `proj` rows into the layer's pages."""
@@ -232,23 +274,45 @@ def attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits) -> int:
     return int(library().bt_attention_decode_scratch_floats(c_int(n_seqs), c_int(n_heads), c_int(head_dim), c_int(n_splits)))
 
 
+_TICKETS: dict = {}
+
+
+def _tickets(device, count: int) -> torch.Tensor:
+    """Zeroed counters for the decode attention's merge; the kernel leaves them zero, so they are made once."""
+    t = _TICKETS.get(device)
+    if t is None or t.numel() < count:
+        t = torch.zeros(max(count, 1 << 14), dtype=torch.int32, device=device)
+        _TICKETS[device] = t
+    return t
+
+
 def attention_decode(q_proj, out, k_pool, v_pool, table, table_len, ctx_len, n_seqs, n_heads, n_kv_heads, head_dim,
-                     scale, *, window=0, n_splits=1, scratch=None):
-    """Attention of one new token per sequence over that sequence's pages."""
+                     scale, *, window=0, n_splits=1, scratch=None, new_kv_offsets=None):
+    """Attention of one new token per sequence over that sequence's pages.
+
+    `new_kv_offsets` = (k_offset, v_offset): the new token's key and value are channels of the same `q_proj` rows;
+    the kernel reads them from there and files them in the pages itself.  None: the pages already hold them."""
     _need(q_proj, "q_proj", (torch.float32, torch.bfloat16))
     _need(out, "out", q_proj.dtype, (None, n_heads * head_dim))
     _need(k_pool, "k_pool", q_proj.dtype)
     _need(v_pool, "v_pool", q_proj.dtype)
     _need(table, "table", torch.int32)
+    tickets = None
     if n_splits > 1:
         need = attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise ShapeError(f"attention_decode: {n_splits} splits need {need} floats of scratch")
+        tickets = _tickets(q_proj.device, n_seqs * n_heads)
+    es = q_proj.element_size()
+    new_k = new_v = c_void_p(0)
+    if new_kv_offsets is not None:
+        new_k = c_void_p(q_proj.data_ptr() + new_kv_offsets[0] * es)
+        new_v = c_void_p(q_proj.data_ptr() + new_kv_offsets[1] * es)
     _check(library().bt_attention_decode(
-        _ptr(q_proj), c_longlong(q_proj.shape[1]), _ptr(k_pool), _ptr(v_pool), _ptr(table), c_int(table.shape[1]),
-        c_int(table_len), c_int(PAGE_SIZE), _ptr(out), _ptr(scratch), _ptr(ctx_len), c_int(n_seqs), c_int(n_heads),
-        c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(n_splits), c_int(_code(q_proj.dtype)),
-        _stream()))
+        _ptr(q_proj), c_longlong(q_proj.shape[1]), new_k, new_v, _ptr(k_pool), _ptr(v_pool), _ptr(table),
+        c_int(table.shape[1]), c_int(table_len), c_int(PAGE_SIZE), _ptr(out), _ptr(scratch), _ptr(tickets), _ptr(ctx_len),
+        c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window),
+        c_int(n_splits), c_int(_code(q_proj.dtype)), _stream()))
 
 
 def sample(logits, n_rows, *, do_sample, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0, uniforms=None,

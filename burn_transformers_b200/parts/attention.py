@@ -67,7 +67,7 @@ class CausalSelfAttention(Mixer):
         k_pool, v_pool, group, g = ctx.cache.layer_pools(entry)
         table = ctx.tables[g]
         window = self.window or 0
-        if owns_cache:
+        if owns_cache and not ctx.is_decode:
             kernels.kv_append(proj, self.q_width, self.q_width + self.kv_width, ctx.positions, ctx.token_seq,
                               ctx.ctx_len, table, group.table_len, k_pool, v_pool, n, self.n_kv_heads, self.head_dim)
         mixed = ctx.ws.take((n, self.q_width), dtype)
@@ -79,7 +79,8 @@ class CausalSelfAttention(Mixer):
                 scratch = ctx.ws.take((need,), torch.float32)
             kernels.attention_decode(proj, mixed, k_pool, v_pool, table, group.table_len, ctx.ctx_len, ctx.n_seqs,
                                      self.n_heads, self.n_kv_heads, self.head_dim, self.scale, window=window,
-                                     n_splits=splits, scratch=scratch)
+                                     n_splits=splits, scratch=scratch,
+                                     new_kv_offsets=(self.q_width, self.q_width + self.kv_width) if owns_cache else None)
         elif ctx.fresh and owns_cache:
             # every sequence starts at position 0: keys and values are the step's own projections
             kernels.attention_prefill_simt(proj, mixed, ctx.seq_start, ctx.past_len, ctx.n_seqs, ctx.max_new,

@@ -30,6 +30,14 @@ def linear(ctx, a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=
         n = w.shape[0] if w_is_nk else w.shape[1]
         k = w.shape[1] if w_is_nk else w.shape[0]
         fuse = lazy and m <= 16 and a.norm.fusable
+        if w_is_nk and n >= 8192 and kernels.linear_stream_supports(m, n, k, fuse):
+            # a wide [N, K] table (the readout): long weight rows, streamed straight into registers
+            if lazy and not fuse:
+                a, lazy = a.materialize(ctx), False
+            norm = (a.x32, a.norm.t_weight, a.norm.t_bias if a.norm.has_bias else None, a.norm.eps, a.rows) if lazy else None
+            kernels.linear_stream(None if lazy else a, w, bias, out, m=m, activation=activation, residual=residual,
+                                  norm=norm)
+            return
         if kernels.linear_skinny_supports(m, n, k, w_is_nk, fuse):
             if lazy and not fuse:
                 a, lazy = a.materialize(ctx), False

@@ -133,11 +133,47 @@ def test_linear_skinny(m, n, k, nk, split):
         assert rel(out, normed @ w.double() + bias.double()) < 2e-3   # a row value at a rounding tie may flip
 
 
+@pytest.mark.parametrize("m", [1, 8, 9, 16, 17, 64])
+@pytest.mark.parametrize("n, k, warps_k", [(768, 768, 0), (2304, 768, 4), (768, 3072, 2), (104, 240, 1), (203, 96, 4),
+                                           (777, 200, 0), (50257, 64, 0)])
+def test_linear_stream(m, n, k, warps_k):
+    a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    bias, res = torch.randn(n, device=DEV), torch.randn(m, n, device=DEV)
+    assert kernels.linear_stream_supports(m, n, k, False)
+    product = a.double() @ w.double().T
+    out = res.clone()
+    kernels.linear_stream(a, w, bias, out, m=m, activation="gelu_new", residual=out, warps_k=warps_k)
+    want = torch.nn.functional.gelu(product + bias.double(), approximate="tanh") + res.double()
+    assert rel(out, want) < 2e-6
+    low = torch.full((m + 2, n), 3.0, device=DEV, dtype=torch.bfloat16)
+    kernels.linear_stream(a, w, None, low, m=m, activation="gelu", warps_k=warps_k)
+    assert rel(low[:m], torch.nn.functional.gelu(product)) < 4e-3 and float((low[m:].float() - 3.0).abs().max()) == 0.0
+    if m > 1:     # the same row gives the same bits whatever else is in the call
+        alone, both = torch.empty(1, n, device=DEV), torch.empty(m, n, device=DEV)
+        kernels.linear_stream(a[m - 1:].contiguous(), w, bias, alone, m=1, warps_k=warps_k)
+        kernels.linear_stream(a, w, bias, both, m=m, warps_k=warps_k)
+        assert torch.equal(alone[0], both[m - 1])
+    if m <= 16:   # LayerNorm of 32-bit rows on the way in, rows picked by an index
+        x = torch.randn(m + 3, k, device=DEV) * 2 + 3
+        g, b = torch.randn(k, device=DEV), torch.randn(k, device=DEV)
+        rows = torch.randperm(m + 3, device=DEV)[:m].to(torch.int32)
+        normed = torch.nn.functional.layer_norm(x.double()[rows.long()], (k,), g.double(), b.double(), 1e-5)
+        normed = normed.float().to(torch.bfloat16).double()          # the kernel rounds the rows once too
+        out = torch.empty(m, n, device=DEV)
+        kernels.linear_stream(None, w, bias, out, m=m, norm=(x, g, b, 1e-5, rows), warps_k=warps_k)
+        assert rel(out, normed @ w.double().T + bias.double()) < 2e-3   # a row value at a rounding tie may flip
+        out2 = torch.empty(m, n, device=DEV)
+        kernels.linear_stream(None, w, None, out2, m=m, norm=(x, g, None, 1e-5, None), warps_k=warps_k)
+        normed = torch.nn.functional.layer_norm(x.double()[:m], (k,), g.double(), None, 1e-5).float().to(torch.bfloat16)
+        assert rel(out2, normed.double() @ w.double().T) < 2e-3
+
+
 def test_linear_skinny_refuses_what_it_cannot_do():
     assert not kernels.linear_skinny_supports(65, 64, 64, False, False)
     assert not kernels.linear_skinny_supports(4, 100, 64, False, False)     # [K,N] rows of 100 are not 16-byte chunks
     assert not kernels.linear_skinny_supports(4, 64, 100, True, False)
-    assert not kernels.linear_skinny_supports(4, 64, 4096, False, True)     # too wide to normalise in registers
+    assert not kernels.linear_skinny_supports(17, 64, 64, False, True)      # the fused LayerNorm takes one 16-row tile
     with pytest.raises(KernelError, match="not supported"):
         kernels.linear_skinny(torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16),
                               torch.zeros(100, 100, device=DEV, dtype=torch.bfloat16), None,
@@ -396,6 +432,34 @@ def test_sampling_follows_the_inverse_cdf(vocab, options):
         below = c[k - 1] if k > 0 else 0.0
         assert below - 1e-5 <= float(u[r]) <= c[k] + 1e-5, f"row {r}: u={float(u[r])} outside [{below}, {c[k]}]"
         assert abs(logp[r] - lsm[k]) < 2e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_decode_files_the_new_token_itself(dtype):
+    """Given the step's projections, the kernel reads the newest key and value from them and writes them into
+    the page; the result equals appending first and attending then."""
+    hq, hkv, hd = 6, 3, 32
+    lengths = [1, 64, 65, 200]
+    n = len(lengths)
+    k_pool, v_pool, table, _, _ = make_paged(lengths, hkv, hd, dtype)
+    proj = torch.randn(n, (hq + 2 * hkv) * hd, device=DEV).to(dtype)
+    ctx_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    k_ref, v_ref = k_pool.clone(), v_pool.clone()
+    positions = (ctx_len - 1).contiguous()
+    token_seq = torch.arange(n, dtype=torch.int32, device=DEV)
+    kernels.kv_append(proj, hq * hd, (hq + hkv) * hd, positions, token_seq, ctx_len, table, table.shape[1], k_ref, v_ref,
+                      n, hkv, hd)
+    for splits in (1, 3):
+        scratch = torch.empty(max(1, kernels.attention_decode_scratch_floats(n, hq, hd, splits)), device=DEV)
+        want = torch.empty(n, hq * hd, device=DEV, dtype=dtype)
+        kernels.attention_decode(proj, want, k_ref, v_ref, table, table.shape[1], ctx_len, n, hq, hkv, hd, 0.4,
+                                 n_splits=splits, scratch=scratch)
+        k_new, v_new = k_pool.clone(), v_pool.clone()
+        got = torch.empty_like(want)
+        kernels.attention_decode(proj, got, k_new, v_new, table, table.shape[1], ctx_len, n, hq, hkv, hd, 0.4,
+                                 n_splits=splits, scratch=scratch, new_kv_offsets=(hq * hd, (hq + hkv) * hd))
+        assert torch.equal(got, want)
+        assert torch.equal(k_new, k_ref) and torch.equal(v_new, v_ref)
 
 
 def test_logit_edits():
