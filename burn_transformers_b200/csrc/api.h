@@ -31,8 +31,9 @@ int bt_attention_prefill_simt(const void* q, long long q_row_stride, const void*
 long long bt_attention_decode_scratch_floats(int n_seqs, int n_heads, int head_dim, int n_splits);
 int bt_attention_decode(const void* q, long long q_row_stride, const void* new_k, const void* new_v, void* k_pool,
                         void* v_pool, const int* kv_table, int table_stride, int table_len, int page_size, void* out,
-                        float* scratch, int* tickets, const int* ctx_len, int n_seqs, int n_heads, int n_kv_heads,
-                        int head_dim, float scale, int window, int n_splits, int dtype, cudaStream_t stream);
+                        float* scratch, int* tickets, int* status, const int* ctx_len, int n_seqs, int n_heads,
+                        int n_kv_heads, int head_dim, float scale, int window, int n_splits, int max_ctx, int merge,
+                        int dtype, cudaStream_t stream);
 
 int bt_sample(const float* logits, long long row_stride, int n_rows, int vocab, int do_sample, float temperature,
               int top_k, float top_p, float min_p, const float* uniforms, const unsigned long long* stream_seeds,

@@ -1,6 +1,7 @@
 #include "common.cuh"
 #include <atomic>
 #include <cstdarg>
+#include <cstdlib>
 
 namespace bt {
 char* error_buffer() {
@@ -13,6 +14,13 @@ int fail(const char* fmt, ...) {
   vsnprintf(error_buffer(), 512, fmt, args);
   va_end(args);
   return 1;
+}
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("BT_NO_PDL");
+    return !(v && v[0] == '1');
+  }();
+  return on;
 }
 static std::atomic<long long> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }

@@ -36,6 +36,9 @@ void count_launch();
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// BT_NO_PDL=1 in the environment launches every kernel fully serialised (for measurements).
+bool pdl_enabled();
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               int cluster_x, Args... args) {
@@ -47,7 +50,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cudaLaunchAttribute attr[2];
   int n = 0;
   attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[n].val.programmaticStreamSerializationAllowed = 1;
+  attr[n].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
   ++n;
   if (cluster_x > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;

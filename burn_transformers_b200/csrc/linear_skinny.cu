@@ -108,28 +108,34 @@ linear_skinny_kernel(SkinnyParams p) {
 
   // ---- rows ----------------------------------------------------------------------------------------
   if (FUSE_LN) {
+    // Statistics of all rows at once: the block's 128 threads are dealt out 16 (at most 8 rows) or 8 (at most
+    // 16 rows) to a row, so every row's loads are in flight together and one memory round trip serves them all.
+    // Pass 1 sums the row; pass 2 re-reads it (from L1 now) and sums the squared deviations.
     __shared__ float stats[16][2];
-    for (int r = warp; r < 16; r += SK_THREADS / 32) {
-      float mean = 0.f, rstd = 0.f;
-      if (r < p.M) {
-        const float* src = p.x32 + (long long)(p.rows ? p.rows[r] : r) * p.K;
-        float s = 0.f;
-        for (int c = lane * 4; c < p.K; c += 128) {
+    {
+      const int lanes_per_row = p.M <= 8 ? 16 : 8;
+      const int r = tid / lanes_per_row, li = tid % lanes_per_row;
+      const bool live = r < p.M;
+      const float* src = p.x32 + (long long)(live ? (p.rows ? p.rows[r] : r) : 0) * p.K;
+      float s = 0.f;
+      if (live)
+        for (int c = li * 4; c < p.K; c += lanes_per_row * 4) {
           const float4 v = *reinterpret_cast<const float4*>(src + c);
           s += (v.x + v.y) + (v.z + v.w);
         }
-        mean = warp_sum(s) / (float)p.K;
-        float d2 = 0.f;
-        for (int c = lane * 4; c < p.K; c += 128) {
+      for (int o = lanes_per_row >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      const float mean = s / (float)p.K;
+      float d2 = 0.f;
+      if (live)
+        for (int c = li * 4; c < p.K; c += lanes_per_row * 4) {
           const float4 v = *reinterpret_cast<const float4*>(src + c);
           const float a = v.x - mean, b = v.y - mean, cc = v.z - mean, d = v.w - mean;
           d2 += (a * a + b * b) + (cc * cc + d * d);
         }
-        rstd = 1.f / sqrtf(warp_sum(d2) / (float)p.K + p.eps);
-      }
-      if (lane == 0) {
-        stats[r][0] = mean;
-        stats[r][1] = rstd;
+      for (int o = lanes_per_row >> 1; o > 0; o >>= 1) d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+      if (li == 0 && r < 16) {
+        stats[r][0] = live ? mean : 0.f;
+        stats[r][1] = live ? 1.f / sqrtf(d2 / (float)p.K + p.eps) : 0.f;
       }
     }
     __syncthreads();

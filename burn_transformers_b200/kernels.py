@@ -286,19 +286,33 @@ def _tickets(device, count: int) -> torch.Tensor:
     return t
 
 
+_STATUS: dict = {}
+
+
+def kernel_status(device) -> torch.Tensor:
+    """One int per device that a kernel sets when a bounded wait of its own ran out (see attention_decode)."""
+    t = _STATUS.get(device)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS[device] = t
+    return t
+
+
 def attention_decode(q_proj, out, k_pool, v_pool, table, table_len, ctx_len, n_seqs, n_heads, n_kv_heads, head_dim,
-                     scale, *, window=0, n_splits=1, scratch=None, new_kv_offsets=None):
+                     scale, *, max_ctx, window=0, n_splits=1, scratch=None, new_kv_offsets=None, merge_in_scratch=False):
     """Attention of one new token per sequence over that sequence's pages.
 
-    `new_kv_offsets` = (k_offset, v_offset): the new token's key and value are channels of the same `q_proj` rows;
-    the kernel reads them from there and files them in the pages itself.  None: the pages already hold them."""
+    `max_ctx`: no sequence of the call is longer than this.  `new_kv_offsets` = (k_offset, v_offset): the new
+    token's key and value are channels of the same `q_proj` rows; the kernel reads them from there and files
+    them in the pages itself.  None: the pages already hold them.  Up to 8 splits merge inside a thread-block
+    cluster; more (or `merge_in_scratch`) need `scratch`."""
     _need(q_proj, "q_proj", (torch.float32, torch.bfloat16))
     _need(out, "out", q_proj.dtype, (None, n_heads * head_dim))
     _need(k_pool, "k_pool", q_proj.dtype)
     _need(v_pool, "v_pool", q_proj.dtype)
     _need(table, "table", torch.int32)
     tickets = None
-    if n_splits > 1:
+    if n_splits > 1 and (n_splits > 8 or merge_in_scratch):
         need = attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise ShapeError(f"attention_decode: {n_splits} splits need {need} floats of scratch")
@@ -310,9 +324,10 @@ def attention_decode(q_proj, out, k_pool, v_pool, table, table_len, ctx_len, n_s
         new_v = c_void_p(q_proj.data_ptr() + new_kv_offsets[1] * es)
     _check(library().bt_attention_decode(
         _ptr(q_proj), c_longlong(q_proj.shape[1]), new_k, new_v, _ptr(k_pool), _ptr(v_pool), _ptr(table),
-        c_int(table.shape[1]), c_int(table_len), c_int(PAGE_SIZE), _ptr(out), _ptr(scratch), _ptr(tickets), _ptr(ctx_len),
-        c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window),
-        c_int(n_splits), c_int(_code(q_proj.dtype)), _stream()))
+        c_int(table.shape[1]), c_int(table_len), c_int(PAGE_SIZE), _ptr(out), _ptr(scratch), _ptr(tickets),
+        _ptr(kernel_status(q_proj.device)), _ptr(ctx_len), c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads),
+        c_int(head_dim), c_float(scale), c_int(window), c_int(n_splits), c_int(max_ctx),
+        c_int(1 if merge_in_scratch else 0), c_int(_code(q_proj.dtype)), _stream()))
 
 
 def sample(logits, n_rows, *, do_sample, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0, uniforms=None,

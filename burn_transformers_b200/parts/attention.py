@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from ..cache.spec import CacheNeed, KvSpec
+from ..cache.spec import PAGE_SIZE, CacheNeed, KvSpec
 from ..errors import CacheError
 from ..weights.spec import MATRIX, VECTOR, TensorSpec
 from .base import Mixer
@@ -53,11 +53,14 @@ class CausalSelfAttention(Mixer):
         return CacheNeed(kv=KvSpec(self.n_kv_heads, self.head_dim, self.window))
 
     def _splits(self, ctx) -> int:
+        """Blocks per (sequence, head) in a decode step: enough to fill the GPU about twice and to keep a block's
+        share of the cache to a few pages; at most 8, so that they merge inside one thread-block cluster."""
         units = max(1, ctx.n_seqs * self.n_heads)
         span = ctx.ctx_bound if self.window is None else min(ctx.ctx_bound, self.window)
-        by_work = max(1, (span + 127) // 128)           # at least 128 keys per split
-        by_fill = max(1, (2 * _SM_COUNT + units - 1) // units)
-        return int(min(by_work, by_fill, 64))
+        pages = max(1, -(-span // PAGE_SIZE))
+        by_fill = -(-2 * _SM_COUNT // units)
+        by_share = -(-pages // 4)
+        return int(max(1, min(max(by_fill, by_share), pages, 8)))
 
     def forward(self, ctx, x, residual, entry, owns_cache=True):
         n = ctx.n_tokens
@@ -72,14 +75,9 @@ class CausalSelfAttention(Mixer):
                               ctx.ctx_len, table, group.table_len, k_pool, v_pool, n, self.n_kv_heads, self.head_dim)
         mixed = ctx.ws.take((n, self.q_width), dtype)
         if ctx.is_decode:
-            splits = self._splits(ctx)
-            scratch = None
-            if splits > 1:
-                need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.n_heads, self.head_dim, splits)
-                scratch = ctx.ws.take((need,), torch.float32)
             kernels.attention_decode(proj, mixed, k_pool, v_pool, table, group.table_len, ctx.ctx_len, ctx.n_seqs,
                                      self.n_heads, self.n_kv_heads, self.head_dim, self.scale, window=window,
-                                     n_splits=splits, scratch=scratch,
+                                     n_splits=self._splits(ctx), max_ctx=ctx.ctx_bound,
                                      new_kv_offsets=(self.q_width, self.q_width + self.kv_width) if owns_cache else None)
         elif ctx.fresh and owns_cache:
             # every sequence starts at position 0: keys and values are the step's own projections

@@ -223,9 +223,10 @@ def attend(q, k, v, scale, q_pos, window=0, causal=True):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hq, hkv, hd, window, splits", [
-    (4, 4, 16, 0, 1), (5, 5, 48, 0, 3), (6, 2, 80, 0, 2), (8, 1, 128, 100, 4), (2, 2, 256, 0, 1), (3, 3, 32, 64, 7)])
+    (4, 4, 16, 0, 1), (5, 5, 48, 0, 3), (6, 2, 80, 0, 2), (8, 1, 128, 100, 4), (2, 2, 256, 0, 1), (3, 3, 32, 64, 7),
+    (2, 2, 64, 0, 8), (2, 1, 64, 0, 12), (2, 2, 256, 0, 2)])
 def test_attention_decode(dtype, hq, hkv, hd, window, splits):
-    lengths = [1, 63, 64, 65, 300, 129]
+    lengths = [1, 63, 64, 65, 300, 129] + ([1500] if hd == 256 else [])     # 1500 x 256 needs several rounds of pages
     k_pool, v_pool, table, dk, dv = make_paged(lengths, hkv, hd, dtype)
     n = len(lengths)
     q = torch.randn(n, (hq + 2 * hkv) * hd, device=DEV).to(dtype)     # queries inside a wider projection row
@@ -233,12 +234,16 @@ def test_attention_decode(dtype, hq, hkv, hd, window, splits):
     out = torch.empty(n, hq * hd, device=DEV, dtype=dtype)
     scratch = torch.empty(max(1, kernels.attention_decode_scratch_floats(n, hq, hd, splits)), device=DEV)
     scale = 0.37
-    kernels.attention_decode(q, out, k_pool, v_pool, table, table.shape[1], ctx_len, n, hq, hkv, hd, scale,
-                             window=window, n_splits=splits, scratch=scratch)
-    for s, length in enumerate(lengths):
-        qs = q[s, :hq * hd].double().cpu().view(1, hq, hd)
-        want = attend(qs, dk[s], dv[s], scale, torch.tensor([length - 1]), window)
-        assert rel(out[s].view(1, hq, hd), want) < TOL[dtype] * 2, f"sequence {s} of length {length}"
+    for in_scratch in (False, True):
+        out.fill_(float("nan"))
+        kernels.attention_decode(q, out, k_pool, v_pool, table, table.shape[1], ctx_len, n, hq, hkv, hd, scale,
+                                 window=window, n_splits=splits, scratch=scratch, max_ctx=max(lengths),
+                                 merge_in_scratch=in_scratch)
+        for s, length in enumerate(lengths):
+            qs = q[s, :hq * hd].double().cpu().view(1, hq, hd)
+            want = attend(qs, dk[s], dv[s], scale, torch.tensor([length - 1]), window)
+            assert rel(out[s].view(1, hq, hd), want) < TOL[dtype] * 2, f"sequence {s} of length {length}"
+    assert int(kernels.kernel_status(q.device)) == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -259,7 +264,7 @@ def test_attention_decode_finds_one_far_key_among_hundreds(dtype, target, splits
     out = torch.empty(1, hq * hd, device=DEV, dtype=dtype)
     scratch = torch.empty(max(1, kernels.attention_decode_scratch_floats(1, hq, hd, splits)), device=DEV)
     kernels.attention_decode(q, out, k_pool, v_pool, table, table.shape[1], ctx_len, 1, hq, hkv, hd, 1.0,
-                             n_splits=splits, scratch=scratch)
+                             n_splits=splits, scratch=scratch, max_ctx=length)
     got = out.float().view(hq, hd)
     for h in range(hq):
         assert float((got[h] - (50.0 + h)).abs().max()) < 0.5
@@ -280,7 +285,7 @@ def test_attention_decode_window_edge(dtype):
         scratch = torch.empty(kernels.attention_decode_scratch_floats(1, 1, hd, 2), device=DEV)
         kernels.attention_decode(q, out, k_pool, v_pool, table, table.shape[1],
                                  torch.tensor([length], dtype=torch.int32, device=DEV), 1, 1, 1, hd, 1.0,
-                                 window=window, n_splits=2, scratch=scratch)
+                                 window=window, n_splits=2, scratch=scratch, max_ctx=length)
         assert (float(out.float().mean()) > 80.0) == inside
 
 
@@ -453,11 +458,12 @@ def test_attention_decode_files_the_new_token_itself(dtype):
         scratch = torch.empty(max(1, kernels.attention_decode_scratch_floats(n, hq, hd, splits)), device=DEV)
         want = torch.empty(n, hq * hd, device=DEV, dtype=dtype)
         kernels.attention_decode(proj, want, k_ref, v_ref, table, table.shape[1], ctx_len, n, hq, hkv, hd, 0.4,
-                                 n_splits=splits, scratch=scratch)
+                                 n_splits=splits, scratch=scratch, max_ctx=max(lengths))
         k_new, v_new = k_pool.clone(), v_pool.clone()
         got = torch.empty_like(want)
         kernels.attention_decode(proj, got, k_new, v_new, table, table.shape[1], ctx_len, n, hq, hkv, hd, 0.4,
-                                 n_splits=splits, scratch=scratch, new_kv_offsets=(hq * hd, (hq + hkv) * hd))
+                                 n_splits=splits, scratch=scratch, new_kv_offsets=(hq * hd, (hq + hkv) * hd),
+                                 max_ctx=max(lengths))
         assert torch.equal(got, want)
         assert torch.equal(k_new, k_ref) and torch.equal(v_new, v_ref)
 

@@ -54,7 +54,8 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(dtype, tol):
         want = torch.empty(n, c["hq"] * c["hd"], device=DEV, dtype=dtype)
         scratch = torch.empty(kernels.attention_decode_scratch_floats(n, c["hq"], c["hd"], c["splits"]), device=DEV)
         kernels.attention_decode(q, want, k, v, table, table.shape[1], ctx_len, n, c["hq"], c["hkv"], c["hd"], 0.3,
-                                 window=c["window"], n_splits=c["splits"], scratch=scratch)
+                                 window=c["window"], n_splits=c["splits"], scratch=scratch, max_ctx=max(c["lengths"]),
+                                 merge_in_scratch=True)
         got = torch.full_like(want, float("nan"))
         before = torch.cuda.memory_allocated()
         rc = call_static(lib, q, k, v, table, ctx_len, got, c["hq"], c["hkv"], c["hd"], 0.3, c["window"], c["splits"])
