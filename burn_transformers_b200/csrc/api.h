@@ -40,6 +40,9 @@ int bt_sample(const float* logits, long long row_stride, int n_rows, int vocab, 
               const int* counters, int* out_ids, float* out_logp, cudaStream_t stream);
 int bt_advance(const int* ids, int* tokens, int* positions, int* past_len, int* ctx_len, int* counters, int n,
                cudaStream_t stream);
+int bt_linear_tcgen05_supports(int M, int N, int K);
+int bt_linear_tcgen05(const void* a, const void* w, const float* bias, const float* residual, void* out, int* status,
+                      int M, int N, int K, int act, int out_is_f32, cudaStream_t stream);
 int bt_linear_stream_supports(int M, int N, int K, int fuse_ln);
 int bt_linear_stream(const void* a, const float* x32, const int* rows, const float* gamma, const float* beta, float eps,
                      const void* w, const float* bias, const float* residual, void* out, int M, int N, int K, int act,

@@ -1,0 +1,255 @@
+// Matrix products for steps with many rows (prefill), bfloat16 operands, 32-bit accumulation, on the
+// fifth-generation tensor cores:  out[M,N] = act(A[M,K] @ W[N,K]^T + bias) (+ residual).
+//
+// One block computes a 128 x BN tile of the output.  Its six warps have fixed jobs:
+//   warp 0    asks the tensor memory accelerator (TMA) for the next 128 x 64 tile of A and BN x 64 tile of W
+//             (cp.async.bulk.tensor, 128-byte swizzle) into a ring of shared-memory stages;
+//   warp 1    one elected thread issues tcgen05.mma (M = 128, N = BN, K = 16, four per stage) whose accumulator
+//             lives in tensor memory (TMEM), and commits each stage back to the producer when it has been read;
+//   warps 2-5 wait for the last commit, read the accumulator with tcgen05.ld (a warp reaches the 32 TMEM lanes of
+//             its quarter), add the bias, apply GELU, add the 32-bit residual and store 32-bit or bfloat16 rows.
+// Both operands are K-major (K contiguous): A as the activations are stored, W as [N, K].
+// Stages hand over through mbarriers; every wait is bounded, and a wait that runs out marks the call as failed
+// (status word) instead of hanging: the block still frees its tensor memory and returns.
+// Rows and columns beyond M, N, K are zero-filled by the TMA on the way in and skipped on the way out.
+#include "common.cuh"
+#include "tma.cuh"
+
+namespace bt {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;                 // bfloat16 per stage row: 128 bytes, the swizzle span
+constexpr int TC_THREADS = 192;
+constexpr int TC_WAIT_LIMIT = 1 << 22;    // polls of an mbarrier before giving up
+
+struct TcParams {
+  const float* bias;        // [N] or null
+  const float* residual;    // [M, N] 32-bit or null (may be `out`)
+  void* out;                // [M, N] 32-bit or bfloat16
+  int* status;              // set to 1 when a bounded wait ran out
+  int M, N, K, act, out_is_f32;
+};
+
+__device__ __forceinline__ unsigned tc_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void tc_bar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void tc_bar_expect(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool tc_bar_wait(unsigned long long* bar, unsigned parity) {
+  for (int i = 0; i < TC_WAIT_LIMIT; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(tc_smem(bar)), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tc_tma_load(void* dst, const CUtensorMap* map, int col, int row, unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+          tc_smem(dst)),
+      "l"(map), "r"(col), "r"(row), "r"(tc_smem(bar))
+      : "memory");
+}
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ unsigned long long tc_desc(const void* tile) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((tc_smem(tile) & 0x3FFFFu) >> 4);   // start address, 16-byte units
+  d |= (unsigned long long)1 << 16;                             // leading byte offset (unused with this swizzle)
+  d |= (unsigned long long)(1024 >> 4) << 32;                   // stride byte offset: next group of 8 rows
+  d |= (unsigned long long)1 << 46;                             // descriptor version of this architecture
+  d |= (unsigned long long)2 << 61;                             // 128-byte swizzle
+  return d;
+}
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(unsigned taddr, float (&v)[16]) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared memory: STAGES x (A tile 128 x 64, W tile BN x 64), each tile 1024-byte aligned.
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS)
+linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, TcParams p) {
+  extern __shared__ unsigned char tc_smem_raw[];
+  __shared__ __align__(8) unsigned long long full[STAGES], empty[STAGES], acc_ready;
+  __shared__ unsigned tmem_base;
+  __shared__ int failed;
+  constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2;
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<unsigned long long>(tc_smem_raw) + 1023ull) & ~1023ull);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+  const int k_blocks = (p.K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tc_bar_init(&full[s], 1);
+      tc_bar_init(&empty[s], 1);
+    }
+    tc_bar_init(&acc_ready, 1);
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    // the accumulator: BN 32-bit columns of tensor memory (a power of two of at least 32)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(&tmem_base)), "r"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_acc = tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !tc_bar_wait(&empty[s], ((kb / STAGES) - 1) & 1)) {
+          failed = 1;
+          break;
+        }
+        tc_bar_expect(&full[s], A_BYTES + W_BYTES);
+        unsigned char* a_tile = tiles + (size_t)s * (A_BYTES + W_BYTES);
+        tc_tma_load(a_tile, &map_a, kb * TC_BK, m0, &full[s]);
+        tc_tma_load(a_tile + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // instruction descriptor: 32-bit accumulator, bfloat16 operands, both K-major, N = BN, M = 128
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; ++kb) {
+        const int s = kb % STAGES;
+        if (!tc_bar_wait(&full[s], (kb / STAGES) & 1)) {
+          failed = 1;
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        unsigned char* a_tile = tiles + (size_t)s * (A_BYTES + W_BYTES);
+        const unsigned long long da = tc_desc(a_tile), dw = tc_desc(a_tile + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k)   // 16 bfloat16 = 32 bytes further along the row: +2 in 16-byte units
+          tc_mma(tmem_acc, da + 2ull * k, dw + 2ull * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&empty[s]);                  // arrives when these products have read the stage
+      }
+      tc_commit(&acc_ready);                   // arrives when every product issued so far has finished
+    }
+  } else {
+    // epilogue: warp w reaches TMEM lanes 32 * (w % 4) .. + 31, i.e. the tile's rows of that quarter
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    const bool ok = tc_bar_wait(&acc_ready, 0);
+    if (!ok) failed = 1;
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        tc_ld16(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, v);
+        if (row < p.M) {
+          const long long o = (long long)row * p.N + n0 + c0;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int col = n0 + c0 + i;
+            if (col < p.N) {
+              float x = v[i];
+              if (p.bias) x += p.bias[col];
+              x = apply_activation(x, p.act);
+              if (p.residual) x += p.residual[o + i];
+              v[i] = x;
+            }
+          }
+          if (n0 + c0 + 16 <= p.N && (p.N & 7) == 0) {
+            if (p.out_is_f32) {
+              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o);
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                __nv_bfloat162 h[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+                dst[i] = *reinterpret_cast<uint4*>(h);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (n0 + c0 + i < p.N) {
+                if (p.out_is_f32)
+                  reinterpret_cast<float*>(p.out)[o + i] = v[i];
+                else
+                  reinterpret_cast<__nv_bfloat16*>(p.out)[o + i] = __float2bfloat16_rn(v[i]);
+              }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_acc), "r"(BN) : "memory");
+  }
+  if (threadIdx.x == 0 && failed && p.status) atomicExch(p.status, 2);
+}
+
+template <int BN, int STAGES>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const TcParams& p, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+  auto kern = linear_tcgen05_kernel<BN, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  BT_CHECK(e == cudaSuccess, "linear_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+  dim3 grid((p.N + BN - 1) / BN, (p.M + TC_BM - 1) / TC_BM);
+  kern<<<grid, TC_THREADS, smem, stream>>>(ma, mw, p);
+  BT_LAUNCH_OK("linear_tcgen05");
+  return 0;
+}
+
+}  // namespace bt
+
+extern "C" int bt_linear_tcgen05_supports(int M, int N, int K) {
+  return M >= 1 && N >= 8 && K >= 8 && K % 8 == 0;   // rows of A and W are 16-byte multiples
+}
+
+// a: [M, K] bfloat16; w: [N, K] bfloat16; out: [M, N] 32-bit (out_is_f32) or bfloat16.
+extern "C" int bt_linear_tcgen05(const void* a, const void* w, const float* bias, const float* residual, void* out,
+                                 int* status, int M, int N, int K, int act, int out_is_f32, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(bt_linear_tcgen05_supports(M, N, K), "linear_tcgen05: sizes M=%d N=%d K=%d are not supported", M, N, K);
+  BT_CHECK(act >= 0 && act <= 2, "linear_tcgen05: unknown activation %d", act);
+  BT_CHECK(!(residual && !out_is_f32), "linear_tcgen05: a residual needs a 32-bit output");
+  // narrow outputs take narrower tiles so that the grid still covers the GPU
+  const long long tiles128 = (long long)((M + TC_BM - 1) / TC_BM) * ((N + 127) / 128);
+  const int bn = (N <= 64 || tiles128 < 148) ? 64 : 128;
+  CUtensorMap ma, mw;
+  if (int rc = tensor_map_2d_bf16(&ma, a, (unsigned long long)M, (unsigned long long)K, (unsigned long long)K, TC_BM)) return rc;
+  if (int rc = tensor_map_2d_bf16(&mw, w, (unsigned long long)N, (unsigned long long)K, (unsigned long long)K, (unsigned)bn)) return rc;
+  TcParams p{bias, residual, out, status, M, N, K, act, out_is_f32};
+  if (bn == 64) return launch_tc<64, 4>(ma, mw, p, stream);
+  return launch_tc<128, 3>(ma, mw, p, stream);   // 96 KB of stages: two blocks per SM, one computes while the other stores
+}

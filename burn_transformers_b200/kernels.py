@@ -186,6 +186,30 @@ def linear_skinny(a, w, bias, out, *, m, w_is_nk=False, activation=None, residua
                                       c_int(1 if out.dtype == torch.float32 else 0), c_int(split), _stream()))
 
 
+def linear_tcgen05_supports(m, n, k) -> bool:
+    return bool(library().bt_linear_tcgen05_supports(c_int(m), c_int(n), c_int(k)))
+
+
+def linear_tcgen05(a, w, bias, out, *, m, activation=None, residual=None):
+    """out[:m] = act(a[:m] @ w^T + bias) (+ residual) on the tcgen05 tensor cores; a [M, K] and w [N, K] bfloat16."""
+    n, k = w.shape
+    _need(a, "a", torch.bfloat16, (None, k))
+    _need(w, "w", torch.bfloat16, (n, k))
+    _need(out, "out", (torch.float32, torch.bfloat16), (None, n))
+    if a.shape[0] < m or out.shape[0] < m:
+        raise ShapeError(f"linear_tcgen05: {m} rows asked of a[{a.shape[0]}] and out[{out.shape[0]}]")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (n,))
+    if residual is not None:
+        _need(residual, "residual", torch.float32, (None, n))
+    if activation not in ACTIVATIONS:
+        raise ShapeError(f"linear_tcgen05: unknown activation {activation!r}")
+    _check(library().bt_linear_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out),
+                                       _ptr(kernel_status(a.device)), c_int(m), c_int(n), c_int(k),
+                                       c_int(ACTIVATIONS[activation]), c_int(1 if out.dtype == torch.float32 else 0),
+                                       _stream()))
+
+
 def linear_stream_supports(m, n, k, fuse_ln) -> bool:
     return bool(library().bt_linear_stream_supports(c_int(m), c_int(n), c_int(k), c_int(1 if fuse_ln else 0)))
 

@@ -25,6 +25,7 @@ class CausalSelfAttention(Mixer):
     """
 
     accepts_lazy_norm = True
+    linear_weights = ("qkv.weight", "out.weight")
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, *,
                  causal: bool = True, window: int | None = None, bias: bool = True,
@@ -66,7 +67,8 @@ class CausalSelfAttention(Mixer):
         n = ctx.n_tokens
         dtype = ctx.dtype
         proj = ctx.ws.take((n, self.proj_width), dtype)
-        linear(ctx, x, self.t_qkv_weight, self.t_qkv_bias if self.has_bias else None, proj, m=n)
+        linear(ctx, x, self.t_qkv_weight, self.t_qkv_bias if self.has_bias else None, proj, m=n,
+               w_is_nk=self.nk_qkv_weight)
         k_pool, v_pool, group, g = ctx.cache.layer_pools(entry)
         table = ctx.tables[g]
         window = self.window or 0
@@ -94,4 +96,4 @@ class CausalSelfAttention(Mixer):
                                            causal=self.causal, window=window, k_pool=k_pool, v_pool=v_pool,
                                            table=table, table_len=group.table_len)
         linear(ctx, mixed, self.t_out_weight, self.t_out_bias if self.has_bias else None, residual, m=n,
-               residual=residual)
+               residual=residual, w_is_nk=self.nk_out_weight)

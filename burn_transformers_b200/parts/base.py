@@ -27,9 +27,21 @@ class Part:
     def specs(self) -> dict[str, TensorSpec]:
         return {}
 
+    # Names of [in, out] matrices that are only ever the right-hand side of parts.linear.linear.  In bfloat16
+    # they are kept transposed, [out, in] with the input axis contiguous: the layout the tensor-core and the
+    # weight-streaming kernels read (both operands K-major).  `nk_<name>` says which layout `t_<name>` has.
+    linear_weights: tuple[str, ...] = ()
+
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         for name in self.specs():
-            setattr(self, "t_" + name.replace(".", "_"), tensors[name])
+            tensor = tensors[name]
+            attr = name.replace(".", "_")
+            if name in self.linear_weights:
+                transposed = tensor.dtype == torch.bfloat16
+                if transposed:
+                    tensor = tensor.t().contiguous()
+                setattr(self, "nk_" + attr, transposed)
+            setattr(self, "t_" + attr, tensor)
 
     # Parts made only of this library's kernels can be captured in a CUDA graph.
     graph_safe = True

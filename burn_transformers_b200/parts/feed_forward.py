@@ -14,6 +14,7 @@ class DenseFeedForward(FeedForward):
     accumulator and rounded once."""
 
     accepts_lazy_norm = True
+    linear_weights = ("up.weight", "down.weight")
 
     def __init__(self, width: int, inner: int, activation: str, *, bias: bool = True, init_std: float = 0.02,
                  down_init_std: float | None = None):
@@ -35,6 +36,6 @@ class DenseFeedForward(FeedForward):
         n = ctx.n_tokens
         hidden = ctx.ws.take((n, self.inner), ctx.dtype)
         linear(ctx, x, self.t_up_weight, self.t_up_bias if self.has_bias else None, hidden, m=n,
-               activation=self.activation)
+               activation=self.activation, w_is_nk=self.nk_up_weight)
         linear(ctx, hidden, self.t_down_weight, self.t_down_bias if self.has_bias else None, residual, m=n,
-               residual=residual)
+               residual=residual, w_is_nk=self.nk_down_weight)

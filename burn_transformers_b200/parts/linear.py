@@ -20,15 +20,15 @@ class LazyNorm:
 
 
 def linear(ctx, a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=None):
-    """out[:m] = act(a[:m] @ w + bias) (+ residual[:m]).
+    """out[:m] = act(a[:m] @ w + bias) (+ residual[:m]);  w is [K, N], or [N, K] when `w_is_nk`.
 
-    32-bit operands always take the plain fused-multiply-add kernel: the 32-bit path has no
-    reduced-precision matrix mode.  bfloat16 products of at most 64 rows take the weight-streaming kernel,
-    which can also normalise its rows on the way in."""
+    32-bit operands always take the plain fused-multiply-add kernel: the 32-bit path has no reduced-precision
+    matrix mode.  bfloat16 products of at most 64 rows take a weight-streaming kernel, which can also normalise
+    its rows on the way in; with more rows (and [N, K] weights) they run on the tcgen05 tensor cores."""
     lazy = isinstance(a, LazyNorm)
+    n = w.shape[0] if w_is_nk else w.shape[1]
+    k = w.shape[1] if w_is_nk else w.shape[0]
     if w.dtype == torch.bfloat16 and m <= 64:
-        n = w.shape[0] if w_is_nk else w.shape[1]
-        k = w.shape[1] if w_is_nk else w.shape[0]
         fuse = lazy and m <= 16 and a.norm.fusable
         if w_is_nk and n >= 8192 and kernels.linear_stream_supports(m, n, k, fuse):
             # a wide [N, K] table (the readout): long weight rows, streamed straight into registers
@@ -47,4 +47,7 @@ def linear(ctx, a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=
             return
     if lazy:
         a = a.materialize(ctx)
+    if w.dtype == torch.bfloat16 and w_is_nk and m > 64 and kernels.linear_tcgen05_supports(m, n, k):
+        kernels.linear_tcgen05(a, w, bias, out, m=m, activation=activation, residual=residual)
+        return
     kernels.linear_simt(a, w, bias, out, m=m, w_is_nk=w_is_nk, activation=activation, residual=residual)

@@ -169,6 +169,30 @@ def test_linear_stream(m, n, k, warps_k):
         assert rel(out2, normed.double() @ w.double().T) < 2e-3
 
 
+@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (2048, 2304, 768), (300, 768, 3072), (1000, 3072, 768), (65, 200, 96),
+                                     (129, 50257, 64), (2, 8, 8), (513, 776, 1000)])
+def test_linear_tcgen05(m, n, k):
+    a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    bias, res = torch.randn(n, device=DEV), torch.randn(m, n, device=DEV)
+    assert kernels.linear_tcgen05_supports(m, n, k)
+    product = a.double() @ w.double().T
+    # a 32-bit sum of K products: roundings add up like a random walk, sqrt(K) * 2^-24, with a factor for the
+    # tensor core's own accumulation order
+    tol = 4.0 * math.sqrt(k) * 2.0 ** -24
+    out = torch.full((m + 1, n), 5.0, device=DEV)
+    kernels.linear_tcgen05(a, w, None, out, m=m)
+    assert rel(out[:m], product) < tol and float((out[m:] - 5.0).abs().max()) == 0.0
+    out = res.clone()
+    kernels.linear_tcgen05(a, w, bias, out, m=m, activation="gelu_new", residual=out)
+    want = torch.nn.functional.gelu(product + bias.double(), approximate="tanh") + res.double()
+    assert rel(out, want) < tol
+    low = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    kernels.linear_tcgen05(a, w, bias, low, m=m, activation="gelu")
+    assert rel(low, torch.nn.functional.gelu(product + bias.double())) < 4e-3
+    assert int(kernels.kernel_status(a.device)) == 0
+
+
 def test_linear_skinny_refuses_what_it_cannot_do():
     assert not kernels.linear_skinny_supports(65, 64, 64, False, False)
     assert not kernels.linear_skinny_supports(4, 100, 64, False, False)     # [K,N] rows of 100 are not 16-byte chunks
