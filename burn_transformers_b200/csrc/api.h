@@ -28,6 +28,12 @@ int bt_attention_prefill_simt(const void* q, long long q_row_stride, const void*
                               int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim, float scale,
                               int causal, int window, int dtype, cudaStream_t stream);
 
+int bt_attention_prefill_mma_supports(int head_dim, int page_size);
+int bt_attention_prefill_mma(const void* q, long long q_row_stride, const void* k, const void* v, const int* kv_table,
+                             int table_stride, int table_len, int page_size, long long kv_row_stride, void* out,
+                             const int* seq_start, const int* past_len, int n_seqs, int max_new, int n_heads,
+                             int n_kv_heads, int head_dim, float scale, int causal, int window, cudaStream_t stream);
+
 long long bt_attention_decode_scratch_floats(int n_seqs, int n_heads, int head_dim, int n_splits);
 int bt_attention_decode(const void* q, long long q_row_stride, const void* new_k, const void* new_v, void* k_pool,
                         void* v_pool, const int* kv_table, int table_stride, int table_len, int page_size, void* out,

@@ -294,6 +294,42 @@ def attention_prefill_simt(q_proj, out, seq_start, past_len, n_seqs, max_new, n_
         c_int(_code(q_proj.dtype)), _stream()))
 
 
+def attention_prefill(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale, **kw):
+    """Attention of several new tokens per sequence: on tensor cores for bfloat16 and the head sizes that kernel is
+    built for, else with the plain 32-bit kernel.  Arguments as attention_prefill_simt."""
+    lib = library()
+    if q_proj.dtype == torch.bfloat16 and lib.bt_attention_prefill_mma_supports(c_int(head_dim), c_int(PAGE_SIZE)):
+        return _attention_prefill_call(lib.bt_attention_prefill_mma, False, q_proj, out, seq_start, past_len, n_seqs,
+                                       max_new, n_heads, n_kv_heads, head_dim, scale, **kw)
+    return attention_prefill_simt(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim,
+                                  scale, **kw)
+
+
+def _attention_prefill_call(fn, with_dtype, q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads,
+                            head_dim, scale, *, causal=True, window=0, k_pool=None, v_pool=None, table=None,
+                            table_len=0, k_offset=None, v_offset=None):
+    _need(q_proj, "q_proj", (torch.float32, torch.bfloat16))
+    _need(out, "out", q_proj.dtype, (None, n_heads * head_dim))
+    stride = q_proj.shape[1]
+    es = q_proj.element_size()
+    if table is None:
+        k_ptr = c_void_p(q_proj.data_ptr() + k_offset * es)
+        v_ptr = c_void_p(q_proj.data_ptr() + v_offset * es)
+        t_ptr, t_stride = c_void_p(0), 0
+    else:
+        _need(k_pool, "k_pool", q_proj.dtype)
+        _need(v_pool, "v_pool", q_proj.dtype)
+        _need(table, "table", torch.int32)
+        k_ptr, v_ptr, t_ptr, t_stride = _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1]
+    args = [_ptr(q_proj), c_longlong(stride), k_ptr, v_ptr, t_ptr, c_int(t_stride), c_int(table_len), c_int(PAGE_SIZE),
+            c_longlong(stride), _ptr(out), _ptr(seq_start), _ptr(past_len), c_int(n_seqs), c_int(max_new), c_int(n_heads),
+            c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(1 if causal else 0), c_int(window)]
+    if with_dtype:
+        args.append(c_int(_code(q_proj.dtype)))
+    args.append(_stream())
+    _check(fn(*args))
+
+
 def attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits) -> int:
     return int(library().bt_attention_decode_scratch_floats(c_int(n_seqs), c_int(n_heads), c_int(head_dim), c_int(n_splits)))
 

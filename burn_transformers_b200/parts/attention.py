@@ -83,7 +83,7 @@ class CausalSelfAttention(Mixer):
                                      new_kv_offsets=(self.q_width, self.q_width + self.kv_width) if owns_cache else None)
         elif ctx.fresh and owns_cache:
             # every sequence starts at position 0: keys and values are the step's own projections
-            kernels.attention_prefill_simt(proj, mixed, ctx.seq_start, ctx.past_len, ctx.n_seqs, ctx.max_new,
+            kernels.attention_prefill(proj, mixed, ctx.seq_start, ctx.past_len, ctx.n_seqs, ctx.max_new,
                                            self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
                                            causal=self.causal, window=window,
                                            k_offset=self.q_width, v_offset=self.q_width + self.kv_width)
@@ -91,7 +91,7 @@ class CausalSelfAttention(Mixer):
             if group.is_ring:
                 raise CacheError("a step that brings several tokens to sequences that already hold some is not "
                                  "supported for windowed layers: their ring of pages keeps one window only")
-            kernels.attention_prefill_simt(proj, mixed, ctx.seq_start, ctx.past_len, ctx.n_seqs, ctx.max_new,
+            kernels.attention_prefill(proj, mixed, ctx.seq_start, ctx.past_len, ctx.n_seqs, ctx.max_new,
                                            self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
                                            causal=self.causal, window=window, k_pool=k_pool, v_pool=v_pool,
                                            table=table, table_len=group.table_len)

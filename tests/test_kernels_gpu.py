@@ -316,20 +316,20 @@ def test_attention_decode_window_edge(dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hq, hkv, hd, window, causal", [
     (4, 4, 16, 0, True), (5, 5, 48, 0, True), (6, 3, 80, 0, True), (2, 1, 128, 40, True), (2, 2, 256, 0, True),
-    (3, 3, 64, 0, False)])
+    (3, 3, 64, 0, False), (3, 3, 64, 0, True), (4, 2, 64, 70, True), (2, 2, 128, 0, True)])
 def test_attention_prefill_packed_and_paged(dtype, hq, hkv, hd, window, causal):
     """Several new tokens per sequence: from the step's own projections (sequences that start at 0) and from
     the pages (sequences that already hold tokens), with unequal lengths."""
-    news, pasts = [1, 17, 64, 100], [0, 0, 0, 0]
+    news, pasts = [1, 17, 64, 100, 200], [0, 0, 0, 0, 0]
     width = (hq + 2 * hkv) * hd
     n_tok = sum(news)
     proj = torch.randn(n_tok, width, device=DEV).to(dtype)
     seq_start = torch.tensor([0] + list(np.cumsum(news)), dtype=torch.int32, device=DEV)
     out = torch.empty(n_tok, hq * hd, device=DEV, dtype=dtype)
     scale = 0.3
-    kernels.attention_prefill_simt(proj, out, seq_start, torch.tensor(pasts, dtype=torch.int32, device=DEV),
-                                   len(news), max(news), hq, hkv, hd, scale, causal=causal, window=window,
-                                   k_offset=hq * hd, v_offset=(hq + hkv) * hd)
+    kernels.attention_prefill(proj, out, seq_start, torch.tensor(pasts, dtype=torch.int32, device=DEV),
+                              len(news), max(news), hq, hkv, hd, scale, causal=causal, window=window,
+                              k_offset=hq * hd, v_offset=(hq + hkv) * hd)
     p64 = proj.double().cpu()
     for s, n in enumerate(news):
         rows = p64[int(seq_start[s]):int(seq_start[s]) + n]
@@ -342,7 +342,7 @@ def test_attention_prefill_packed_and_paged(dtype, hq, hkv, hd, window, causal):
     if not causal:
         return
     # paged: sequences hold `past` tokens already; the new tokens' keys are appended first
-    pasts = [0, 5, 64, 130]
+    pasts = [0, 5, 64, 130, 77]
     lengths = [p + n for p, n in zip(pasts, news)]
     k_pool, v_pool, table, dk, dv = make_paged(lengths, hkv, hd, dtype)
     positions = torch.cat([torch.arange(p, p + n) for p, n in zip(pasts, news)]).to(torch.int32).to(DEV)
@@ -350,9 +350,9 @@ def test_attention_prefill_packed_and_paged(dtype, hq, hkv, hd, window, causal):
     ctx_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
     kernels.kv_append(proj, hq * hd, (hq + hkv) * hd, positions, token_seq, ctx_len, table, table.shape[1], k_pool,
                       v_pool, n_tok, hkv, hd)
-    kernels.attention_prefill_simt(proj, out, seq_start, torch.tensor(pasts, dtype=torch.int32, device=DEV),
-                                   len(news), max(news), hq, hkv, hd, scale, causal=True, window=window,
-                                   k_pool=k_pool, v_pool=v_pool, table=table, table_len=table.shape[1])
+    kernels.attention_prefill(proj, out, seq_start, torch.tensor(pasts, dtype=torch.int32, device=DEV),
+                              len(news), max(news), hq, hkv, hd, scale, causal=True, window=window,
+                              k_pool=k_pool, v_pool=v_pool, table=table, table_len=table.shape[1])
     for s, n in enumerate(news):
         rows = p64[int(seq_start[s]):int(seq_start[s]) + n]
         k = torch.cat([dk[s][:pasts[s]], rows[:, hq * hd:(hq + hkv) * hd].view(n, hkv, hd)])
@@ -363,9 +363,10 @@ def test_attention_prefill_packed_and_paged(dtype, hq, hkv, hd, window, causal):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_attention_prefill_never_looks_ahead(dtype):
+@pytest.mark.parametrize("hd", [32, 64])
+def test_attention_prefill_never_looks_ahead(dtype, hd):
     """A future key that matches the query perfectly must not be seen; the same key in the past must."""
-    hd, n = 32, 90
+    n = 90
     proj = (torch.randn(n, 3 * hd, device=DEV) * 0.1).to(dtype)
     seq_start = torch.tensor([0, n], dtype=torch.int32, device=DEV)
     past = torch.zeros(1, dtype=torch.int32, device=DEV)
@@ -374,10 +375,10 @@ def test_attention_prefill_never_looks_ahead(dtype):
     proj[key, hd:2 * hd] = 3.0
     proj[key, 2 * hd:] = 70.0
     out = torch.empty(n, hd, device=DEV, dtype=dtype)
-    kernels.attention_prefill_simt(proj, out, seq_start, past, 1, n, 1, 1, hd, 1.0, k_offset=hd, v_offset=2 * hd)
+    kernels.attention_prefill(proj, out, seq_start, past, 1, n, 1, 1, hd, 1.0, k_offset=hd, v_offset=2 * hd)
     assert float(out[query].float().abs().max()) < 5.0          # key 41 is in query 40's future
     proj[query + 2, :hd] = 3.0
-    kernels.attention_prefill_simt(proj, out, seq_start, past, 1, n, 1, 1, hd, 1.0, k_offset=hd, v_offset=2 * hd)
+    kernels.attention_prefill(proj, out, seq_start, past, 1, n, 1, 1, hd, 1.0, k_offset=hd, v_offset=2 * hd)
     assert float(out[query + 2].float().min()) > 60.0           # and in query 42's past
 
 
