@@ -1,13 +1,15 @@
 // Matrix products for steps with many rows (prefill), bfloat16 operands, 32-bit accumulation, on the
 // fifth-generation tensor cores:  out[M,N] = act(A[M,K] @ W[N,K]^T + bias) (+ residual).
 //
-// One block computes a 128 x BN tile of the output.  Its six warps have fixed jobs:
+// A block computes 128 x BN tiles of the output, one after another (one block per SM).  Its six warps have fixed jobs:
 //   warp 0    asks the tensor memory accelerator (TMA) for the next 128 x 64 tile of A and BN x 64 tile of W
 //             (cp.async.bulk.tensor, 128-byte swizzle) into a ring of shared-memory stages;
 //   warp 1    one elected thread issues tcgen05.mma (M = 128, N = BN, K = 16, four per stage) whose accumulator
 //             lives in tensor memory (TMEM), and commits each stage back to the producer when it has been read;
-//   warps 2-5 wait for the last commit, read the accumulator with tcgen05.ld (a warp reaches the 32 TMEM lanes of
-//             its quarter), add the bias, apply GELU, add the 32-bit residual and store 32-bit or bfloat16 rows.
+//   warps 2-5 wait for a tile's last commit, read the accumulator with tcgen05.ld (a warp reaches the 32 TMEM lanes
+//             of its quarter), turn it through shared memory so that a warp writes whole row segments, add the bias,
+//             apply GELU, add the 32-bit residual and store 32-bit or bfloat16.  There are two accumulators, so
+//             this runs while the next tile's products are already being issued.
 // Both operands are K-major (K contiguous): A as the activations are stored, W as [N, K].
 // Stages hand over through mbarriers; every wait is bounded, and a wait that runs out marks the call as failed
 // (status word) instead of hanging: the block still frees its tensor memory and returns.
@@ -86,18 +88,53 @@ __device__ __forceinline__ void tc_ld16(unsigned taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// Shared memory: STAGES x (A tile 128 x 64, W tile BN x 64), each tile 1024-byte aligned.
+__device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+      "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// GELU of the epilogue.  When the result is rounded to bfloat16 anyway, the tanh form uses the hardware's tanh
+// (relative error about 2^-11, below that rounding); a 32-bit result gets the full-precision functions.
+__device__ __forceinline__ float tc_activation(float x, int act, bool exact) {
+  if (exact) return apply_activation(x, act);
+  if (act == kActGeluTanh) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;\n" : "=f"(t) : "f"(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    return 0.5f * x * (1.f + t);
+  }
+  if (act == kActGeluErf) return gelu_erf(x);
+  return x;
+}
+__device__ __forceinline__ void tc_bar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc_smem(bar)) : "memory");
+}
+
+// Persistent: a block walks over output tiles (tile, tile + grid, ...).  The accumulator is double-buffered in
+// tensor memory (2 x BN columns), so the epilogue of one tile runs while the products of the next are issued.
+// Shared memory: STAGES x (A tile 128 x 64, W tile BN x 64), each tile 1024-byte aligned, then a 32 x 33 float
+// patch per epilogue warp through which accumulator rows are turned into coalesced global rows.
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, TcParams p) {
   extern __shared__ unsigned char tc_smem_raw[];
-  __shared__ __align__(8) unsigned long long full[STAGES], empty[STAGES], acc_ready;
+  __shared__ __align__(8) unsigned long long full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
   __shared__ unsigned tmem_base;
   __shared__ int failed;
   constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2;
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<unsigned long long>(tc_smem_raw) + 1023ull) & ~1023ull);
+  float* patches = reinterpret_cast<float*>(tiles + (size_t)STAGES * (A_BYTES + W_BYTES));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+  const int tiles_m = (p.M + TC_BM - 1) / TC_BM, tiles_n = (p.N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + TC_BK - 1) / TC_BK;
 
   if (threadIdx.x == 0) {
@@ -105,13 +142,16 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       tc_bar_init(&full[s], 1);
       tc_bar_init(&empty[s], 1);
     }
-    tc_bar_init(&acc_ready, 1);
+    for (int b = 0; b < 2; ++b) {
+      tc_bar_init(&acc_full[b], 1);
+      tc_bar_init(&acc_empty[b], 4);       // one arrival per epilogue warp
+    }
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
-    // the accumulator: BN 32-bit columns of tensor memory (a power of two of at least 32)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(&tmem_base)), "r"(BN) : "memory");
+    // two accumulators of BN 32-bit columns each (the count is a power of two of at least 32)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(&tmem_base)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -121,111 +161,123 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % STAGES;
-        if (kb >= STAGES && !tc_bar_wait(&empty[s], ((kb / STAGES) - 1) & 1)) {
-          failed = 1;
-          break;
+      int it = 0;                          // k-blocks loaded so far, over all tiles
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !tc_bar_wait(&empty[s], ((it / STAGES) - 1) & 1)) {
+            failed = 1;
+            tile = n_tiles;
+            break;
+          }
+          tc_bar_expect(&full[s], A_BYTES + W_BYTES);
+          unsigned char* a_tile = tiles + (size_t)s * (A_BYTES + W_BYTES);
+          tc_tma_load(a_tile, &map_a, kb * TC_BK, m0, &full[s]);
+          tc_tma_load(a_tile + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
         }
-        tc_bar_expect(&full[s], A_BYTES + W_BYTES);
-        unsigned char* a_tile = tiles + (size_t)s * (A_BYTES + W_BYTES);
-        tc_tma_load(a_tile, &map_a, kb * TC_BK, m0, &full[s]);
-        tc_tma_load(a_tile + A_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // instruction descriptor: 32-bit accumulator, bfloat16 operands, both K-major, N = BN, M = 128
       const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
+      int it = 0, local = 0;
       bool ok = true;
-      for (int kb = 0; kb < k_blocks && ok; ++kb) {
-        const int s = kb % STAGES;
-        if (!tc_bar_wait(&full[s], (kb / STAGES) & 1)) {
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        // the epilogue must have emptied this accumulator (it was last used two tiles ago)
+        if (local >= 2 && !tc_bar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1)) {
           failed = 1;
-          ok = false;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        unsigned char* a_tile = tiles + (size_t)s * (A_BYTES + W_BYTES);
-        const unsigned long long da = tc_desc(a_tile), dw = tc_desc(a_tile + A_BYTES);
+        const unsigned d_tmem = tmem_acc + (unsigned)(buf * BN);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!tc_bar_wait(&full[s], (it / STAGES) & 1)) {
+            failed = 1;
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          unsigned char* a_tile = tiles + (size_t)s * (A_BYTES + W_BYTES);
+          const unsigned long long da = tc_desc(a_tile), dw = tc_desc(a_tile + A_BYTES);
 #pragma unroll
-        for (int k = 0; k < TC_BK / 16; ++k)   // 16 bfloat16 = 32 bytes further along the row: +2 in 16-byte units
-          tc_mma(tmem_acc, da + 2ull * k, dw + 2ull * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-        tc_commit(&empty[s]);                  // arrives when these products have read the stage
+          for (int k = 0; k < TC_BK / 16; ++k)   // 16 bfloat16 = 32 bytes further along the row: +2 in 16-byte units
+            tc_mma(d_tmem, da + 2ull * k, dw + 2ull * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&empty[s]);                  // arrives when these products have read the stage
+        }
+        tc_commit(&acc_full[buf]);               // arrives when every product issued so far has finished
       }
-      tc_commit(&acc_ready);                   // arrives when every product issued so far has finished
     }
   } else {
     // epilogue: warp w reaches TMEM lanes 32 * (w % 4) .. + 31, i.e. the tile's rows of that quarter
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
-    const bool ok = tc_bar_wait(&acc_ready, 0);
-    if (!ok) failed = 1;
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    if (ok) {
+    float* patch = patches + (size_t)(warp - 2) * (32 * 33);
+    int local = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+      const bool ok = tc_bar_wait(&acc_full[buf], (local >> 1) & 1);
+      if (!ok) {
+        failed = 1;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const int row_base = m0 + quarter * 32;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float v[16];
-        tc_ld16(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, v);
-        if (row < p.M) {
-          const long long o = (long long)row * p.N + n0 + c0;
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        tc_ld32(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + c0), v);
+        __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int col = n0 + c0 + i;
-            if (col < p.N) {
-              float x = v[i];
-              if (p.bias) x += p.bias[col];
-              x = apply_activation(x, p.act);
-              if (p.residual) x += p.residual[o + i];
-              v[i] = x;
-            }
-          }
-          if (n0 + c0 + 16 <= p.N && (p.N & 7) == 0) {
-            if (p.out_is_f32) {
-              float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            } else {
-              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o);
-#pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                __nv_bfloat162 h[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
-                dst[i] = *reinterpret_cast<uint4*>(h);
-              }
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (n0 + c0 + i < p.N) {
-                if (p.out_is_f32)
-                  reinterpret_cast<float*>(p.out)[o + i] = v[i];
-                else
-                  reinterpret_cast<__nv_bfloat16*>(p.out)[o + i] = __float2bfloat16_rn(v[i]);
-              }
+        for (int i = 0; i < 32; ++i) patch[lane * 33 + i] = v[i];    // row `lane` of the chunk
+        __syncwarp();
+        const int col = n0 + c0 + lane;                              // now: one column per lane, rows in turn
+        if (col < p.N) {
+          const float bias = p.bias ? p.bias[col] : 0.f;
+          const int rows = min(32, p.M - row_base);
+          for (int r = 0; r < rows; ++r) {
+            float x = patch[r * 33 + lane] + bias;
+            x = tc_activation(x, p.act, p.out_is_f32 != 0);
+            const long long o = (long long)(row_base + r) * p.N + col;
+            if (p.residual) x += p.residual[o];
+            if (p.out_is_f32)
+              reinterpret_cast<float*>(p.out)[o] = x;
+            else
+              reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(x);
           }
         }
       }
+      // this warp has read its part of the accumulator: hand the buffer back to the issuer
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) tc_bar_arrive(&acc_empty[buf]);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_acc), "r"(BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_acc), "r"(2 * BN) : "memory");
   }
   if (threadIdx.x == 0 && failed && p.status) atomicExch(p.status, 2);
 }
 
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const TcParams& p, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+  constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 4 * 32 * 33 * sizeof(float);
   auto kern = linear_tcgen05_kernel<BN, STAGES>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  BT_CHECK(e == cudaSuccess, "linear_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-  dim3 grid((p.N + BN - 1) / BN, (p.M + TC_BM - 1) / TC_BM);
-  kern<<<grid, TC_THREADS, smem, stream>>>(ma, mw, p);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    BT_CHECK(e == cudaSuccess, "linear_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int n_tiles = ((p.N + BN - 1) / BN) * ((p.M + TC_BM - 1) / TC_BM);
+  const int blocks = n_tiles < 148 ? n_tiles : 148;     // one persistent block per SM
+  kern<<<blocks, TC_THREADS, smem, stream>>>(ma, mw, p);
   BT_LAUNCH_OK("linear_tcgen05");
   return 0;
 }
@@ -243,13 +295,15 @@ extern "C" int bt_linear_tcgen05(const void* a, const void* w, const float* bias
   BT_CHECK(bt_linear_tcgen05_supports(M, N, K), "linear_tcgen05: sizes M=%d N=%d K=%d are not supported", M, N, K);
   BT_CHECK(act >= 0 && act <= 2, "linear_tcgen05: unknown activation %d", act);
   BT_CHECK(!(residual && !out_is_f32), "linear_tcgen05: a residual needs a 32-bit output");
-  // narrow outputs take narrower tiles so that the grid still covers the GPU
-  const long long tiles128 = (long long)((M + TC_BM - 1) / TC_BM) * ((N + 127) / 128);
-  const int bn = (N <= 64 || tiles128 < 148) ? 64 : 128;
+  // wide tiles reuse every loaded row of A for more columns; narrow outputs take narrower tiles so that the
+  // grid still covers the GPU
+  const long long rows = (M + TC_BM - 1) / TC_BM;
+  const int bn = rows * ((N + 255) / 256) >= 90 ? 256 : (rows * ((N + 127) / 128) >= 90 ? 128 : 64);
   CUtensorMap ma, mw;
   if (int rc = tensor_map_2d_bf16(&ma, a, (unsigned long long)M, (unsigned long long)K, (unsigned long long)K, TC_BM)) return rc;
   if (int rc = tensor_map_2d_bf16(&mw, w, (unsigned long long)N, (unsigned long long)K, (unsigned long long)K, (unsigned)bn)) return rc;
   TcParams p{bias, residual, out, status, M, N, K, act, out_is_f32};
-  if (bn == 64) return launch_tc<64, 4>(ma, mw, p, stream);
-  return launch_tc<128, 3>(ma, mw, p, stream);   // 96 KB of stages: two blocks per SM, one computes while the other stores
+  if (bn == 64) return launch_tc<64, 6>(ma, mw, p, stream);
+  if (bn == 128) return launch_tc<128, 6>(ma, mw, p, stream);
+  return launch_tc<256, 4>(ma, mw, p, stream);
 }

@@ -50,6 +50,9 @@ class Engine:
         self.use_graphs = plan.graph_safe
         self.max_graph_batch = 256
         self._graphs: dict = {}
+        self._shape_seen: dict = {}        # how often a prefill shape has come by
+        self._shape_graphs: dict = {}      # shape -> StepGraph, the most recently used last
+        self.max_shape_graphs = 8
         self.h2d_bytes_last = 0
 
     # ---- construction ------------------------------------------------------------------
@@ -110,6 +113,33 @@ class Engine:
             self._graphs[key] = DecodeGraph(self, n, selection)
         return self._graphs[key]
 
+    def _shape_step(self, entries: list[StepEntry]):
+        """A step that is not one token per sequence.  A shape met for the second time is recorded as a CUDA graph
+        and replayed from then on; the eight most recently used shapes are kept."""
+        news = [len(e.tokens) for e in entries]
+        shape = (sum(news), len(entries), max(news), sum(len(e.want) for e in entries),
+                 all(self.cache.length(e.slot) == 0 for e in entries))
+        if self.use_graphs:
+            recorded = self._shape_graphs.pop(shape, None)
+            seen = self._shape_seen.get(shape, 0)
+            self._shape_seen[shape] = seen + 1
+            if len(self._shape_seen) > 4096:
+                self._shape_seen.clear()
+            if recorded is None and seen >= 1:
+                from .graphs import StepGraph
+                recorded = StepGraph(self)
+                while len(self._shape_graphs) >= self.max_shape_graphs:
+                    self._shape_graphs.pop(next(iter(self._shape_graphs)))
+            if recorded is not None:
+                self._shape_graphs[shape] = recorded
+                logits = recorded.run(entries)
+                self.h2d_bytes_last = recorded.builder.h2d_bytes_last
+                return logits
+        self.ws.reset()
+        ctx = self.builder.build(entries)
+        self.h2d_bytes_last = self.builder.h2d_bytes_last
+        return self.plan.forward(ctx)
+
     def _graph_step(self, entries: list[StepEntry]):
         graph = self.decode_graph(len(entries))
         cache = self.cache
@@ -135,10 +165,7 @@ class Engine:
         if self.use_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
             logits = self._graph_step(entries)
         else:
-            self.ws.reset()
-            ctx = self.builder.build(entries)
-            self.h2d_bytes_last = self.builder.h2d_bytes_last
-            logits = self.plan.forward(ctx)
+            logits = self._shape_step(entries)
         for e in entries:
             self.cache.commit(e.slot, self.cache.length(e.slot) + len(e.tokens))
         self.steps_run += 1

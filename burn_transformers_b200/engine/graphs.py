@@ -142,6 +142,7 @@ class DecodeGraph:
             torch.cuda.current_stream().synchronize()
             keep = first.clone()
             self.ws.buffer = torch.empty(max(need, 2 * self.ws.buffer.numel()), dtype=torch.uint8, device=self.ws.device)
+            self.ws._typed.clear()
             self.ws._retired.clear()
             first = keep
         self.ws.frozen = True
@@ -153,6 +154,55 @@ class DecodeGraph:
         try:
             with torch.cuda.graph(graph):
                 self.logits = self._issue()
+        finally:
+            if was_enabled:
+                gc.enable()
+        self.graph = graph
+        return first
+
+
+class StepGraph:
+    """A recorded step of any shape: the kernels of steps that bring the same number of tokens, sequences and
+    wanted rows (and the same longest new run) are the same launches with the same arguments, only the integers
+    differ.  The engine records a shape when it meets it a second time and replays it afterwards, which takes
+    the per-launch cost of the host out of prompts that repeat a shape."""
+
+    def __init__(self, engine):
+        from .step import StepBuilder
+        self._engine = weakref.ref(engine)
+        self.builder = StepBuilder(engine.cache, engine.dtype, engine.device)
+        self.graph = None
+        self.logits = None
+        self.launches = 0
+
+    def run(self, entries):
+        engine = self._engine()
+        ws = self.builder.ws
+        ctx = self.builder.build(entries)          # packs and uploads the step's integers to fixed addresses
+        if self.graph is not None:
+            self.graph.replay()
+            return self.logits
+        ws.reset()
+        before = kernels.launch_count()
+        first = engine.plan.forward(ctx)
+        self.launches = kernels.launch_count() - before
+        need = ws.offset + (1 << 16)
+        if ws._retired or ws.buffer.numel() < need:
+            torch.cuda.current_stream().synchronize()
+            keep = None if first is None else first.clone()
+            ws.buffer = torch.empty(max(need, 2 * ws.buffer.numel()), dtype=torch.uint8, device=ws.device)
+            ws._typed.clear()
+            ws._retired.clear()
+            first = keep
+        ws.frozen = True
+        graph = torch.cuda.CUDAGraph()
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                ws.reset()
+                self.logits = engine.plan.forward(ctx)
         finally:
             if was_enabled:
                 gc.enable()

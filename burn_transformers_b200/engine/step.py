@@ -23,6 +23,7 @@ class Workspace:
     def __init__(self, device, initial_bytes: int = 1 << 20):
         self.device = torch.device(device)
         self.buffer = torch.empty(initial_bytes, dtype=torch.uint8, device=self.device)
+        self._typed: dict = {}     # flat views of the buffer per element type
         self.offset = 0
         self.frozen = False       # set while a CUDA graph is captured or replayed: addresses must not move
         self._retired: list[torch.Tensor] = []
@@ -31,11 +32,14 @@ class Workspace:
         self.offset = 0
         self._retired.clear()
 
+    _SIZES = {torch.float32: 4, torch.bfloat16: 2, torch.int32: 4, torch.float16: 2, torch.int64: 8, torch.uint8: 1}
+
     def take(self, shape, dtype) -> torch.Tensor:
         count = 1
         for s in shape:
             count *= int(s)
-        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        size = self._SIZES.get(dtype) or torch.empty((), dtype=dtype).element_size()
+        nbytes = count * size
         start = (self.offset + 255) & ~255
         if start + nbytes > self.buffer.numel():
             if self.frozen:
@@ -44,9 +48,16 @@ class Workspace:
             self._retired.append(self.buffer)
             self.buffer = torch.empty(max(2 * self.buffer.numel(), start + nbytes + (1 << 20)), dtype=torch.uint8,
                                       device=self.device)
+            self._typed.clear()
             start = 0
         self.offset = start + nbytes
-        return self.buffer[start:start + nbytes].view(dtype).view(*shape)
+        flat = self._typed.get(dtype)
+        if flat is None or flat.data_ptr() != self.buffer.data_ptr():
+            usable = self.buffer.numel() // size * size
+            flat = self.buffer[:usable].view(dtype)
+            self._typed[dtype] = flat
+        first = start // size
+        return flat[first:first + count].view(shape)
 
 
 class StepContext:

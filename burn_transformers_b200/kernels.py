@@ -57,19 +57,25 @@ def _ptr(t: torch.Tensor | None) -> c_void_p:
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
-    if not isinstance(t, torch.Tensor):
-        raise ShapeError(f"{name}: expected a tensor, found {type(t).__name__}")
-    if not t.is_cuda:
-        raise KernelError(f"{name}: lies on {t.device}; the kernels of this library run on a CUDA device only")
-    if not t.is_contiguous():
+    """Device, layout, element type and extents of one argument (None in `shape` leaves an extent free)."""
+    try:
+        ok = t.is_cuda and t.is_contiguous()
+    except AttributeError:
+        raise ShapeError(f"{name}: expected a tensor, found {type(t).__name__}") from None
+    if not ok:
+        if not t.is_cuda:
+            raise KernelError(f"{name}: lies on {t.device}; the kernels of this library run on a CUDA device only")
         raise ShapeError(f"{name}: must be contiguous")
-    if dtype is not None:
-        allowed = dtype if isinstance(dtype, (tuple, list)) else (dtype,)
-        if t.dtype not in allowed:
-            raise ShapeError(f"{name}: expected dtype {allowed}, found {t.dtype}")
+    if dtype is not None and t.dtype is not dtype:
+        if not isinstance(dtype, (tuple, list)) or t.dtype not in dtype:
+            raise ShapeError(f"{name}: expected dtype {dtype}, found {t.dtype}")
     if shape is not None:
-        if len(shape) != t.dim() or any(w is not None and w != g for w, g in zip(shape, t.shape)):
-            raise ShapeError(f"{name}: expected shape {list(shape)}, found {list(t.shape)}")
+        got = t.shape
+        if len(shape) != len(got):
+            raise ShapeError(f"{name}: expected shape {list(shape)}, found {list(got)}")
+        for want, have in zip(shape, got):
+            if want is not None and want != have:
+                raise ShapeError(f"{name}: expected shape {list(shape)}, found {list(got)}")
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -143,8 +149,7 @@ def linear_simt(a, w, bias, out, *, m=None, w_is_nk=False, activation=None, resi
 
 
 def linear_skinny_supports(m, n, k, w_is_nk, fuse_ln) -> bool:
-    return bool(library().bt_linear_skinny_supports(c_int(m), c_int(n), c_int(k), c_int(1 if w_is_nk else 0),
-                                                    c_int(1 if fuse_ln else 0)))
+    return _supports("bt_linear_skinny_supports", m, n, k, 1 if w_is_nk else 0, 1 if fuse_ln else 0)
 
 
 def linear_skinny(a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=None, norm=None, split=0):
@@ -186,8 +191,21 @@ def linear_skinny(a, w, bias, out, *, m, w_is_nk=False, activation=None, residua
                                       c_int(1 if out.dtype == torch.float32 else 0), c_int(split), _stream()))
 
 
+_SUPPORTS: dict = {}
+
+
+def _supports(name: str, *args) -> bool:
+    """Answers of the library's pure `..._supports` questions, remembered."""
+    key = (name, args)
+    hit = _SUPPORTS.get(key)
+    if hit is None:
+        hit = bool(getattr(library(), name)(*[c_int(int(a)) for a in args]))
+        _SUPPORTS[key] = hit
+    return hit
+
+
 def linear_tcgen05_supports(m, n, k) -> bool:
-    return bool(library().bt_linear_tcgen05_supports(c_int(m), c_int(n), c_int(k)))
+    return _supports("bt_linear_tcgen05_supports", m, n, k)
 
 
 def linear_tcgen05(a, w, bias, out, *, m, activation=None, residual=None):
@@ -211,7 +229,7 @@ def linear_tcgen05(a, w, bias, out, *, m, activation=None, residual=None):
 
 
 def linear_stream_supports(m, n, k, fuse_ln) -> bool:
-    return bool(library().bt_linear_stream_supports(c_int(m), c_int(n), c_int(k), c_int(1 if fuse_ln else 0)))
+    return _supports("bt_linear_stream_supports", m, n, k, 1 if fuse_ln else 0)
 
 
 def linear_stream(a, w, bias, out, *, m, activation=None, residual=None, norm=None, warps_k=0):
@@ -298,7 +316,7 @@ def attention_prefill(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads
     """Attention of several new tokens per sequence: on tensor cores for bfloat16 and the head sizes that kernel is
     built for, else with the plain 32-bit kernel.  Arguments as attention_prefill_simt."""
     lib = library()
-    if q_proj.dtype == torch.bfloat16 and lib.bt_attention_prefill_mma_supports(c_int(head_dim), c_int(PAGE_SIZE)):
+    if q_proj.dtype == torch.bfloat16 and _supports("bt_attention_prefill_mma_supports", head_dim, PAGE_SIZE):
         return _attention_prefill_call(lib.bt_attention_prefill_mma, False, q_proj, out, seq_start, past_len, n_seqs,
                                        max_new, n_heads, n_kv_heads, head_dim, scale, **kw)
     return attention_prefill_simt(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim,
