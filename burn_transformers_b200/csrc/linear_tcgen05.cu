@@ -238,15 +238,28 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (col < p.N) {
           const float bias = p.bias ? p.bias[col] : 0.f;
           const int rows = min(32, p.M - row_base);
-          for (int r = 0; r < rows; ++r) {
-            float x = patch[r * 33 + lane] + bias;
-            x = tc_activation(x, p.act, p.out_is_f32 != 0);
-            const long long o = (long long)(row_base + r) * p.N + col;
-            if (p.residual) x += p.residual[o];
-            if (p.out_is_f32)
-              reinterpret_cast<float*>(p.out)[o] = x;
-            else
-              reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(x);
+          const long long o0 = (long long)row_base * p.N + col;
+          if (p.residual) {
+            // all of the chunk's residual values first, so that their latencies overlap (the output may be the
+            // residual itself, which keeps the compiler from moving these loads above the stores on its own)
+            float res[32];
+#pragma unroll
+            for (int r = 0; r < 32; ++r) res[r] = r < rows ? p.residual[o0 + (long long)r * p.N] : 0.f;
+#pragma unroll
+            for (int r = 0; r < 32; ++r)
+              if (r < rows) {
+                const float x = tc_activation(patch[r * 33 + lane] + bias, p.act, true) + res[r];
+                reinterpret_cast<float*>(p.out)[o0 + (long long)r * p.N] = x;
+              }
+          } else {
+            for (int r = 0; r < rows; ++r) {
+              const float x = tc_activation(patch[r * 33 + lane] + bias, p.act, p.out_is_f32 != 0);
+              const long long o = o0 + (long long)r * p.N;
+              if (p.out_is_f32)
+                reinterpret_cast<float*>(p.out)[o] = x;
+              else
+                reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(x);
+            }
           }
         }
       }

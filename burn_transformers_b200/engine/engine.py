@@ -98,12 +98,13 @@ class Engine:
             if past + len(e.tokens) > self.cache_config.max_context:
                 raise CacheError(f"slot {e.slot}: {past} + {len(e.tokens)} tokens exceed the longest sequence of "
                                  f"{self.cache_config.max_context}")
-            for t in e.tokens:
-                if not (0 <= int(t) < vocab):
-                    raise ShapeError(f"slot {e.slot}: token id {t} is outside the vocabulary of {vocab}")
-            for w in e.want:
-                if not (0 <= int(w) < len(e.tokens)):
-                    raise ShapeError(f"slot {e.slot}: wanted place {w} is outside the {len(e.tokens)} tokens of the step")
+            lo, hi = min(e.tokens), max(e.tokens)
+            if lo < 0 or hi >= vocab:
+                bad = lo if lo < 0 else hi
+                raise ShapeError(f"slot {e.slot}: token id {bad} is outside the vocabulary of {vocab}")
+            if e.want and not (0 <= min(e.want) and max(e.want) < len(e.tokens)):
+                raise ShapeError(f"slot {e.slot}: wanted place {[w for w in e.want if not 0 <= w < len(e.tokens)][0]} "
+                                 f"is outside the {len(e.tokens)} tokens of the step")
 
     def decode_graph(self, n: int, selection: dict | None = None):
         """The recorded decode step for `n` sequences (with token selection when `selection` is given)."""

@@ -3,6 +3,7 @@ from __future__ import annotations
 
 import dataclasses
 
+import numpy as np
 import torch
 
 from ..errors import KernelError
@@ -101,44 +102,45 @@ class StepBuilder:
         n_seqs = len(entries)
         pasts = [cache.length(e.slot) for e in entries]
         news = [len(e.tokens) for e in entries]
-        tokens, positions, token_seq, seq_start, want_rows = [], [], [], [0], []
-        for i, e in enumerate(entries):
-            base = seq_start[-1]
-            tokens.extend(int(t) for t in e.tokens)
-            positions.extend(range(pasts[i], pasts[i] + news[i]))
-            token_seq.extend([i] * news[i])
-            want_rows.extend(base + int(w) for w in e.want)
-            seq_start.append(base + news[i])
+        seq_start = [0]
+        for n in news:
+            seq_start.append(seq_start[-1] + n)
+        n_tokens = seq_start[-1]
+        want_rows = [seq_start[i] + int(w) for i, e in enumerate(entries) for w in e.want]
         ctx_len = [p + n for p, n in zip(pasts, news)]
         slots = [e.slot for e in entries]
         width = cache.table_width
-        sections = [tokens, positions, token_seq, seq_start, pasts, ctx_len, slots, want_rows]
-        for g in range(len(cache.groups)):
-            flat = []
-            for e in entries:
-                row = cache.table_row(g, e.slot)
-                flat.extend(row)
-                flat.extend([0] * (width - len(row)))
-            sections.append(flat)
+        sizes = [n_tokens, n_tokens, n_tokens, n_seqs + 1, n_seqs, n_seqs, n_seqs, len(want_rows)]
+        sizes += [n_seqs * width] * len(cache.groups)
         offsets, total = [], 0
-        for s in sections:
+        for size in sizes:
             offsets.append(total)
-            total += _align4(max(1, len(s)))
+            total += _align4(max(1, size))
         if self._host is None or self._host.numel() < total:
             cap = max(total, 4096)
-            self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            self._host = torch.zeros(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            self._host_np = self._host.numpy()
             self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
-        flat_all = []
-        for off, s in zip(offsets, sections):
-            flat_all.extend([0] * (off - len(flat_all)))
-            flat_all.extend(s)
-        flat_all.extend([0] * (total - len(flat_all)))
-        self._host[:total] = torch.tensor(flat_all, dtype=torch.int32)
+        h = self._host_np
+        for i, e in enumerate(entries):
+            lo, hi = seq_start[i], seq_start[i + 1]
+            h[offsets[0] + lo:offsets[0] + hi] = e.tokens
+            h[offsets[1] + lo:offsets[1] + hi] = np.arange(pasts[i], pasts[i] + news[i], dtype=np.int32)
+            h[offsets[2] + lo:offsets[2] + hi] = i
+        for section, values in ((3, seq_start), (4, pasts), (5, ctx_len), (6, slots), (7, want_rows)):
+            h[offsets[section]:offsets[section] + len(values)] = values
+        for g in range(len(cache.groups)):
+            base = offsets[8 + g]
+            h[base:base + n_seqs * width] = 0
+            for i, e in enumerate(entries):
+                row = cache.table_row(g, e.slot)
+                h[base + i * width:base + i * width + len(row)] = row
         self._dev[:total].copy_(self._host[:total], non_blocking=True)
         self.h2d_bytes_last = total * 4
         dev = self._dev
-        view = lambda i: dev[offsets[i]:offsets[i] + max(1, len(sections[i]))]
+        view = lambda i: dev[offsets[i]:offsets[i] + max(1, sizes[i])]
         tables = [view(8 + g).view(n_seqs, width) for g in range(len(cache.groups))]
+        tokens = range(n_tokens)
         return StepContext(
             dtype=self.dtype, cache=cache, ws=self.ws, n_tokens=len(tokens), n_seqs=n_seqs, n_want=len(want_rows),
             max_new=max(news), is_decode=all(n == 1 for n in news), fresh=all(p == 0 for p in pasts),
