@@ -157,6 +157,8 @@ attention_decode_kernel(DecodeParams p) {
   auto issue_round = [&](int r) {
     const int pa = my_first + r * p.round_pages, pb = min(my_end, pa + p.round_pages);
     const unsigned bytes = (unsigned)(page_elems * sizeof(T));
+    // shared memory that ordinary instructions have just read is about to be overwritten by the copy engine
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     if (lane == 0) mbar_expect(&bar, 2u * bytes * (unsigned)(pb - pa));
     __syncwarp();
     for (int pg = pa + lane; pg < pb; pg += 32) {

@@ -48,6 +48,8 @@ class Engine:
         self.steps_run = 0
         # decode steps are replayed from CUDA graphs when every part is made of this library's kernels
         self.use_graphs = plan.graph_safe
+        # decode steps as one persistent kernel where the model's parts and the batch size have phases for it
+        self.use_fused_step = True
         self.max_graph_batch = 256
         self._graphs: dict = {}
         self._shape_seen: dict = {}        # how often a prefill shape has come by

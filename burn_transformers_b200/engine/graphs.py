@@ -109,8 +109,43 @@ class DecodeGraph:
             past_len=m.view("past_len"), ctx_len=m.view("ctx_len"), slots=m.view("slots"),
             want_rows=m.view("want_rows"), tables=[m.table(g) for g in range(len(cache.groups))])
         self.graph = None
+        self.program = None        # the fused step, where the model and the batch size allow it
         self.logits = None
         self.launches = 0          # kernels inside one replay
+
+    def _record_program(self):
+        """Records the step as the phase program of the fused decode kernel; None if something has no phase."""
+        from .program import DecodeProgram, ProgramUnsupported
+        engine = self._engine()
+        if engine.dtype != torch.bfloat16 or not getattr(engine, "use_fused_step", True):
+            return None
+        try:
+            program = DecodeProgram(engine.device, self.n)
+            self.ws.reset()
+            self.ctx.program = program
+            logits = engine.plan.forward(self.ctx)
+            if self.selection is not None:
+                program.add_sample(logits, self.meta, self.selection)
+            program.finalize()
+            self.logits = logits
+            return program
+        except ProgramUnsupported:
+            return None
+        finally:
+            self.ctx.program = None
+
+    def _settle(self, keep):
+        """Makes the workspace one buffer that holds a whole step with room to spare; `keep` (a result that lies in
+        it) is copied out first if the buffer has to move."""
+        ws = self.ws
+        need = ws.offset + (1 << 16)
+        if ws._retired or ws.buffer.numel() < need:
+            torch.cuda.current_stream().synchronize()
+            keep = None if keep is None else keep.clone()
+            ws.buffer = torch.empty(max(need, 2 * ws.buffer.numel()), dtype=torch.uint8, device=ws.device)
+            ws._typed.clear()
+            ws._retired.clear()
+        return keep
 
     def _issue(self):
         """Launches the step's kernels on the current stream (eagerly, or into a recording)."""
@@ -129,23 +164,28 @@ class DecodeGraph:
     def run(self) -> torch.Tensor:
         """Runs the step on what the device copy of the integers holds.  The first call runs the kernels directly
         and then records them; later calls replay the recording."""
+        if self.program is not None:
+            self.program.launch()
+            return self.logits
         if self.graph is not None:
             self.graph.replay()
             return self.logits
         before = kernels.launch_count()
         first = self._issue()
         self.launches = kernels.launch_count() - before
-        # the recording must find every piece of scratch at a fixed address: size the workspace for a whole
-        # step before recording, and let it grow no more
-        need = self.ws.offset + (1 << 16)
-        if self.ws._retired or self.ws.buffer.numel() < need:
-            torch.cuda.current_stream().synchronize()
-            keep = first.clone()
-            self.ws.buffer = torch.empty(max(need, 2 * self.ws.buffer.numel()), dtype=torch.uint8, device=self.ws.device)
-            self.ws._typed.clear()
-            self.ws._retired.clear()
-            first = keep
+        # a recording must find every piece of scratch at a fixed address: size the workspace for a whole step
+        # before recording, and let it grow no more
+        first = self._settle(first)
+        self.program = self._record_program()
+        if self.program is not None and self.ws._retired:
+            # the fused step needed more scratch than the separate kernels: make room, then record for good
+            first = self._settle(first)
+            self.program = self._record_program()
         self.ws.frozen = True
+        if self.program is not None:
+            self.launches = 2          # the clear of the barrier counter and the step itself
+            return first
+        first = self._settle(first)
         graph = torch.cuda.CUDAGraph()
         # nothing may free device or pinned memory while the stream records: keep the collector out
         gc.collect()

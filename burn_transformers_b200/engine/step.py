@@ -78,6 +78,7 @@ class StepContext:
         self.seq_start, self.past_len, self.ctx_len, self.slots = seq_start, past_len, ctx_len, slots
         self.want_rows = want_rows
         self.tables = tables            # per cache group: [n_seqs, table_width] page ids
+        self.program = None             # set while a fused decode step is recorded (engine.program.DecodeProgram)
         # the same facts as Python lists, for parts that plan on the host
         self.host_slots, self.host_seq_start, self.host_past_len = host_slots, host_seq_start, host_past_len
 

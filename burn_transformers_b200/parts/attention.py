@@ -75,6 +75,16 @@ class CausalSelfAttention(Mixer):
         if owns_cache and not ctx.is_decode:
             kernels.kv_append(proj, self.q_width, self.q_width + self.kv_width, ctx.positions, ctx.token_seq,
                               ctx.ctx_len, table, group.table_len, k_pool, v_pool, n, self.n_kv_heads, self.head_dim)
+        program = getattr(ctx, "program", None)
+        if program is not None and ctx.is_decode:
+            # recorded as a phase of the fused step; its partial results are merged by the output projection
+            mixed = program.add_attention(ctx, proj, k_pool, v_pool, table, group.table_len, n_heads=self.n_heads,
+                                          n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, scale=self.scale,
+                                          window=window,
+                                          new_kv_offsets=(self.q_width, self.q_width + self.kv_width) if owns_cache else None)
+            linear(ctx, mixed, self.t_out_weight, self.t_out_bias if self.has_bias else None, residual, m=n,
+                   residual=residual, w_is_nk=self.nk_out_weight)
+            return
         mixed = ctx.ws.take((n, self.q_width), dtype)
         if ctx.is_decode:
             kernels.attention_decode(proj, mixed, k_pool, v_pool, table, group.table_len, ctx.ctx_len, ctx.n_seqs,

@@ -20,6 +20,10 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx, positions_part, out32):
         table = positions_part.t_weight if getattr(positions_part, "adds_to_embedding", False) else None
+        program = getattr(ctx, "program", None)
+        if program is not None:
+            program.add_embed(ctx.tokens, ctx.positions if table is not None else None, self.t_weight, table, out32)
+            return
         kernels.embed(ctx.tokens, ctx.positions, self.t_weight, table, out32, status=None)
 
 

@@ -25,6 +25,10 @@ def linear(ctx, a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=
     32-bit operands always take the plain fused-multiply-add kernel: the 32-bit path has no reduced-precision
     matrix mode.  bfloat16 products of at most 64 rows take a weight-streaming kernel, which can also normalise
     its rows on the way in; with more rows (and [N, K] weights) they run on the tcgen05 tensor cores."""
+    program = getattr(ctx, "program", None)
+    if program is not None:      # a fused decode step is being recorded: this product becomes one of its phases
+        program.add_linear(a, w, bias, out, m=m, w_is_nk=w_is_nk, activation=activation, residual=residual)
+        return
     lazy = isinstance(a, LazyNorm)
     n = w.shape[0] if w_is_nk else w.shape[1]
     k = w.shape[1] if w_is_nk else w.shape[0]

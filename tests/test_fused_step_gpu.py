@@ -1,0 +1,134 @@
+"""The fused decode step (one persistent kernel for a whole step) at head sizes, batch sizes and context lengths
+that the tiny configurations of the other tests do not reach: against the plain implementation, and its token
+selection against the selection kernel on the step's own logits."""
+import numpy as np
+import pytest
+import torch
+
+import engine_replay as replay
+import plain_gpt2 as plain
+import burn_transformers_b200 as bt
+from burn_transformers_b200 import Engine, StepEntry, kernels
+from burn_transformers_b200.engine import program as step_program
+from burn_transformers_b200.engine.graphs import DecodeSession
+from burn_transformers_b200.sampling.sampler import DeviceSampler
+from burn_transformers_b200.sampling.tracker import SequenceTracker
+from tiny_configs import make_folder, random_prompts
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16 = 3e-2        # as in test_model_gpu.py: against the plain implementation that rounds where the engine does
+
+# head sizes 64, 96 and 128 (two, three and four 32-wide blocks of a head), widths that are no power of two
+FUSED_CONFIGS = {
+    "h64": dict(model_type="gpt2", n_layer=2, n_embd=192, n_head=3, n_inner=320, vocab_size=1003, n_positions=704,
+                layer_norm_epsilon=1e-5, activation_function="gelu_new"),
+    "h96": dict(model_type="gpt2", n_layer=2, n_embd=192, n_head=2, n_inner=256, vocab_size=777, n_positions=704,
+                layer_norm_epsilon=2e-5, activation_function="gelu", scale_attn_by_inverse_layer_idx=True),
+    "h128": dict(model_type="gpt2", n_layer=1, n_embd=256, n_head=2, n_inner=512, vocab_size=520, n_positions=704,
+                 layer_norm_epsilon=1e-5, activation_function="gelu_new"),
+}
+LENGTHS = [40, 130, 333, 700]
+
+
+@pytest.fixture(scope="module", params=sorted(FUSED_CONFIGS))
+def case(request, tmp_path_factory):
+    cfg = FUSED_CONFIGS[request.param]
+    folder = make_folder(tmp_path_factory.mktemp(f"fused_{request.param}"), cfg, seed=3, storage="bfloat16", loud=False)
+    pcfg, pw = plain.load_model(folder)
+    seqs = random_prompts(cfg, LENGTHS, seed=9)
+    rounded = {k: (plain.round_to_bf16(v) if v.ndim == 2 else v) for k, v in pw.items()}
+    ref = [plain.logits(pcfg, rounded, s, quant=plain.round_to_bf16) for s in seqs]
+    return cfg, folder, seqs, ref
+
+
+def fused_programs(engine):
+    return [g.program for g in engine._graphs.values() if g.program is not None]
+
+
+@pytest.mark.parametrize("splits", [None, 1, 3])
+def test_decoding_one_by_one_through_the_fused_step(case, splits, monkeypatch):
+    """The last 32 tokens of every request come one at a time: each is one fused step with one sequence.  With one
+    split a block takes all pages of a head, more than its ring of page slots holds at once for the long
+    requests."""
+    cfg, folder, seqs, ref = case
+    monkeypatch.setattr(step_program, "SPLITS_OVERRIDE", splits)
+    engine = Engine.from_folder(folder, "bfloat16", max_tokens=64 * 12)
+    got = replay.tail_one_by_one(engine, seqs)
+    assert fused_programs(engine), "the decode steps did not run as a fused step"
+    err, where = replay.worst_error(got, ref)
+    assert err < TOL_BF16, f"fused tail: {err:.3e} at {where}"
+
+
+def test_batches_through_the_fused_step(case):
+    """Unequal requests decode together (each prompt cut to a third): the steps bring one token per sequence and
+    the shorter requests end earlier, so several batch sizes run as fused steps."""
+    cfg, folder, seqs, ref = case
+    engine = Engine.from_folder(folder, "bfloat16", max_tokens=64 * 24)
+    short = [s[:160] for s in seqs] + [s[5:90] for s in seqs]
+    pcfg, pw = plain.load_model(folder)
+    rounded = {k: (plain.round_to_bf16(v) if v.ndim == 2 else v) for k, v in pw.items()}
+    refs = [plain.logits(pcfg, rounded, s, quant=plain.round_to_bf16) for s in short]
+    groups = [list(range(len(short)))]
+    got = replay.batches(engine, short, groups, [max(1, len(s) // 3) for s in short])
+    assert len(fused_programs(engine)) >= 2
+    err, where = replay.worst_error(got, refs)
+    assert err < TOL_BF16, f"fused batches: {err:.3e} at {where}"
+
+
+@pytest.mark.parametrize("mode", ["greedy", "sample"])
+@pytest.mark.parametrize("batch", [1, 5, 16])
+def test_selection_inside_the_fused_step(case, mode, batch):
+    """The step's ids and log-probabilities are what the selection kernel gives on the step's own logits, and the
+    step moves every sequence on by one token."""
+    cfg, folder, seqs, _ = case
+    config = bt.GenerationConfig(max_new_tokens=8, strategy=mode, temperature=0.8, top_k=50, top_p=0.9, seed=4)
+    engine = Engine.from_folder(folder, "bfloat16", max_tokens=64 * 12 * 16, max_slots=16)
+    vocab = cfg["vocab_size"]
+    prompts = random_prompts(cfg, [17 + 37 * i for i in range(batch)], seed=2)
+    sampler = DeviceSampler(config, vocab, engine.device, batch)
+    trackers = [SequenceTracker(i, p, config) for i, p in enumerate(prompts)]
+    slots = {i: engine.new_sequence() for i in range(batch)}
+    logits = engine.step([StepEntry(slots[i], p, [len(p) - 1]) for i, p in enumerate(prompts)])
+    ids, lps = sampler.select(logits, trackers)
+    for t, a, b in zip(trackers, ids, lps):
+        t.push(a, b)
+    engine.cache.reserve([(slots[i], len(prompts[i]) + 8) for i in range(batch)])
+    session = DecodeSession(engine, config, batch)
+    graph = session._compose(trackers, slots)
+    for step in range(4):
+        meta = graph.meta
+        before = {name: meta.view(name)[:batch].clone() for name in ("tokens", "positions", "past_len", "ctx_len", "counters")}
+        step_logits = graph.run()          # (the first run is made of separate kernels; the recording serves the later ones)
+        assert graph.program is not None, "the session's step does not run as a fused step"
+        torch.cuda.synchronize()
+        out_ids = meta.out[:batch].clone()
+        out_lp = meta.out[batch:2 * batch].view(torch.float32).clone()
+        want = torch.zeros(2 * batch, dtype=torch.int32, device=engine.device)
+        s = session.selection
+        kernels.sample(step_logits, batch, do_sample=s["do_sample"], temperature=s["temperature"], top_k=s["top_k"],
+                       top_p=s["top_p"], min_p=s["min_p"], stream_seeds=meta.seeds if s["do_sample"] else None,
+                       counters=before["counters"] if s["do_sample"] else None, out_ids=want[:batch],
+                       out_logp=want[batch:].view(torch.float32))
+        torch.cuda.synchronize()
+        assert out_ids.tolist() == want[:batch].tolist(), f"step {step}"
+        np.testing.assert_allclose(out_lp.cpu().numpy(), want[batch:].view(torch.float32).cpu().numpy(), rtol=0, atol=2e-5)
+        assert meta.view("tokens")[:batch].tolist() == out_ids.tolist()
+        for name in ("positions", "past_len", "ctx_len", "counters"):
+            assert meta.view(name)[:batch].tolist() == (before[name] + 1).tolist(), name
+        for i in range(batch):     # the host's view of the cache follows, as the session does after reading a step
+            engine.cache.commit(slots[i], engine.cache.length(slots[i]) + 1)
+
+
+def test_fused_and_separate_kernels_agree(case):
+    """The same decode steps with the fused step switched off give the same logits beyond bfloat16 rounding."""
+    cfg, folder, seqs, ref = case
+    fused = Engine.from_folder(folder, "bfloat16", max_tokens=64 * 12)
+    plain_path = Engine.from_folder(folder, "bfloat16", max_tokens=64 * 12)
+    plain_path.use_fused_step = False
+    a = replay.tail_one_by_one(fused, seqs[1:3], tail=8)
+    b = replay.tail_one_by_one(plain_path, seqs[1:3], tail=8)
+    assert fused_programs(fused) and not fused_programs(plain_path)
+    scale = max(float(np.abs(r).max()) for r in ref)
+    drift = max(float(np.abs(a[k] - b[k]).max()) for k in a) / scale
+    assert drift < TOL_BF16
