@@ -179,6 +179,8 @@ def run_ours(args):
     with tempfile.TemporaryDirectory() as folder:
         bt.write_random_model(folder, cfg, seed=0, storage="bfloat16")
         engine = bt.Engine.from_folder(folder, "bfloat16", max_tokens=64 * CONTEXT, max_slots=64)
+    if args.separate_kernels:
+        engine.use_fused_step = False
     before_all = kernels.launch_count()
     if args.only == "decode":
         ms, launches, mean_ctx = decode_points(engine, cfg, args.batch, prompt_len, steps, warmup, torch, bt, rng)
@@ -255,6 +257,8 @@ def main() -> int:
     parser.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                         help="for profiling: run only the decode steps (at --batch) or only the prefill")
     parser.add_argument("--batch", type=int, default=8, help="batch of the decode steps under --only decode")
+    parser.add_argument("--separate-kernels", action="store_true",
+                        help="decode steps as a CUDA graph of separate kernels instead of the fused decode step")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate (Cargo.toml only): pip "
