@@ -8,6 +8,11 @@ const char* bt_last_error();
 int bt_abi_version();
 long long bt_launch_count();
 
+// Fills `out` (128 bytes) with a tensor map of a rows x cols bfloat16 tensor (rows `row_stride` elements apart)
+// that is copied in boxes of box_rows x 64 columns with the 128-byte swizzle.
+int bt_tensor_map_2d_bf16(void* out, const void* base, unsigned long long rows, unsigned long long cols,
+                          unsigned long long row_stride, unsigned box_rows);
+
 int bt_embed(const int* tokens, const int* positions, const void* wte, const void* wpe, float* out, int n_tokens,
              int width, int vocab, int n_positions, int dtype, int* status, cudaStream_t stream);
 

@@ -19,6 +19,7 @@
 // results.  Nothing is accumulated with atomics: results do not depend on timing.
 #include "common.cuh"
 #include "sampling.cuh"
+#include "tma.cuh"
 
 namespace bt {
 
@@ -90,7 +91,11 @@ struct Phase {
   int n_partials;
   int pad0_;
   long long pad1_;
+  // ---- attention: tensor maps of the layer's key and value pools, seen as [pages * kv_heads * 64 rows][head_dim] ----
+  alignas(64) CUtensorMap k_map;
+  CUtensorMap v_map;
 };
+static_assert(sizeof(Phase) % 64 == 0, "tensor maps in an array of phases stay on 64-byte boundaries");
 
 __device__ __forceinline__ unsigned ds_ld_acquire(const unsigned* p) {
   unsigned v;
@@ -141,11 +146,9 @@ struct StepShared {
   int ok;                          // result of the last bounded wait
   float red[DS_WARPS][4][32][4];   // partial sums of the warps, per tile of a group
   float stats[16][2];
-  float ml[DS_WARPS][2];
-  float w8[DS_WARPS];
-  float blk_ml[2];
+  float ml[2][DS_WARPS][2];
   SampleShared sample;
-  alignas(16) Phase phase[2];
+  alignas(64) Phase phase[2];
   AttnWork work;
   // lengths and page tables of the step's sequences (the same in every layer of a cache group), read once
   const int* ctx_src;
@@ -677,13 +680,22 @@ __device__ void ds_linear_phase(const Phase& ph, unsigned char* smem, StepShared
 // the first ones before the grid barrier), every slot with a completion barrier of its own; a warp takes chunks
 // of 8 T keys of a landed page by itself, so nothing is synchronised inside a page.  The block's warps (and,
 // with splits, its blocks) are merged afterwards.
+// A page slot holds the page's keys, then its values, each as ceil(head_dim / 64) tiles of 64 rows x 128 bytes
+// in the tensor memory accelerator's 128-byte swizzle: the 16-byte chunk c of row r lies at chunk c ^ (r & 7).
+__device__ __host__ __forceinline__ int ds_col_blocks(int head_dim) { return (head_dim + 63) / 64; }
+__device__ __host__ __forceinline__ int ds_slot_bytes(int head_dim) { return 2 * ds_col_blocks(head_dim) * DS_PAGE * 128; }
 __device__ __host__ __forceinline__ int ds_attn_slots(int head_dim) {
-  const int fit = DS_SLOT_BYTES_TOTAL / (2 * DS_PAGE * head_dim * 2);
-  return fit < 1 ? 1 : (fit > DS_MAX_SLOTS ? DS_MAX_SLOTS : fit);
+  const int fit = DS_SLOT_BYTES_TOTAL / ds_slot_bytes(head_dim);
+  int slots = 1;                      // a power of two
+  while (2 * slots <= fit && 2 * slots <= DS_MAX_SLOTS) slots *= 2;
+  return slots;
 }
 __device__ __host__ __forceinline__ long long ds_attn_smem(int head_dim) {
-  return 2ll * ds_attn_slots(head_dim) * DS_PAGE * head_dim * 2 + (long long)DS_WARPS * head_dim * 4 +
-         (long long)DS_MAX_ITEMS * 3 * head_dim * 2;      // page slots, the warps' results, the items' new rows
+  return 1024 + (long long)ds_attn_slots(head_dim) * ds_slot_bytes(head_dim) + 2ll * DS_WARPS * head_dim * 4 +
+         (long long)DS_MAX_ITEMS * 3 * head_dim * 2;      // alignment, page slots, the warps' results, the items' new rows
+}
+__device__ __forceinline__ unsigned char* ds_ring_base(unsigned char* smem) {
+  return smem + ((1024u - (ds_smem(smem) & 1023u)) & 1023u);      // the swizzle pattern repeats every 1024 bytes
 }
 
 // Work items are (sequence, head, split); a split owns a run of pages.
@@ -758,13 +770,14 @@ __device__ void ds_attn_plan(const Phase& ph, StepShared& sh) {
 }
 
 // Warp 0 asks for the pages [ka, kb) of the block's stream, at most 32 of them: each lane looks one page up and
-// issues its two copies.  Pages are numbered through the whole launch (`base` is the number of the phase's first
-// page): number n lies in slot n % slots, and its completion is phase (n / slots) & 1 of that slot's barrier.
-__device__ __forceinline__ void ds_issue_stream(const Phase& ph, int ka, int kb, unsigned base, unsigned char* smem, StepShared& sh) {
+// issues its copies (a 64 x 64 box per tile).  Pages are numbered through the whole launch (`base` is the number of
+// the phase's first page): number n lies in slot n % slots, and its completion is phase (n / slots) & 1 of that
+// slot's barrier.  `maps`: the phase in global memory (tensor maps are read from there).
+__device__ __forceinline__ void ds_issue_stream(const Phase& ph, const Phase* maps, int ka, int kb, unsigned base,
+                                               unsigned char* ring, StepShared& sh) {
   const int lane = threadIdx.x & 31;
-  const int page_elems = DS_PAGE * ph.head_dim;
-  const unsigned bytes = (unsigned)(page_elems * 2);
-  const unsigned slots = (unsigned)ds_attn_slots(ph.head_dim);
+  const int cbs = ds_col_blocks(ph.head_dim);
+  const unsigned slots = (unsigned)ds_attn_slots(ph.head_dim), slot_bytes = (unsigned)ds_slot_bytes(ph.head_dim);
   // the shared memory may just have been read or written by ordinary instructions: order them before the copies
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   const int k = ka + lane;
@@ -775,18 +788,21 @@ __device__ __forceinline__ void ds_issue_stream(const Phase& ph, int ka, int kb,
     const int pg = it.pg_first + (k - sh.work.start[j]);
     const int kv_head = it.head / (ph.n_heads / ph.n_kv_heads);
     const unsigned slot = (base + (unsigned)k) % slots;
-    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem) + (size_t)slot * 2 * page_elems;
+    unsigned char* dst = ring + (size_t)slot * slot_bytes;
     const unsigned bar = ds_smem(&sh.bars[slot]);
-    const long long page = ds_table_entry(ph, sh, it.seq, pg % ph.table_len);
-    const long long off = (page * ph.n_kv_heads + kv_head) * (long long)page_elems;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(2u * bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(ds_smem(Ks)),
-                 "l"(ph.k_pool + off), "r"(bytes), "r"(bar)
-                 : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
-                     ds_smem(Ks + page_elems)),
-                 "l"(ph.v_pool + off), "r"(bytes), "r"(bar)
-                 : "memory");
+    const int page = ds_table_entry(ph, sh, it.seq, pg % ph.table_len);
+    const int row = (page * ph.n_kv_heads + kv_head) * DS_PAGE;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(slot_bytes) : "memory");
+    for (int cb = 0; cb < cbs; ++cb) {
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                       ds_smem(dst + cb * DS_PAGE * 128)),
+                   "l"(&maps->k_map), "r"(cb * 64), "r"(row), "r"(bar)
+                   : "memory");
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                       ds_smem(dst + (cbs + cb) * DS_PAGE * 128)),
+                   "l"(&maps->v_map), "r"(cb * 64), "r"(row), "r"(bar)
+                   : "memory");
+    }
   }
 }
 // Every lane of a warp waits (with a limit) until the slot's copies of this use have landed.
@@ -801,32 +817,27 @@ __device__ __forceinline__ bool ds_wait_slot(StepShared& sh, unsigned slot, unsi
   return false;
 }
 
-// A chunk's keys for this lane, from the page's slot: row g of each of the T tiles, 16 bytes of every 32-dim block.
-template <int I, int T>
-__device__ __forceinline__ void ds_attn_fetch_keys(int hd, int row0, const __nv_bfloat16* Ks, uint4 (&kb)[I * T]) {
-  const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-#pragma unroll
-  for (int t = 0; t < T; ++t) {
-    const __nv_bfloat16* krow = Ks + (row0 + 8 * t + g) * hd;
-#pragma unroll
-    for (int i = 0; i < I; ++i) {
-      const int d = 32 * i + 8 * q;
-      kb[t * I + i] = d < hd ? *reinterpret_cast<const uint4*>(krow + d) : make_uint4(0, 0, 0, 0);
-    }
-  }
+__device__ __forceinline__ void ds_ldmatrix_x4(unsigned (&r)[4], unsigned smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
 }
-__device__ __forceinline__ void ds_ldmatrix_x4_trans(unsigned (&r)[4], const void* smem_row) {
+__device__ __forceinline__ void ds_ldmatrix_x4_trans(unsigned (&r)[4], unsigned smem_addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(ds_smem(smem_row)));
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+// Shared-memory address of the 16-byte chunk `chunk` (8 dims) of row `row` of a page's keys or values.
+__device__ __forceinline__ unsigned ds_swizzled(unsigned tiles, int row, int chunk) {
+  return tiles + (unsigned)((chunk >> 3) * DS_PAGE * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-// One chunk of 8 T keys (rows row0.. of the page in Ks / Vs): scores, the running softmax (32-bit), the weighted
-// values.  The values' fragments are the page's 8 x 8 blocks read transposed from shared memory.
+// One chunk of 8 T keys (rows row0.. of the page whose keys lie at Ks and values at Vs, shared-memory addresses):
+// scores, the running softmax (32-bit), the weighted values.  `qa`: the query's fragments (row 0 of the tile),
+// two registers per 16 dims.
 template <int I, int T>
-__device__ __forceinline__ void ds_attn_chunk(const uint4 (&qa)[I], const uint4 (&kb)[I * T], const __nv_bfloat16* Vs, int hd, int row0,
-                                              int key0, int lo, int hi, float scale_log2, float& m, float& l,
-                                              float (&acc)[I * 4][4]) {
+__device__ __forceinline__ void ds_attn_chunk(const unsigned (&qa)[I * 4], unsigned Ks, unsigned Vs, int hd, int row0, int key0, int lo,
+                                              int hi, float scale_log2, float& m, float& l, float (&acc)[I * 4][4]) {
   const int lane = threadIdx.x & 31, q = lane & 3;
+  const int blk = lane >> 3, r = lane & 7;       // this lane gives the address of row r of block blk of a load of four
   float s[T][4];
 #pragma unroll
   for (int t = 0; t < T; ++t) {
@@ -834,8 +845,12 @@ __device__ __forceinline__ void ds_attn_chunk(const uint4 (&qa)[I], const uint4 
     for (int e = 0; e < 4; ++e) s[t][e] = 0.f;
 #pragma unroll
     for (int i = 0; i < I; ++i) {
-      ds_mma(s[t], qa[i].x, 0u, qa[i].y, 0u, kb[t * I + i].x, kb[t * I + i].y);
-      ds_mma(s[t], qa[i].z, 0u, qa[i].w, 0u, kb[t * I + i].z, kb[t * I + i].w);
+      if (32 * i < hd) {           // four chunks = 32 dims = two products
+        unsigned kf[4];
+        ds_ldmatrix_x4(kf, ds_swizzled(Ks, row0 + 8 * t + r, 4 * i + blk));
+        ds_mma(s[t], qa[4 * i], 0u, qa[4 * i + 1], 0u, kf[0], kf[1]);
+        ds_mma(s[t], qa[4 * i + 2], 0u, qa[4 * i + 3], 0u, kf[2], kf[3]);
+      }
     }
   }
   float mx = -INFINITY;
@@ -867,15 +882,14 @@ __device__ __forceinline__ void ds_attn_chunk(const uint4 (&qa)[I], const uint4 
     acc[n][0] *= corr;
     acc[n][1] *= corr;
   }
-  // lane L gives the address of row L % 8 of block L / 8 of a load of four blocks: keys 16 b (+ 8), dims 16 n (+ 8)
-  const int blk = lane >> 3, r = lane & 7;
+  // values: blocks (keys 16 b (+ 8), dims 16 n (+ 8)) read transposed
 #pragma unroll
   for (int b = 0; b < T / 2; ++b)
 #pragma unroll
     for (int n = 0; n < I * 2; ++n) {
       if (16 * n < hd) {
         unsigned v[4];
-        ds_ldmatrix_x4_trans(v, Vs + (row0 + 16 * b + (blk & 1) * 8 + r) * hd + 16 * n + (blk >> 1) * 8);
+        ds_ldmatrix_x4_trans(v, ds_swizzled(Vs, row0 + 16 * b + (blk & 1) * 8 + r, 2 * n + (blk >> 1)));
         ds_mma(acc[2 * n], pa[2 * b], 0u, pa[2 * b + 1], 0u, v[0], v[1]);
         ds_mma(acc[2 * n + 1], pa[2 * b], 0u, pa[2 * b + 1], 0u, v[2], v[3]);
       }
@@ -885,15 +899,16 @@ __device__ __forceinline__ void ds_attn_chunk(const uint4 (&qa)[I], const uint4 
 // `page_seq`: the number the next page to be asked for gets (see ds_issue_stream).
 // `asked`: how many pages of the block's stream were asked for before the grid barrier.
 template <int I, int T>
-__device__ bool ds_attention_items(const Phase& ph, unsigned char* smem, StepShared& sh, unsigned& page_seq, int asked) {
+__device__ bool ds_attention_items(const Phase& ph, const Phase* maps, unsigned char* smem, StepShared& sh, unsigned& page_seq,
+                                   int asked) {
   constexpr int CK = 8 * T, CPP = DS_PAGE / CK;       // keys of a chunk, chunks of a page
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, q = lane & 3;
   const int hd = ph.head_dim, page_elems = DS_PAGE * hd;
   const float scale_log2 = ph.scale_log2;
-  const int slots = ds_attn_slots(hd);
-  const __nv_bfloat16* ring = reinterpret_cast<const __nv_bfloat16*>(smem);                       // [slots][2][page]
-  float* s_acc = reinterpret_cast<float*>(smem + (size_t)slots * 2 * page_elems * 2);             // [DS_WARPS][hd]
-  __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(s_acc + DS_WARPS * hd);                  // [items][query, new key, new value][hd]
+  const int slots = ds_attn_slots(hd), slot_bytes = ds_slot_bytes(hd), cbs = ds_col_blocks(hd);
+  unsigned char* ring = ds_ring_base(smem);                                                       // [slots][keys | values][tile][64][128 B]
+  float* s_acc = reinterpret_cast<float*>(ring + (size_t)slots * slot_bytes);                     // [2][DS_WARPS][hd]
+  __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(s_acc + 2 * DS_WARPS * hd);                  // [items][query, new key, new value][hd]
   const int n_mine = sh.work.n, total = sh.work.start[n_mine];
   {
     // every item's query and new key and value come into shared memory while the pages travel
@@ -911,7 +926,7 @@ __device__ bool ds_attention_items(const Phase& ph, unsigned char* smem, StepSha
   page_seq += (unsigned)total;
   // pages travel in waves of as many as there are slots; the first wave may have been asked for already
   int wave_end = min(total, slots);
-  if (asked < wave_end && warp == 0) ds_issue_stream(ph, asked, wave_end, base, smem, sh);
+  if (asked < wave_end && warp == 0) ds_issue_stream(ph, maps, asked, wave_end, base, ring, sh);
   ds_cp_wait();
   __syncthreads();
   bool ok = true;
@@ -922,11 +937,11 @@ __device__ bool ds_attention_items(const Phase& ph, unsigned char* smem, StepSha
     const int kv_head = it.head / (ph.n_heads / ph.n_kv_heads);
     const int lo = max(it.lo, it.pg_first * DS_PAGE), hi = min(it.L, it.pg_end * DS_PAGE);
     // the query in the layout of the keys' loads; only row 0 of the tile (lanes with g = 0) is a query
-    uint4 qa[I];
+    unsigned qa[I * 4];          // per 16 dims: dims 2q, 2q + 1 and 8 + 2q, 9 + 2q
 #pragma unroll
-    for (int i = 0; i < I; ++i) {
-      const int d = 32 * i + 8 * q;
-      qa[i] = (g == 0 && d < hd) ? *reinterpret_cast<const uint4*>(my_rows + d) : make_uint4(0, 0, 0, 0);
+    for (int j = 0; j < I * 4; ++j) {
+      const int d = 16 * (j >> 1) + 8 * (j & 1) + 2 * q;
+      qa[j] = (g == 0 && d < hd) ? *reinterpret_cast<const unsigned*>(my_rows + d) : 0u;
     }
     if (ph.new_k && it.split == 0 && it.head == kv_head * (ph.n_heads / ph.n_kv_heads)) {
       // this block also files the new token's key and value in the sequence's page
@@ -946,100 +961,98 @@ __device__ bool ds_attention_items(const Phase& ph, unsigned char* smem, StepSha
     for (int n = 0; n < I * 4; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
-    for (int p = 0; p < n_pages; ++p) {
-      const int k = k0 + p;
-      if (k == wave_end) {       // (uniform in the block) everyone is done with the slots: the next wave can come
-        __syncthreads();
-        wave_end = min(total, k + slots);
-        if (warp == 0) ds_issue_stream(ph, k, wave_end, base, smem, sh);
+    // One chunk of the block's stream of chunks (CPP to a page), if it holds keys of this item's range.
+    auto take_chunk = [&](int c) {
+      const int k = c / CPP, h = c % CPP;
+      const int key0 = (it.pg_first + (k - k0)) * DS_PAGE + h * CK;
+      if (key0 >= hi || key0 + CK <= lo) return;
+      const unsigned n = base + (unsigned)k, slot = n & (unsigned)(slots - 1);
+      unsigned char* Kt = ring + (size_t)slot * slot_bytes;          // the page's key tiles; its value tiles follow
+      const unsigned Ks = ds_smem(Kt), Vs = Ks + (unsigned)(cbs * DS_PAGE * 128);
+      if (!ds_wait_slot(sh, slot, (n / (unsigned)slots) & 1u)) ok = false;
+      if (ph.new_k && it.L - 1 >= key0 && it.L - 1 < key0 + CK) {
+        // the newest key and value are not in their page yet (or only just): they come from the projections.
+        // (No other warp touches this chunk's rows; the rows beyond are masked and hold old, finite numbers.)
+        const int row = (it.L - 1) % DS_PAGE;
+        for (int ch = lane; ch < hd / 8; ch += 32) {
+          const unsigned off = (unsigned)((ch >> 3) * DS_PAGE * 128 + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
+          *reinterpret_cast<uint4*>(Kt + off) = *reinterpret_cast<const uint4*>(my_rows + hd + ch * 8);
+          *reinterpret_cast<uint4*>(Kt + cbs * DS_PAGE * 128 + off) = *reinterpret_cast<const uint4*>(my_rows + 2 * hd + ch * 8);
+        }
+        __syncwarp();
       }
-      const int pg = it.pg_first + p;
-      const unsigned n = base + (unsigned)k, slot = n % (unsigned)slots;
-      const __nv_bfloat16* Ks = ring + (size_t)slot * 2 * page_elems;
-      bool waited = false;
-      // the page's chunks go round the warps (counted through the block's stream, so that every warp gets some)
+      ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, scale_log2, m, l, acc);
+    };
+    // chunks go round the warps, counted through the block's stream so that every warp gets some
+    if (total <= slots) {          // (uniform in the block) all pages are on their way: a warp goes straight to its chunks
+      const int c_lo = k0 * CPP, c_hi = (k0 + n_pages) * CPP;
+      for (int c = c_lo + ((warp - c_lo) & (DS_WARPS - 1)); c < c_hi; c += DS_WARPS) take_chunk(c);
+    } else {
+      for (int p = 0; p < n_pages; ++p) {
+        const int k = k0 + p;
+        if (k == wave_end) {       // everyone is done with the slots: the next wave can come
+          __syncthreads();
+          wave_end = min(total, k + slots);
+          if (warp == 0) ds_issue_stream(ph, maps, k, wave_end, base, ring, sh);
+        }
 #pragma unroll 1
-      for (int h = 0; h < CPP; ++h) {
-        if ((k * CPP + h) % DS_WARPS != warp) continue;
-        const int key0 = pg * DS_PAGE + h * CK;
-        if (key0 >= hi || key0 + CK <= lo) continue;
-        if (!waited) {
-          if (!ds_wait_slot(sh, slot, (n / (unsigned)slots) & 1u)) ok = false;
-          waited = true;
-        }
-        __nv_bfloat16* Kw = const_cast<__nv_bfloat16*>(Ks);
-        if (ph.new_k && it.L - 1 >= key0 && it.L - 1 < key0 + CK) {
-          // the newest key and value are not in their page yet (or only just): they come from the projections.
-          // (No other warp touches this chunk's rows; the rows beyond are masked and hold old, finite numbers.)
-          const int row = (it.L - 1) % DS_PAGE;
-          for (int c = lane; c < hd / 8; c += 32) {
-            *reinterpret_cast<uint4*>(Kw + row * hd + c * 8) = *reinterpret_cast<const uint4*>(my_rows + hd + c * 8);
-            *reinterpret_cast<uint4*>(Kw + page_elems + row * hd + c * 8) = *reinterpret_cast<const uint4*>(my_rows + 2 * hd + c * 8);
-          }
-          __syncwarp();
-        }
-        uint4 kb[I * T];
-        ds_attn_fetch_keys<I, T>(hd, h * CK, Ks, kb);
-        ds_attn_chunk<I, T>(qa, kb, Ks + page_elems, hd, h * CK, key0, lo, hi, scale_log2, m, l, acc);
+        for (int h = 0; h < CPP; ++h)
+          if ((k * CPP + h) % DS_WARPS == warp) take_chunk(k * CPP + h);
       }
     }
     ds_stamp(sh, 2 + min(mine, 5));      // (when the item's chunks were done)
     // the four lanes of a row each summed their own keys' weights
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
-    // lane q of row 0 holds dims 8 n + 2 q + {0, 1} of value tile n
+    // lane q of row 0 holds dims 8 n + 2 q + {0, 1} of value tile n.  (Two sets of the warps' results, used in
+    // turn: the block-wide hand-over of the next item orders this item's reads before the item after that writes.)
+    float* my_acc = s_acc + (mine & 1) * DS_WARPS * hd;
+    float (*my_ml)[2] = sh.ml[mine & 1];
     if (g == 0) {
 #pragma unroll
       for (int n = 0; n < I * 4; ++n) {
         const int d = 8 * n + 2 * q;
-        if (d < hd) *reinterpret_cast<float2*>(s_acc + warp * hd + d) = make_float2(acc[n][0], acc[n][1]);
+        if (d < hd) *reinterpret_cast<float2*>(my_acc + warp * hd + d) = make_float2(acc[n][0], acc[n][1]);
       }
       if (q == 0) {
-        sh.ml[warp][0] = m;
-        sh.ml[warp][1] = l;
+        my_ml[warp][0] = m;
+        my_ml[warp][1] = l;
       }
     }
     __syncthreads();
-    if (warp == 0) {
-      const float mw = lane < DS_WARPS ? sh.ml[lane][0] : -INFINITY;
-      const float Mb = warp_max(mw);
-      const float wg = (lane < DS_WARPS && Mb != -INFINITY) ? ds_exp2(mw - Mb) : 0.f;
-      const float Lb = warp_sum(lane < DS_WARPS ? sh.ml[lane][1] * wg : 0.f);
-      if (lane < DS_WARPS) sh.w8[lane] = wg;
-      if (lane == 0) {
-        sh.blk_ml[0] = Mb;
-        sh.blk_ml[1] = Lb;
-      }
-    }
-    __syncthreads();
-    float* dst = ph.part_out + ((long long)(it.seq * ph.n_heads + it.head) * ph.n_splits + it.split) * (hd + 4);
-    for (int c = tid; c < hd; c += DS_THREADS) {
-      float o = 0.f;
+    if (tid < hd) {
+      float Mb = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < DS_WARPS; ++w) o += s_acc[w * hd + c] * sh.w8[w];
-      dst[c] = o;
+      for (int w = 0; w < DS_WARPS; ++w) Mb = fmaxf(Mb, my_ml[w][0]);
+      float Lb = 0.f, o = 0.f;
+#pragma unroll
+      for (int w = 0; w < DS_WARPS; ++w) {
+        const float wg = Mb == -INFINITY ? 0.f : ds_exp2(my_ml[w][0] - Mb);
+        Lb += my_ml[w][1] * wg;
+        o += my_acc[w * hd + tid] * wg;
+      }
+      float* dst = ph.part_out + ((long long)(it.seq * ph.n_heads + it.head) * ph.n_splits + it.split) * (hd + 4);
+      dst[tid] = o;
+      if (tid == 0) {
+        dst[hd] = Mb;
+        dst[hd + 1] = Lb;
+      }
     }
-    if (tid == 0) {
-      dst[hd] = sh.blk_ml[0];
-      dst[hd + 1] = sh.blk_ml[1];
-    }
-    __syncthreads();
   }
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }
 
 // 32-dim blocks of a head and 8-key tiles of a chunk for a head size (a multiple of 16, at most 128).
 // `asked` < 0: the block's items have not even been listed yet.
-__device__ bool ds_attention_phase(const Phase& ph, unsigned char* smem, StepShared& sh, unsigned& page_seq, int asked) {
+__device__ bool ds_attention_phase(const Phase& ph, const Phase* maps, unsigned char* smem, StepShared& sh, unsigned& page_seq,
+                                   int asked) {
   if (asked < 0) {
     ds_attn_plan(ph, sh);
     asked = 0;
   }
   const int hd = ph.head_dim;
-  if (hd <= 32) return ds_attention_items<1, 4>(ph, smem, sh, page_seq, asked);
-  if (hd <= 64) return ds_attention_items<2, 4>(ph, smem, sh, page_seq, asked);
-  if (hd <= 96) return ds_attention_items<3, 2>(ph, smem, sh, page_seq, asked);
-  return ds_attention_items<4, 2>(ph, smem, sh, page_seq, asked);
+  if (hd <= 64) return ds_attention_items<2, 4>(ph, maps, smem, sh, page_seq, asked);       // chunks of 32 keys
+  return ds_attention_items<4, 2>(ph, maps, smem, sh, page_seq, asked);                      // chunks of 16 keys
 }
 
 __global__ void __launch_bounds__(DS_THREADS, 1)
@@ -1090,7 +1103,7 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* cou
     } else if (ph.type == PH_LINEAR) {
       ds_linear_phase(ph, ds_smem_raw, sh, wpre, have_pre, params_pre);
     } else if (ph.type == PH_ATTENTION) {
-      if (!ds_attention_phase(ph, ds_smem_raw, sh, page_seq, pages_pre)) failed = true;
+      if (!ds_attention_phase(ph, phases + pi, ds_smem_raw, sh, page_seq, pages_pre)) failed = true;
     } else if (ph.type == PH_SAMPLE) {
       for (int r = blockIdx.x; r < ph.M; r += gridDim.x) {
         if (!ph.do_sample && ph.partials) {
@@ -1158,7 +1171,7 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* cou
         pages_pre = 0;
         if (nx.new_k) {
           pages_pre = min(sh.work.start[sh.work.n], ds_attn_slots(nx.head_dim));
-          if (warp == 0 && pages_pre > 0) ds_issue_stream(nx, 0, pages_pre, page_seq, ds_smem_raw, sh);
+          if (warp == 0 && pages_pre > 0) ds_issue_stream(nx, phases + pi + 1, 0, pages_pre, page_seq, ds_ring_base(ds_smem_raw), sh);
         }
       }
       if (!ds_grid_wait(counter, (unsigned)(pi + 1) * gridDim.x, sh)) failed = true;

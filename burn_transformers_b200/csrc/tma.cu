@@ -74,3 +74,13 @@ int tensor_map_2d_bf16(CUtensorMap* map, const void* base, unsigned long long ro
 }
 
 }  // namespace bt
+
+// A tensor map for a caller that keeps it in its own memory (128 bytes, to be placed on a 64-byte boundary).
+extern "C" int bt_tensor_map_2d_bf16(void* out, const void* base, unsigned long long rows, unsigned long long cols,
+                                     unsigned long long row_stride, unsigned box_rows) {
+  static_assert(sizeof(CUtensorMap) == 128, "a tensor map is 128 bytes");
+  CUtensorMap map;
+  if (bt::tensor_map_2d_bf16(&map, base, rows, cols, row_stride, box_rows) != 0) return 1;
+  std::memcpy(out, &map, sizeof(map));
+  return 0;
+}

@@ -54,6 +54,8 @@ class Phase(ctypes.Structure):
         ("seeds", c_void_p), ("counters", c_void_p), ("out_ids", c_void_p), ("out_logp", c_void_p),
         ("adv_tokens", c_void_p), ("adv_positions", c_void_p), ("adv_past", c_void_p), ("adv_ctx", c_void_p),
         ("partials", c_void_p), ("n_partials", c_int), ("pad0_", c_int), ("pad1_", c_longlong),
+        ("pad2_", ctypes.c_ubyte * 32),                                   # the tensor maps lie on a 64-byte boundary
+        ("k_map", ctypes.c_ubyte * 128), ("v_map", ctypes.c_ubyte * 128),
     ]
 
 
@@ -159,6 +161,15 @@ class DecodeProgram:
                    k_pool=_p(k_pool), v_pool=_p(v_pool), table=_p(table), table_stride=table.shape[1],
                    table_len=table_len, ctx_len=_p(ctx.ctx_len), n_kv_heads=n_kv_heads,
                    scale_log2=scale * 1.4426950408889634, window=window or 0, part_out=_p(part))
+        # the layer's pools as [pages * kv_heads * 64 rows][head_dim]: a page of one head is a box of 64 rows
+        lib = kernels.library()
+        rows = k_pool.numel() // head_dim
+        for pool, field in ((k_pool, "k_map"), (v_pool, "v_map")):
+            buf = (ctypes.c_ubyte * 128)()
+            kernels._check(lib.bt_tensor_map_2d_bf16(buf, c_void_p(pool.data_ptr()), ctypes.c_ulonglong(rows),
+                                                     ctypes.c_ulonglong(head_dim), ctypes.c_ulonglong(head_dim),
+                                                     ctypes.c_uint(PAGE_SIZE)))
+            setattr(ph, field, buf)
         self._add(ph, proj, k_pool, v_pool, table, part)
         return AttentionPartials(part, splits, n_heads, head_dim)
 
