@@ -209,21 +209,21 @@ __device__ __forceinline__ void ds_cp16(const void* smem_dst, const void* src) {
 }
 __device__ __forceinline__ void ds_cp_wait() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
-// Shared memory of a linear phase: the panel (16 rows of bfloat16), then what the panel is made from
+// Shared memory of a linear phase: the panel (8 or 16 rows of bfloat16), then what the panel is made from
 // (LayerNorm: the rows in 32-bit, gamma, beta; merge: the attention phase's partials).
-__device__ __host__ __forceinline__ long long ds_panel_bytes(int K) {
+__device__ __host__ __forceinline__ long long ds_panel_bytes(int K, int M) {
   long long row = (long long)K * 2;
   row += (64 - (row % 128) + 128) % 128;
-  return 16 * row;
+  return (M > 8 ? 16 : 8) * row;        // the second eight rows are read only when there are more than eight
 }
 __device__ __host__ __forceinline__ long long ds_linear_smem(const Phase& ph) {
-  long long bytes = ds_panel_bytes(ph.K);
+  long long bytes = ds_panel_bytes(ph.K, ph.M);
   if (ph.a_kind == A_LAYERNORM) bytes += ((long long)ph.M + 2) * ph.K * 4;
   if (ph.a_kind == A_MERGE) bytes += (long long)ph.M * ph.n_heads * ph.n_splits * (ph.head_dim + 4) * 4;
   return bytes;
 }
 __device__ __forceinline__ float* ds_norm_params(const Phase& ph, unsigned char* smem) {   // gamma[K], beta[K]
-  return reinterpret_cast<float*>(smem + ds_panel_bytes(ph.K)) + (long long)ph.M * ph.K;
+  return reinterpret_cast<float*>(smem + ds_panel_bytes(ph.K, ph.M)) + (long long)ph.M * ph.K;
 }
 // gamma and beta never change: they can be asked for before the grid barrier that precedes the phase
 __device__ __forceinline__ void ds_prefetch_norm_params(const Phase& ph, unsigned char* smem) {
@@ -280,7 +280,7 @@ __device__ void ds_build_panel(const Phase& ph, unsigned char* smem, StepShared&
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = ph.K, KP = ds_panel_stride(K), M = ph.M;
   __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(smem);
-  float* stage = reinterpret_cast<float*>(smem + ds_panel_bytes(K));
+  float* stage = reinterpret_cast<float*>(smem + ds_panel_bytes(K, M));
   // rows at and beyond M are never written: their products land in rows of the result that are not stored
   if (ph.a_kind == A_ROWS) {
     const __nv_bfloat16* a = ph.a;
