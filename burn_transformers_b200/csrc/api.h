@@ -40,6 +40,15 @@ int bt_attention_prefill_mma(const void* q, long long q_row_stride, const void* 
                              int n_kv_heads, int head_dim, float scale, int causal, int window, cudaStream_t stream);
 
 long long bt_attention_decode_scratch_floats(int n_seqs, int n_heads, int head_dim, int n_splits);
+// Decode attention on tensor cores (bfloat16, head sizes 16..128 in steps of 16): arguments as bt_attention_decode,
+// plus the number of pages of the pools.
+int bt_attention_decode_mma_supports(int head_dim);
+int bt_attention_decode_mma(const void* q, long long q_row_stride, const void* new_k, const void* new_v, void* k_pool,
+                            void* v_pool, long long pool_pages, const int* kv_table, int table_stride, int table_len,
+                            void* out, float* scratch, int* tickets, int* status, const int* ctx_len, int n_seqs,
+                            int n_heads, int n_kv_heads, int head_dim, float scale, int window, int n_splits, int max_ctx,
+                            int merge, cudaStream_t stream);
+
 int bt_attention_decode(const void* q, long long q_row_stride, const void* new_k, const void* new_v, void* k_pool,
                         void* v_pool, const int* kv_table, int table_stride, int table_len, int page_size, void* out,
                         float* scratch, int* tickets, int* status, const int* ctx_len, int n_seqs, int n_heads,

@@ -1,0 +1,105 @@
+// Decode attention on tensor cores: the pieces that the fused decode step and the stand-alone decode attention share.
+// One query per (sequence, head) is row 0 of a 16-row tile; keys and values lie in shared memory as the tensor
+// memory accelerator leaves them with the 128-byte swizzle (tiles of 64 rows x 128 bytes; the 16-byte chunk c of
+// row r lies at chunk c ^ (r & 7)), so that the 8 x 8 blocks ldmatrix reads fall into different banks.
+#pragma once
+#include "common.cuh"
+
+namespace bt {
+
+constexpr int DS_PAGE = 64;          // tokens per page
+
+__device__ __forceinline__ void ds_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned ds_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ float ds_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ unsigned ds_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ds_ldmatrix_x4(unsigned (&r)[4], unsigned smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+__device__ __forceinline__ void ds_ldmatrix_x4_trans(unsigned (&r)[4], unsigned smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+// Shared-memory address of the 16-byte chunk `chunk` (8 dims) of row `row` of a page's keys or values.
+__device__ __forceinline__ unsigned ds_swizzled(unsigned tiles, int row, int chunk) {
+  return tiles + (unsigned)((chunk >> 3) * DS_PAGE * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+// One chunk of 8 T keys (rows row0.. of the page whose keys lie at Ks and values at Vs, shared-memory addresses):
+// scores, the running softmax (32-bit), the weighted values.  `qa`: the query's fragments (row 0 of the tile),
+// two registers per 16 dims.
+template <int I, int T>
+__device__ __forceinline__ void ds_attn_chunk(const unsigned (&qa)[I * 4], unsigned Ks, unsigned Vs, int hd, int row0, int key0, int lo,
+                                              int hi, float scale_log2, float& m, float& l, float (&acc)[I * 4][4]) {
+  const int lane = threadIdx.x & 31, q = lane & 3;
+  const int blk = lane >> 3, r = lane & 7;       // this lane gives the address of row r of block blk of a load of four
+  float s[T][4];
+#pragma unroll
+  for (int t = 0; t < T; ++t) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[t][e] = 0.f;
+#pragma unroll
+    for (int i = 0; i < I; ++i) {
+      if (32 * i < hd) {           // four chunks = 32 dims = two products
+        unsigned kf[4];
+        ds_ldmatrix_x4(kf, ds_swizzled(Ks, row0 + 8 * t + r, 4 * i + blk));
+        ds_mma(s[t], qa[4 * i], 0u, qa[4 * i + 1], 0u, kf[0], kf[1]);
+        ds_mma(s[t], qa[4 * i + 2], 0u, qa[4 * i + 3], 0u, kf[2], kf[3]);
+      }
+    }
+  }
+  float mx = -INFINITY;
+#pragma unroll
+  for (int t = 0; t < T; ++t)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int key = key0 + 8 * t + 2 * q + e;
+      s[t][e] = (key >= lo && key < hi) ? s[t][e] * scale_log2 : -INFINITY;
+      mx = fmaxf(mx, s[t][e]);
+    }
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+  const float m_new = fmaxf(m, mx);
+  const float corr = m_new == -INFINITY ? 1.f : ds_exp2(m - m_new);
+  float psum = 0.f;
+  unsigned pa[T];
+#pragma unroll
+  for (int t = 0; t < T; ++t) {
+    const float p0 = s[t][0] == -INFINITY ? 0.f : ds_exp2(s[t][0] - m_new);
+    const float p1 = s[t][1] == -INFINITY ? 0.f : ds_exp2(s[t][1] - m_new);
+    psum += p0 + p1;
+    pa[t] = ds_pack(p0, p1);
+  }
+  l = l * corr + psum;
+  m = m_new;
+#pragma unroll
+  for (int n = 0; n < I * 4; ++n) {
+    acc[n][0] *= corr;
+    acc[n][1] *= corr;
+  }
+  // values: blocks (keys 16 b (+ 8), dims 16 n (+ 8)) read transposed
+#pragma unroll
+  for (int b = 0; b < T / 2; ++b)
+#pragma unroll
+    for (int n = 0; n < I * 2; ++n) {
+      if (16 * n < hd) {
+        unsigned v[4];
+        ds_ldmatrix_x4_trans(v, ds_swizzled(Vs, row0 + 16 * b + (blk & 1) * 8 + r, 2 * n + (blk >> 1)));
+        ds_mma(acc[2 * n], pa[2 * b], 0u, pa[2 * b + 1], 0u, v[0], v[1]);
+        ds_mma(acc[2 * n + 1], pa[2 * b], 0u, pa[2 * b + 1], 0u, v[2], v[3]);
+      }
+    }
+}
+
+}  // namespace bt

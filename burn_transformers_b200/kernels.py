@@ -377,8 +377,12 @@ def kernel_status(device) -> torch.Tensor:
 
 
 def attention_decode(q_proj, out, k_pool, v_pool, table, table_len, ctx_len, n_seqs, n_heads, n_kv_heads, head_dim,
-                     scale, *, max_ctx, window=0, n_splits=1, scratch=None, new_kv_offsets=None, merge_in_scratch=False):
+                     scale, *, max_ctx, window=0, n_splits=1, scratch=None, new_kv_offsets=None, merge_in_scratch=False,
+                     tensor_cores=True):
     """Attention of one new token per sequence over that sequence's pages.
+
+    bfloat16 with a head size of 16..128 in steps of 16 runs on tensor cores (`tensor_cores=False` keeps it on
+    the 32-bit multiply-add kernel that every other case takes).
 
     `max_ctx`: no sequence of the call is longer than this.  `new_kv_offsets` = (k_offset, v_offset): the new
     token's key and value are channels of the same `q_proj` rows; the kernel reads them from there and files
@@ -390,6 +394,8 @@ def attention_decode(q_proj, out, k_pool, v_pool, table, table_len, ctx_len, n_s
     _need(v_pool, "v_pool", q_proj.dtype)
     _need(table, "table", torch.int32)
     tickets = None
+    use_mma = (tensor_cores and q_proj.dtype == torch.bfloat16
+               and bool(library().bt_attention_decode_mma_supports(c_int(head_dim))))
     if n_splits > 1 and (n_splits > 8 or merge_in_scratch):
         need = attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
@@ -400,6 +406,14 @@ def attention_decode(q_proj, out, k_pool, v_pool, table, table_len, ctx_len, n_s
     if new_kv_offsets is not None:
         new_k = c_void_p(q_proj.data_ptr() + new_kv_offsets[0] * es)
         new_v = c_void_p(q_proj.data_ptr() + new_kv_offsets[1] * es)
+    if use_mma:
+        _check(library().bt_attention_decode_mma(
+            _ptr(q_proj), c_longlong(q_proj.shape[1]), new_k, new_v, _ptr(k_pool), _ptr(v_pool),
+            c_longlong(k_pool.numel() // (n_kv_heads * PAGE_SIZE * head_dim)), _ptr(table), c_int(table.shape[1]),
+            c_int(table_len), _ptr(out), _ptr(scratch), _ptr(tickets), _ptr(kernel_status(q_proj.device)), _ptr(ctx_len),
+            c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window),
+            c_int(n_splits), c_int(max_ctx), c_int(1 if merge_in_scratch else 0), _stream()))
+        return
     _check(library().bt_attention_decode(
         _ptr(q_proj), c_longlong(q_proj.shape[1]), new_k, new_v, _ptr(k_pool), _ptr(v_pool), _ptr(table),
         c_int(table.shape[1]), c_int(table_len), c_int(PAGE_SIZE), _ptr(out), _ptr(scratch), _ptr(tickets),

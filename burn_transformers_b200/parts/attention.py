@@ -54,14 +54,14 @@ class CausalSelfAttention(Mixer):
         return CacheNeed(kv=KvSpec(self.n_kv_heads, self.head_dim, self.window))
 
     def _splits(self, ctx) -> int:
-        """Blocks per (sequence, head) in a decode step: enough to fill the GPU about twice and to keep a block's
-        share of the cache to a few pages; at most 8, so that they merge inside one thread-block cluster."""
+        """Blocks per (sequence, head) in a decode step: enough to fill the GPU about twice, none when the batch
+        does that by itself (a split costs a merge); at most 8, so that they merge inside one thread-block
+        cluster, and at most one per page."""
         units = max(1, ctx.n_seqs * self.n_heads)
         span = ctx.ctx_bound if self.window is None else min(ctx.ctx_bound, self.window)
         pages = max(1, -(-span // PAGE_SIZE))
         by_fill = -(-2 * _SM_COUNT // units)
-        by_share = -(-pages // 4)
-        return int(max(1, min(max(by_fill, by_share), pages, 8)))
+        return int(max(1, min(by_fill, pages, 8)))
 
     def forward(self, ctx, x, residual, entry, owns_cache=True):
         n = ctx.n_tokens
@@ -87,9 +87,10 @@ class CausalSelfAttention(Mixer):
             return
         mixed = ctx.ws.take((n, self.q_width), dtype)
         if ctx.is_decode:
+            splits = self._splits(ctx)
             kernels.attention_decode(proj, mixed, k_pool, v_pool, table, group.table_len, ctx.ctx_len, ctx.n_seqs,
                                      self.n_heads, self.n_kv_heads, self.head_dim, self.scale, window=window,
-                                     n_splits=self._splits(ctx), max_ctx=ctx.ctx_bound,
+                                     n_splits=splits, max_ctx=ctx.ctx_bound,
                                      new_kv_offsets=(self.q_width, self.q_width + self.kv_width) if owns_cache else None)
         elif ctx.fresh and owns_cache:
             # every sequence starts at position 0: keys and values are the step's own projections

@@ -258,11 +258,14 @@ def test_attention_decode(dtype, hq, hkv, hd, window, splits):
     out = torch.empty(n, hq * hd, device=DEV, dtype=dtype)
     scratch = torch.empty(max(1, kernels.attention_decode_scratch_floats(n, hq, hd, splits)), device=DEV)
     scale = 0.37
-    for in_scratch in (False, True):
+    # (bfloat16 runs on tensor cores where the head size allows it, and on the multiply-add kernel when told so)
+    for in_scratch, tensor_cores in ((False, True), (True, True), (False, False), (True, False)):
+        if not tensor_cores and dtype == torch.float32:
+            continue
         out.fill_(float("nan"))
         kernels.attention_decode(q, out, k_pool, v_pool, table, table.shape[1], ctx_len, n, hq, hkv, hd, scale,
                                  window=window, n_splits=splits, scratch=scratch, max_ctx=max(lengths),
-                                 merge_in_scratch=in_scratch)
+                                 merge_in_scratch=in_scratch, tensor_cores=tensor_cores)
         for s, length in enumerate(lengths):
             qs = q[s, :hq * hd].double().cpu().view(1, hq, hd)
             want = attend(qs, dk[s], dv[s], scale, torch.tensor([length - 1]), window)
