@@ -1,15 +1,16 @@
 // Matrix products for steps with many rows (prefill), bfloat16 operands, 32-bit accumulation, on the
 // fifth-generation tensor cores:  out[M,N] = act(A[M,K] @ W[N,K]^T + bias) (+ residual).
 //
-// A block computes 128 x BN tiles of the output, one after another (one block per SM).  Its six warps have fixed jobs:
+// A block computes 128 x BN tiles of the output, one after another (one block per SM).  Its ten warps have fixed jobs:
 //   warp 0    asks the tensor memory accelerator (TMA) for the next 128 x 64 tile of A and BN x 64 tile of W
 //             (cp.async.bulk.tensor, 128-byte swizzle) into a ring of shared-memory stages;
 //   warp 1    one elected thread issues tcgen05.mma (M = 128, N = BN, K = 16, four per stage) whose accumulator
 //             lives in tensor memory (TMEM), and commits each stage back to the producer when it has been read;
-//   warps 2-5 wait for a tile's last commit, read the accumulator with tcgen05.ld (a warp reaches the 32 TMEM lanes
-//             of its quarter), turn it through shared memory so that a warp writes whole row segments, add the bias,
-//             apply GELU, add the 32-bit residual and store 32-bit or bfloat16.  There are two accumulators, so
-//             this runs while the next tile's products are already being issued.
+//   warps 2-9 wait for a tile's last commit and read the accumulator with tcgen05.ld (a warp reaches the 32 TMEM lanes
+//             of its quarter; the two warps of a quarter take half of the columns each).  A thread then holds 32
+//             consecutive columns of one row: it adds the bias, applies GELU, adds the 32-bit residual and writes
+//             the segment with 16-byte stores, 32-bit or bfloat16.  There are two accumulators, so this runs
+//             while the next tile's products are already being issued.
 // Both operands are K-major (K contiguous): A as the activations are stored, W as [N, K].
 // Stages hand over through mbarriers; every wait is bounded, and a wait that runs out marks the call as failed
 // (status word) instead of hanging: the block still frees its tensor memory and returns.
@@ -21,7 +22,8 @@ namespace bt {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;                 // bfloat16 per stage row: 128 bytes, the swizzle span
-constexpr int TC_THREADS = 192;
+constexpr int TC_EPI_WARPS = 8;                    // two per quarter of the accumulator's rows, half the columns each
+constexpr int TC_THREADS = (2 + TC_EPI_WARPS) * 32;
 constexpr int TC_WAIT_LIMIT = 1 << 22;    // polls of an mbarrier before giving up
 
 struct TcParams {
@@ -104,6 +106,10 @@ __device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
 }
 // GELU of the epilogue.  When the result is rounded to bfloat16 anyway, the tanh form uses the hardware's tanh
 // (relative error about 2^-11, below that rounding); a 32-bit result gets the full-precision functions.
+__device__ __forceinline__ unsigned tc_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
 __device__ __forceinline__ float tc_activation(float x, int act, bool exact) {
   if (exact) return apply_activation(x, act);
   if (act == kActGeluTanh) {
@@ -131,7 +137,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   __shared__ int failed;
   constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2;
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<unsigned long long>(tc_smem_raw) + 1023ull) & ~1023ull);
-  float* patches = reinterpret_cast<float*>(tiles + (size_t)STAGES * (A_BYTES + W_BYTES));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + TC_BM - 1) / TC_BM, tiles_n = (p.N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
@@ -144,7 +149,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       tc_bar_init(&acc_full[b], 1);
-      tc_bar_init(&acc_empty[b], 4);       // one arrival per epilogue warp
+      tc_bar_init(&acc_empty[b], TC_EPI_WARPS);       // one arrival per epilogue warp
     }
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -212,9 +217,11 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
     }
   } else {
-    // epilogue: warp w reaches TMEM lanes 32 * (w % 4) .. + 31, i.e. the tile's rows of that quarter
-    const int quarter = warp & 3;
-    float* patch = patches + (size_t)(warp - 2) * (32 * 33);
+    // epilogue: warp w reaches TMEM lanes 32 * (w % 4) .. + 31, i.e. the tile's rows of that quarter; the two warps
+    // of a quarter take half of the tile's columns each.  A thread holds 32 consecutive columns of its row: bias,
+    // activation and residual are applied there and the row segment is written with 16-byte stores.
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const bool vec_ok = p.out_is_f32 ? (p.N % 4 == 0) : (p.N % 8 == 0);
     int local = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
       const int buf = local & 1;
@@ -225,41 +232,65 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const int row_base = m0 + quarter * 32;
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
         float v[32];
         tc_ld32(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + c0), v);
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) patch[lane * 33 + i] = v[i];    // row `lane` of the chunk
-        __syncwarp();
-        const int col = n0 + c0 + lane;                              // now: one column per lane, rows in turn
-        if (col < p.N) {
-          const float bias = p.bias ? p.bias[col] : 0.f;
-          const int rows = min(32, p.M - row_base);
-          const long long o0 = (long long)row_base * p.N + col;
-          if (p.residual) {
-            // all of the chunk's residual values first, so that their latencies overlap (the output may be the
+        const int col0 = n0 + c0;
+        if (col0 >= p.N) continue;                 // (uniform in the warp; the load above is collective)
+        const long long o0 = (long long)row * p.N + col0;
+        if (vec_ok && col0 + 32 <= p.N) {
+          float4 res[8];
+          if (p.residual && row_ok) {
+            // the whole segment of the residual first, so that the latencies overlap (the output may be the
             // residual itself, which keeps the compiler from moving these loads above the stores on its own)
-            float res[32];
 #pragma unroll
-            for (int r = 0; r < 32; ++r) res[r] = r < rows ? p.residual[o0 + (long long)r * p.N] : 0.f;
+            for (int j = 0; j < 8; ++j) res[j] = *reinterpret_cast<const float4*>(p.residual + o0 + 4 * j);
+          }
+          if (p.bias) {
 #pragma unroll
-            for (int r = 0; r < 32; ++r)
-              if (r < rows) {
-                const float x = tc_activation(patch[r * 33 + lane] + bias, p.act, true) + res[r];
-                reinterpret_cast<float*>(p.out)[o0 + (long long)r * p.N] = x;
-              }
-          } else {
-            for (int r = 0; r < rows; ++r) {
-              const float x = tc_activation(patch[r * 33 + lane] + bias, p.act, p.out_is_f32 != 0);
-              const long long o = o0 + (long long)r * p.N;
-              if (p.out_is_f32)
-                reinterpret_cast<float*>(p.out)[o] = x;
-              else
-                reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(x);
+            for (int j = 0; j < 8; ++j) {
+              const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + 4 * j));
+              v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
             }
+          }
+          const bool exact = p.residual != nullptr || p.out_is_f32 != 0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = tc_activation(v[i], p.act, exact);
+          if (!row_ok) continue;
+          if (p.out_is_f32) {
+            float* dst = reinterpret_cast<float*>(p.out) + o0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 x = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              if (p.residual) { x.x += res[j].x; x.y += res[j].y; x.z += res[j].z; x.w += res[j].w; }
+              *reinterpret_cast<float4*>(dst + 4 * j) = x;
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + o0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 x;
+              x.x = tc_pack(v[8 * j], v[8 * j + 1]);
+              x.y = tc_pack(v[8 * j + 2], v[8 * j + 3]);
+              x.z = tc_pack(v[8 * j + 4], v[8 * j + 5]);
+              x.w = tc_pack(v[8 * j + 6], v[8 * j + 7]);
+              *reinterpret_cast<uint4*>(dst + 8 * j) = x;
+            }
+          }
+        } else if (row_ok) {
+          // a ragged edge, or rows that are no multiple of 16 bytes: one element at a time
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (col0 + i >= p.N) break;
+            float x = tc_activation(v[i] + (p.bias ? p.bias[col0 + i] : 0.f), p.act, p.residual != nullptr || p.out_is_f32 != 0);
+            if (p.residual) x += p.residual[o0 + i];
+            if (p.out_is_f32)
+              reinterpret_cast<float*>(p.out)[o0 + i] = x;
+            else
+              reinterpret_cast<__nv_bfloat16*>(p.out)[o0 + i] = __float2bfloat16_rn(x);
           }
         }
       }
@@ -280,7 +311,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const TcParams& p, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 4 * 32 * 33 * sizeof(float);
+  constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
   auto kern = linear_tcgen05_kernel<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
