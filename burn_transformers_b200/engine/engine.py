@@ -108,6 +108,10 @@ class Engine:
                 raise ShapeError(f"slot {e.slot}: wanted place {[w for w in e.want if not 0 <= w < len(e.tokens)][0]} "
                                  f"is outside the {len(e.tokens)} tokens of the step")
 
+    def check_kernels(self) -> None:
+        """Raises a KernelError if a kernel of this device reported that a bounded wait of its own ran out."""
+        kernels.check_status(self.device)
+
     def decode_graph(self, n: int, selection: dict | None = None):
         """The recorded decode step for `n` sequences (with token selection when `selection` is given)."""
         from .graphs import DecodeGraph

@@ -103,6 +103,9 @@ def run_batch(engine, sampler, trackers: list[SequenceTracker], on_token: Callab
                 session.run(active, slots, lambda t, token, logp: _emit(t, token, logp, on_token))
                 break
             logits = engine.step([StepEntry(slots[t.request], [t.output.token_ids[-1]], [0]) for t in active])
+        check = getattr(engine, "check_kernels", None)
+        if check is not None:
+            check()          # (the host has read this batch's last tokens: nothing is in flight)
     finally:
         for slot in slots.values():
             engine.release(slot)

@@ -376,6 +376,24 @@ def kernel_status(device) -> torch.Tensor:
     return t
 
 
+_STATUS_TEXT = {1: "decode attention gave up waiting for a copy of cache pages",
+                2: "the tcgen05 matrix product gave up waiting for a stage of its pipeline",
+                3: "the fused decode step gave up at a grid barrier or waiting for cache pages",
+                4: "the fused decode step met a token id or position outside its table"}
+
+
+def check_status(device) -> None:
+    """Raises if a kernel on `device` reported that one of its bounded waits ran out (its results are then not to be
+    trusted), and clears the report.  Reads one int from the device: call it where the host waits anyway."""
+    t = _STATUS.get(device)
+    if t is None:
+        return
+    code = int(t.item())
+    if code:
+        t.zero_()
+        raise KernelError(_STATUS_TEXT.get(code, f"a kernel reported status {code}"))
+
+
 def attention_decode(q_proj, out, k_pool, v_pool, table, table_len, ctx_len, n_seqs, n_heads, n_kv_heads, head_dim,
                      scale, *, max_ctx, window=0, n_splits=1, scratch=None, new_kv_offsets=None, merge_in_scratch=False,
                      tensor_cores=True):

@@ -162,3 +162,15 @@ def test_trace_run_program(model_b, tmp_path, dtype, tol):
         got = np.frombuffer((out / f"{step}.f32").read_bytes(), dtype="<f4").reshape(len(places), TINY_B["vocab_size"])
         for row, (r, p) in zip(got, places):
             assert np.abs(row - ref[r][p]).max() / np.abs(ref[r]).max() < tol, (step, r, p)
+
+
+def test_a_reported_wait_that_ran_out_becomes_an_error(model_a):
+    """Kernels give up a wait of their own after a limit and say so in a status word; the engine turns that into an
+    error where the host waits anyway.  (The report is made here by hand: no kernel is made to wait.)"""
+    from burn_transformers_b200 import Engine, KernelError, kernels
+    engine = Engine.from_folder(model_a[0], "bfloat16", max_tokens=128)
+    engine.check_kernels()
+    kernels.kernel_status(engine.device).fill_(3)
+    with pytest.raises(KernelError, match="fused decode step"):
+        engine.check_kernels()
+    engine.check_kernels()          # the report is cleared
