@@ -187,6 +187,13 @@ __device__ __forceinline__ int ds_panel_stride(int K) {
   return bytes / 2;
 }
 
+// The kernel exists in several builds.  The general one holds the code for every length of product and every head
+// size; the others hold only what a common model shape needs (PWA, PWB: the two values of ds_blocks_per_warp its
+// products have; HDMAX: its largest head size), which keeps the code a step runs through small and close
+// together: the instruction cache is a measurable part of the step.  PWA < 0: everything.
+template <int PWA, int PWB>
+__device__ __forceinline__ constexpr bool ds_built(int pw) { return PWA < 0 || pw == PWA || pw == PWB; }
+
 // ---- the rows' panel -------------------------------------------------------------------------------------
 // Asynchronous 16-byte copies from global memory (through the L2 cache only: other blocks wrote the data during
 // this launch) into shared memory: all of a thread's copies are in flight together.
@@ -262,6 +269,7 @@ __device__ __forceinline__ void ds_layernorm_row(const float* __restrict__ src, 
   }
 }
 
+template <int PWA, int PWB>
 __device__ void ds_build_panel(const Phase& ph, unsigned char* smem, StepShared& sh, bool params_asked) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = ph.K, KP = ds_panel_stride(K), M = ph.M;
@@ -290,12 +298,13 @@ __device__ void ds_build_panel(const Phase& ph, unsigned char* smem, StepShared&
         const int r = r0 + warp;
         const bool live = r < M;
         const float* src = x32 + (long long)(live ? (rows ? rows[r] : r) : 0) * K;
-        if (K <= 4 * 128)
-          ds_layernorm_row<4>(src, live, K, eps, gs, bs, As + r * KP);
-        else if (K <= 8 * 128)
-          ds_layernorm_row<8>(src, live, K, eps, gs, bs, As + r * KP);
-        else
-          ds_layernorm_row<13>(src, live, K, eps, gs, bs, As + r * KP);
+        // (rows of K <= 512, <= 1024, <= 1664 have products of 1..2, 3..4, 6..12 blocks per warp)
+        if constexpr (ds_built<PWA, PWB>(1) || ds_built<PWA, PWB>(2))
+          if (K <= 4 * 128) ds_layernorm_row<4>(src, live, K, eps, gs, bs, As + r * KP);
+        if constexpr (ds_built<PWA, PWB>(3) || ds_built<PWA, PWB>(4))
+          if (K > 4 * 128 && K <= 8 * 128) ds_layernorm_row<8>(src, live, K, eps, gs, bs, As + r * KP);
+        if constexpr (ds_built<PWA, PWB>(6) || ds_built<PWA, PWB>(12))
+          if (K > 8 * 128) ds_layernorm_row<13>(src, live, K, eps, gs, bs, As + r * KP);
       }
     } else {
       // rows too long for registers: staged in shared memory, one warp to a row
@@ -570,17 +579,17 @@ __device__ __forceinline__ int ds_blocks_per_warp(int K) {
 }
 
 // The first group of weights of a phase, asked for before the phase's grid barrier.
+template <int PWA, int PWB>
 __device__ __forceinline__ bool ds_prefetch_weights(const Phase& ph, uint4 (&wpre)[DS_NB]) {
   const int n_tiles = (ph.N + 7) / 8;
   if ((int)blockIdx.x >= n_tiles) return false;
-  switch (ds_blocks_per_warp(ph.K)) {
-    case 1: ds_load_group<1, 4>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true;
-    case 2: ds_load_group<2, 4>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true;
-    case 3: ds_load_group<3, 4>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true;
-    case 4: ds_load_group<4, 3>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true;
-    case 6: ds_load_group<6, 2>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true;
-    case 12: ds_load_group<12, 1>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true;
-  }
+  const int pw = ds_blocks_per_warp(ph.K);
+  if constexpr (ds_built<PWA, PWB>(1)) if (pw == 1) { ds_load_group<1, 4>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true; }
+  if constexpr (ds_built<PWA, PWB>(2)) if (pw == 2) { ds_load_group<2, 4>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true; }
+  if constexpr (ds_built<PWA, PWB>(3)) if (pw == 3) { ds_load_group<3, 4>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true; }
+  if constexpr (ds_built<PWA, PWB>(4)) if (pw == 4) { ds_load_group<4, 3>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true; }
+  if constexpr (ds_built<PWA, PWB>(6)) if (pw == 6) { ds_load_group<6, 2>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true; }
+  if constexpr (ds_built<PWA, PWB>(12)) if (pw == 12) { ds_load_group<12, 1>(ph, blockIdx.x, gridDim.x, n_tiles, 0, wpre); return true; }
   return false;
 }
 
@@ -620,6 +629,7 @@ __device__ void ds_track_write(const Phase& ph, StepShared& sh, Track& trk) {
 // tiles of a group for a K of this many blocks per warp
 __device__ __forceinline__ int ds_tiles_per_group(int pw) { return pw == 0 ? 1 : (DS_NB / pw < 4 ? DS_NB / pw : 4); }
 
+template <int PWA, int PWB>
 __device__ void ds_linear_phase(const Phase& ph, unsigned char* smem, StepShared& sh, uint4 (&wpre)[DS_NB], bool have_pre,
                                 bool params_asked) {
   const __nv_bfloat16* As = reinterpret_cast<const __nv_bfloat16*>(smem);
@@ -635,23 +645,21 @@ __device__ void ds_linear_phase(const Phase& ph, unsigned char* smem, StepShared
   }
   const int pw = ds_blocks_per_warp(ph.K);
   float bias[4], res[4];
-  switch (ds_tiles_per_group(pw)) {      // the first group's finishing operands travel while the panel is built
-    case 4: ds_finish_operands<4>(ph, blockIdx.x, gridDim.x, n_tiles, bias, res); break;
-    case 3: ds_finish_operands<3>(ph, blockIdx.x, gridDim.x, n_tiles, bias, res); break;
-    case 2: ds_finish_operands<2>(ph, blockIdx.x, gridDim.x, n_tiles, bias, res); break;
-    default: if (pw) ds_finish_operands<1>(ph, blockIdx.x, gridDim.x, n_tiles, bias, res); break;
-  }
-  ds_build_panel(ph, smem, sh, params_asked);
+  // the first group's finishing operands travel while the panel is built (4, 4, 4, 3, 2, 1 tiles to a group)
+  if constexpr (ds_built<PWA, PWB>(1) || ds_built<PWA, PWB>(2) || ds_built<PWA, PWB>(3))
+    if (pw >= 1 && pw <= 3) ds_finish_operands<4>(ph, blockIdx.x, gridDim.x, n_tiles, bias, res);
+  if constexpr (ds_built<PWA, PWB>(4)) if (pw == 4) ds_finish_operands<3>(ph, blockIdx.x, gridDim.x, n_tiles, bias, res);
+  if constexpr (ds_built<PWA, PWB>(6)) if (pw == 6) ds_finish_operands<2>(ph, blockIdx.x, gridDim.x, n_tiles, bias, res);
+  if constexpr (ds_built<PWA, PWB>(12)) if (pw == 12) ds_finish_operands<1>(ph, blockIdx.x, gridDim.x, n_tiles, bias, res);
+  ds_build_panel<PWA, PWB>(ph, smem, sh, params_asked);
   ds_stamp(sh, 2);
-  switch (pw) {
-    case 1: ds_linear_tiles<1>(ph, As, sh, wpre, have_pre, bias, res, trk); break;
-    case 2: ds_linear_tiles<2>(ph, As, sh, wpre, have_pre, bias, res, trk); break;
-    case 3: ds_linear_tiles<3>(ph, As, sh, wpre, have_pre, bias, res, trk); break;
-    case 4: ds_linear_tiles<4>(ph, As, sh, wpre, have_pre, bias, res, trk); break;
-    case 6: ds_linear_tiles<6>(ph, As, sh, wpre, have_pre, bias, res, trk); break;
-    case 12: ds_linear_tiles<12>(ph, As, sh, wpre, have_pre, bias, res, trk); break;
-    default: ds_linear_tiles_long(ph, As, sh, trk); break;
-  }
+  if constexpr (ds_built<PWA, PWB>(1)) if (pw == 1) ds_linear_tiles<1>(ph, As, sh, wpre, have_pre, bias, res, trk);
+  if constexpr (ds_built<PWA, PWB>(2)) if (pw == 2) ds_linear_tiles<2>(ph, As, sh, wpre, have_pre, bias, res, trk);
+  if constexpr (ds_built<PWA, PWB>(3)) if (pw == 3) ds_linear_tiles<3>(ph, As, sh, wpre, have_pre, bias, res, trk);
+  if constexpr (ds_built<PWA, PWB>(4)) if (pw == 4) ds_linear_tiles<4>(ph, As, sh, wpre, have_pre, bias, res, trk);
+  if constexpr (ds_built<PWA, PWB>(6)) if (pw == 6) ds_linear_tiles<6>(ph, As, sh, wpre, have_pre, bias, res, trk);
+  if constexpr (ds_built<PWA, PWB>(12)) if (pw == 12) ds_linear_tiles<12>(ph, As, sh, wpre, have_pre, bias, res, trk);
+  if constexpr (ds_built<PWA, PWB>(0)) if (pw == 0) ds_linear_tiles_long(ph, As, sh, trk);
   if (ph.track) ds_track_write(ph, sh, trk);
 }
 
@@ -951,6 +959,7 @@ __device__ bool ds_attention_items(const Phase& ph, const Phase* maps, unsigned 
 
 // 32-dim blocks of a head and 8-key tiles of a chunk for a head size (a multiple of 16, at most 128).
 // `asked` < 0: the block's items have not even been listed yet.
+template <int HDMAX>
 __device__ bool ds_attention_phase(const Phase& ph, const Phase* maps, unsigned char* smem, StepShared& sh, unsigned& page_seq,
                                    int asked) {
   if (asked < 0) {
@@ -959,9 +968,11 @@ __device__ bool ds_attention_phase(const Phase& ph, const Phase* maps, unsigned 
   }
   const int hd = ph.head_dim;
   if (hd <= 64) return ds_attention_items<2, 4>(ph, maps, smem, sh, page_seq, asked);       // chunks of 32 keys
-  return ds_attention_items<4, 2>(ph, maps, smem, sh, page_seq, asked);                      // chunks of 16 keys
+  if constexpr (HDMAX > 64) return ds_attention_items<4, 2>(ph, maps, smem, sh, page_seq, asked);      // chunks of 16 keys
+  return false;
 }
 
+template <int PWA, int PWB, int HDMAX>
 __global__ void __launch_bounds__(DS_THREADS, 1)
 decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* counter, int* status, long long* trace) {
   extern __shared__ __align__(128) unsigned char ds_smem_raw[];
@@ -1008,9 +1019,9 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* cou
         if (!ok && tid == 0 && status) atomicExch(status, 4);
       }
     } else if (ph.type == PH_LINEAR) {
-      ds_linear_phase(ph, ds_smem_raw, sh, wpre, have_pre, params_pre);
+      ds_linear_phase<PWA, PWB>(ph, ds_smem_raw, sh, wpre, have_pre, params_pre);
     } else if (ph.type == PH_ATTENTION) {
-      if (!ds_attention_phase(ph, phases + pi, ds_smem_raw, sh, page_seq, pages_pre)) failed = true;
+      if (!ds_attention_phase<HDMAX>(ph, phases + pi, ds_smem_raw, sh, page_seq, pages_pre)) failed = true;
     } else if (ph.type == PH_SAMPLE) {
       for (int r = blockIdx.x; r < ph.M; r += gridDim.x) {
         if (!ph.do_sample && ph.partials) {
@@ -1066,7 +1077,7 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* cou
       // ask for what the next phase needs and nobody writes during the step
       const Phase& nx = sh.phase[(pi + 1) & 1];
       if (nx.type == PH_LINEAR) {
-        have_pre = ds_prefetch_weights(nx, wpre);
+        have_pre = ds_prefetch_weights<PWA, PWB>(nx, wpre);
         if (nx.a_kind == A_LAYERNORM) {
           ds_prefetch_norm_params(nx, ds_smem_raw);
           params_pre = true;
@@ -1108,15 +1119,39 @@ extern "C" long long bt_decode_step_smem_bytes(const void* phases_host, int n_ph
   return need + 128;
 }
 
-// phases_dev: the program in device memory.  counter: one zero-initialised-per-launch unsigned (this call clears
+// Which build of the kernel serves these phases (host copy of the program): 0 the general one, 1 products of 3 and
+// 12 blocks per warp (K in 513..768 and 1537..3072) with heads up to 64, 2 products of 4 blocks per warp and long
+// ones (K in 769..1024 and over 3072) with heads up to 64.
+extern "C" int bt_decode_step_build(const void* phases_host, int n_phases) {
+  using namespace bt;
+  const Phase* ph = reinterpret_cast<const Phase*>(phases_host);
+  bool fits1 = true, fits2 = true;
+  for (int i = 0; i < n_phases; ++i) {
+    if (ph[i].type == PH_LINEAR) {
+      const int pw = (((ph[i].K + 31) / 32) + DS_WARPS - 1) / DS_WARPS;
+      const int built = pw <= 1 ? 1 : pw <= 2 ? 2 : pw <= 3 ? 3 : pw <= 4 ? 4 : pw <= 6 ? 6 : pw <= 12 ? 12 : 0;
+      if (built != 3 && built != 12) fits1 = false;
+      if (built != 4 && built != 0) fits2 = false;
+    } else if (ph[i].type == PH_ATTENTION && ph[i].head_dim > 64) {
+      fits1 = fits2 = false;
+    }
+  }
+  return fits1 ? 1 : (fits2 ? 2 : 0);
+}
+
+// phases_dev: the program in device memory.  `build`: bt_decode_step_build of the program.  counter: one zero-initialised-per-launch unsigned (this call clears
 // it).  The launch is cooperative: every block is resident, which the grid barrier relies on.
 // trace: optional 8 * n_phases 64-bit slots that receive block 0's timeline of every phase.
-extern "C" int bt_decode_step(const void* phases_dev, int n_phases, long long smem_bytes, unsigned* counter, int* status,
-                              long long* trace, cudaStream_t stream) {
+extern "C" int bt_decode_step(const void* phases_dev, int n_phases, int build, long long smem_bytes, unsigned* counter,
+                              int* status, long long* trace, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_phases >= 1 && smem_bytes <= 200 * 1024, "decode_step: %d phases need %lld bytes of shared memory", n_phases, smem_bytes);
+  BT_CHECK(build >= 0 && build <= 2, "decode_step: unknown build %d", build);
   static int n_sms = 0;
-  static long long configured = -1;
+  static long long configured_all[3] = {-1, -1, -1};
+  long long& configured = configured_all[build];
+  const void* kernel = build == 1 ? (const void*)decode_step_kernel<3, 12, 64>
+                                  : (build == 2 ? (const void*)decode_step_kernel<4, 0, 64> : (const void*)decode_step_kernel<-1, -1, 128>);
   if (n_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1124,7 +1159,7 @@ extern "C" int bt_decode_step(const void* phases_dev, int n_phases, long long sm
     BT_CHECK(n_sms > 0, "decode_step: cannot read the number of SMs");
   }
   if (configured < smem_bytes) {
-    cudaError_t e = cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
     BT_CHECK(e == cudaSuccess, "decode_step: cannot reserve %lld bytes of shared memory: %s", smem_bytes, cudaGetErrorString(e));
     configured = smem_bytes;
   }
@@ -1132,7 +1167,7 @@ extern "C" int bt_decode_step(const void* phases_dev, int n_phases, long long sm
   BT_CHECK(e == cudaSuccess, "decode_step: cannot clear the barrier counter: %s", cudaGetErrorString(e));
   const Phase* program = reinterpret_cast<const Phase*>(phases_dev);
   void* args[] = {(void*)&program, (void*)&n_phases, (void*)&counter, (void*)&status, (void*)&trace};
-  e = cudaLaunchCooperativeKernel((const void*)decode_step_kernel, dim3(n_sms), dim3(DS_THREADS), args, (size_t)smem_bytes, stream);
+  e = cudaLaunchCooperativeKernel(kernel, dim3(n_sms), dim3(DS_THREADS), args, (size_t)smem_bytes, stream);
   BT_CHECK(e == cudaSuccess, "decode_step: launch failed: %s", cudaGetErrorString(e));
   count_launch();
   return 0;

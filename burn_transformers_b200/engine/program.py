@@ -205,12 +205,13 @@ class DecodeProgram:
         lib = kernels.library()
         lib.bt_decode_step_smem_bytes.restype = c_longlong
         self.smem = int(lib.bt_decode_step_smem_bytes(ctypes.cast(array, c_void_p), c_int(len(self.phases))))
+        self.build = int(lib.bt_decode_step_build(ctypes.cast(array, c_void_p), c_int(len(self.phases))))
         if self.smem > 200 * 1024:
             raise ProgramUnsupported(f"the step needs {self.smem} bytes of shared memory")
 
     def launch(self, trace=None):
         """One step.  `trace`: optional int64 tensor of 8 * len(phases) slots for block 0's timeline of each phase."""
         kernels._check(kernels.library().bt_decode_step(
-            c_void_p(self.dev.data_ptr()), c_int(len(self.phases)), c_longlong(self.smem),
+            c_void_p(self.dev.data_ptr()), c_int(len(self.phases)), c_int(self.build), c_longlong(self.smem),
             c_void_p(self.counter.data_ptr()), c_void_p(kernels.kernel_status(self.device).data_ptr()),
             c_void_p(0 if trace is None else trace.data_ptr()), kernels._stream()))
