@@ -972,7 +972,7 @@ __device__ bool ds_attention_phase(const Phase& ph, const Phase* maps, unsigned 
   return false;
 }
 
-template <int PWA, int PWB, int HDMAX>
+template <int PWA, int PWB, int HDMAX, bool SAMPLES>
 __global__ void __launch_bounds__(DS_THREADS, 1)
 decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* counter, int* status, long long* trace) {
   extern __shared__ __align__(128) unsigned char ds_smem_raw[];
@@ -1053,17 +1053,19 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* cou
           }
           continue;
         }
-        float u = 0.f;
-        if (ph.do_sample) u = stream_uniform(ph.seeds[r], (unsigned long long)ph.counters[r]);
-        select_row<DS_THREADS>(ph.logits + (long long)r * ph.vocab, ph.vocab, ph.do_sample, ph.temperature, ph.top_k,
-                               ph.top_p, ph.min_p, u, ph.out_ids + r, ph.out_logp + r, sh.sample);
-        __syncthreads();
-        if (tid == 0) {      // the selected id becomes the next step's token; the sequence moves on by one
-          ph.adv_tokens[r] = ph.out_ids[r];
-          ph.adv_positions[r] += 1;
-          ph.adv_past[r] += 1;
-          ph.adv_ctx[r] += 1;
-          ph.counters[r] += 1;
+        if constexpr (SAMPLES) {      // (the other builds select greedily from the readout's partials only)
+          float u = 0.f;
+          if (ph.do_sample) u = stream_uniform(ph.seeds[r], (unsigned long long)ph.counters[r]);
+          select_row<DS_THREADS>(ph.logits + (long long)r * ph.vocab, ph.vocab, ph.do_sample, ph.temperature, ph.top_k,
+                                 ph.top_p, ph.min_p, u, ph.out_ids + r, ph.out_logp + r, sh.sample);
+          __syncthreads();
+          if (tid == 0) {      // the selected id becomes the next step's token; the sequence moves on by one
+            ph.adv_tokens[r] = ph.out_ids[r];
+            ph.adv_positions[r] += 1;
+            ph.adv_past[r] += 1;
+            ph.adv_ctx[r] += 1;
+            ph.counters[r] += 1;
+          }
         }
       }
     }
@@ -1121,7 +1123,7 @@ extern "C" long long bt_decode_step_smem_bytes(const void* phases_host, int n_ph
 
 // Which build of the kernel serves these phases (host copy of the program): 0 the general one, 1 products of 3 and
 // 12 blocks per warp (K in 513..768 and 1537..3072) with heads up to 64, 2 products of 4 blocks per warp and long
-// ones (K in 769..1024 and over 3072) with heads up to 64.
+// ones (K in 769..1024 and over 3072) with heads up to 64; both for greedy selection (or none) only.
 extern "C" int bt_decode_step_build(const void* phases_host, int n_phases) {
   using namespace bt;
   const Phase* ph = reinterpret_cast<const Phase*>(phases_host);
@@ -1134,6 +1136,8 @@ extern "C" int bt_decode_step_build(const void* phases_host, int n_phases) {
       if (built != 4 && built != 0) fits2 = false;
     } else if (ph[i].type == PH_ATTENTION && ph[i].head_dim > 64) {
       fits1 = fits2 = false;
+    } else if (ph[i].type == PH_SAMPLE && (ph[i].do_sample || ph[i].partials == nullptr)) {
+      fits1 = fits2 = false;       // (those builds select greedily from the readout's partials and hold no sampler)
     }
   }
   return fits1 ? 1 : (fits2 ? 2 : 0);
@@ -1150,8 +1154,9 @@ extern "C" int bt_decode_step(const void* phases_dev, int n_phases, int build, l
   static int n_sms = 0;
   static long long configured_all[3] = {-1, -1, -1};
   long long& configured = configured_all[build];
-  const void* kernel = build == 1 ? (const void*)decode_step_kernel<3, 12, 64>
-                                  : (build == 2 ? (const void*)decode_step_kernel<4, 0, 64> : (const void*)decode_step_kernel<-1, -1, 128>);
+  const void* kernel = build == 1 ? (const void*)decode_step_kernel<3, 12, 64, false>
+                                  : (build == 2 ? (const void*)decode_step_kernel<4, 0, 64, false>
+                                                : (const void*)decode_step_kernel<-1, -1, 128, true>);
   if (n_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
