@@ -126,6 +126,10 @@ struct AttnWork {
   AttnItem it[DS_MAX_ITEMS];
   int start[DS_MAX_ITEMS + 2];     // where each item's pages begin in the block's stream of pages; [n]: their number
   int n;
+  // what the list was made for: the layers of a model ask for the same list again and again within a step
+  const int* for_ctx;
+  const int* for_table;
+  int for_shape[6];
 };
 
 struct StepShared {
@@ -736,6 +740,11 @@ __device__ __forceinline__ AttnItem ds_attn_item(const Phase& ph, const StepShar
 // the stream of all the block's pages.  Every thread calls this.
 __device__ void ds_attn_plan(const Phase& ph, StepShared& sh) {
   const int tid = threadIdx.x;
+  const int shape[6] = {ph.M, ph.n_heads, ph.n_kv_heads, ph.n_splits, ph.window, ph.table_len};
+  bool same = sh.work.for_ctx == ph.ctx_len && sh.work.for_table == ph.table;      // (uniform: shared memory)
+#pragma unroll
+  for (int i = 0; i < 6; ++i) same = same && sh.work.for_shape[i] == shape[i];
+  if (same) return;
   ds_cache_tables(ph, sh);
   const int n_items = ph.M * ph.n_heads * ph.n_splits;
   if (tid < DS_MAX_ITEMS) {
@@ -759,6 +768,10 @@ __device__ void ds_attn_plan(const Phase& ph, StepShared& sh) {
     }
     sh.work.start[n] = total;
     sh.work.n = n;
+    sh.work.for_ctx = ph.ctx_len;
+    sh.work.for_table = ph.table;
+#pragma unroll
+    for (int i = 0; i < 6; ++i) sh.work.for_shape[i] = shape[i];
   }
   __syncthreads();
 }
@@ -985,6 +998,7 @@ decode_step_kernel(const Phase* __restrict__ phases, int n_phases, unsigned* cou
     sh.ok = 1;
     sh.ctx_src = nullptr;
     sh.table_src = nullptr;
+    sh.work.for_ctx = nullptr;
   }
   __syncthreads();
   // The phase being run lies in shared memory (its successor is copied in before the grid barrier): reading its
