@@ -348,8 +348,57 @@ __device__ void ds_build_panel(const Phase& ph, unsigned char* smem, StepShared&
     }
   } else {  // A_MERGE: the attention phase's partial (weighted values, max, sum) of every split, added up
     const int hd = ph.head_dim, S = ph.n_splits, H = ph.n_heads, unit_floats = hd + 4;   // a multiple of four floats: units stay 16-byte aligned
-    const int vecs = M * H * S * (unit_floats / 4);
     const float* part = ph.part;
+    const int cpr = hd / 8, per_row = H * cpr;                 // 16-byte chunks of a head, of a row
+    if (S <= 4) {
+      // few splits: a thread loads everything its 8 dims need straight from global memory, all loads in flight
+      // together (one trip to the L2 cache instead of a copy, two passes and their hand-overs)
+      for (int i = tid; i < M * per_row; i += DS_THREADS) {
+        const int r = i / per_row, j = i - r * per_row;
+        const int h = j / cpr, ch = j - h * cpr;
+        const float* base = part + ((long long)(r * H + h) * S) * unit_floats;
+        float ms[4], ls[4];
+        float4 p0[4], p1[4];
+#pragma unroll
+        for (int s2 = 0; s2 < 4; ++s2) {
+          if (s2 < S) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(base + s2 * unit_floats + hd));
+            ms[s2] = ml.x;
+            ls[s2] = ml.y;
+            p0[s2] = __ldcg(reinterpret_cast<const float4*>(base + s2 * unit_floats + ch * 8));
+            p1[s2] = __ldcg(reinterpret_cast<const float4*>(base + s2 * unit_floats + ch * 8 + 4));
+          } else {
+            ms[s2] = -INFINITY;
+            ls[s2] = 0.f;
+            p0[s2] = p1[s2] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+        const float mx = fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3]));
+        float L = 0.f, wgt[4];
+#pragma unroll
+        for (int s2 = 0; s2 < 4; ++s2) {
+          wgt[s2] = ms[s2] == -INFINITY ? 0.f : ds_exp2(ms[s2] - mx);
+          L += ls[s2] * wgt[s2];
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s2 = 0; s2 < 4; ++s2) {
+          const float w2 = wgt[s2] * inv;
+          o[0] += p0[s2].x * w2; o[1] += p0[s2].y * w2; o[2] += p0[s2].z * w2; o[3] += p0[s2].w * w2;
+          o[4] += p1[s2].x * w2; o[5] += p1[s2].y * w2; o[6] += p1[s2].z * w2; o[7] += p1[s2].w * w2;
+        }
+        uint4 packed;
+        packed.x = ds_pack(o[0], o[1]);
+        packed.y = ds_pack(o[2], o[3]);
+        packed.z = ds_pack(o[4], o[5]);
+        packed.w = ds_pack(o[6], o[7]);
+        *reinterpret_cast<uint4*>(As + r * KP + h * hd + ch * 8) = packed;
+      }
+      __syncthreads();
+      return;
+    }
+    const int vecs = M * H * S * (unit_floats / 4);
 #pragma unroll 4
     for (int i = tid; i < vecs; i += DS_THREADS) ds_cp16(stage + i * 4, part + i * 4);
     ds_cp_wait();
@@ -371,7 +420,6 @@ __device__ void ds_build_panel(const Phase& ph, unsigned char* smem, StepShared&
       }
     }
     __syncthreads();
-    const int cpr = hd / 8, per_row = H * cpr;                 // 16-byte chunks of a head, of a row
     for (int i = tid; i < M * per_row; i += DS_THREADS) {
       const int r = i / per_row, j = i - r * per_row;
       const int h = j / cpr, ch = j - h * cpr;
