@@ -29,13 +29,16 @@ class CausalSelfAttention(Mixer):
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, *,
                  causal: bool = True, window: int | None = None, bias: bool = True,
-                 init_std: float = 0.02, out_init_std: float | None = None):
+                 init_std: float = 0.02, out_init_std: float | None = None, positions=None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads cannot share {n_kv_heads} key heads")
         if head_dim % 16 or head_dim > 256:
             raise ValueError(f"head_dim {head_dim} must be a multiple of 16 and at most 256")
         self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
         self.scale, self.causal, self.window, self.has_bias = float(scale), causal, window, bias
+        # a position encoding that rotates (parts.base.PositionEncoding.rotates): applied to the new queries and
+        # keys before the keys are filed, so that the cache holds rotated keys
+        self.positions = positions if positions is not None and positions.rotates else None
         self.q_width = n_heads * head_dim
         self.kv_width = n_kv_heads * head_dim
         self.proj_width = self.q_width + 2 * self.kv_width
@@ -69,13 +72,18 @@ class CausalSelfAttention(Mixer):
         proj = ctx.ws.take((n, self.proj_width), dtype)
         linear(ctx, x, self.t_qkv_weight, self.t_qkv_bias if self.has_bias else None, proj, m=n,
                w_is_nk=self.nk_qkv_weight)
+        program = getattr(ctx, "program", None)
+        if self.positions is not None:
+            if program is not None:
+                from ..engine.program import ProgramUnsupported
+                raise ProgramUnsupported("a rotating position encoding has no phase in the fused step")
+            self.positions.rotate(ctx, proj, self.n_heads, self.n_kv_heads, self.head_dim)
         k_pool, v_pool, group, g = ctx.cache.layer_pools(entry)
         table = ctx.tables[g]
         window = self.window or 0
         if owns_cache and not ctx.is_decode:
             kernels.kv_append(proj, self.q_width, self.q_width + self.kv_width, ctx.positions, ctx.token_seq,
                               ctx.ctx_len, table, group.table_len, k_pool, v_pool, n, self.n_kv_heads, self.head_dim)
-        program = getattr(ctx, "program", None)
         if program is not None and ctx.is_decode:
             # recorded as a phase of the fused step; its partial results are merged by the output projection
             mixed = program.add_attention(ctx, proj, k_pool, v_pool, table, group.table_len, n_heads=self.n_heads,

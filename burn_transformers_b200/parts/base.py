@@ -64,6 +64,12 @@ class PositionEncoding(Part):
     def max_positions(self) -> int | None:
         return None
 
+    def rotate(self, ctx, proj, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+        """For a kind with `rotates`: turns the query and key channels of the step's projections `proj`
+        ([tokens, (n_heads + 2 * n_kv_heads) * head_dim]: queries, keys, values) in place, each token by its own
+        position `ctx.positions`, angles in 32-bit.  A mixer calls this before it files the keys."""
+        raise NotImplementedError
+
 
 class Mixer(Part):
     accepts_lazy_norm = False   # True: `x` is only ever handed to parts.linear.linear

@@ -13,7 +13,8 @@ from burn_transformers_b200.cache import CacheBank, CacheConfig, CacheNeed, Stat
 from burn_transformers_b200.config import Architecture, ModelConfig, register_architecture, unregister_architecture
 from burn_transformers_b200.config.base import field
 from burn_transformers_b200.engine import LayerCall, ModelPlan, StepBuilder, StepEntry
-from burn_transformers_b200.parts import (CausalSelfAttention, DenseFeedForward, LayerNorm, LearnedPositions, Mixer,
+from burn_transformers_b200.parts import (CausalSelfAttention, DenseFeedForward, FeedForward, LayerNorm, LearnedPositions, Mixer,
+                                          PositionEncoding,
                                           PreNormBlock, TiedReadout, TokenEmbedding)
 from burn_transformers_b200.weights import MATRIX, TensorSpec, random_tensors
 from burn_transformers_b200.weights.spec import WeightPlan
@@ -278,3 +279,176 @@ def test_toy_architecture_with_a_stateful_mixer(tmp_path):
             engine.cache.check()
     finally:
         unregister_architecture("toy_running_mean")
+
+
+# ---- a second toy architecture: a position encoding that rotates, a windowed layer, a routed feed-forward ----
+
+class ToyRotation(PositionEncoding):
+    """Rotates pairs (2i, 2i + 1) of every query and key head by position * base^(-2i / head_dim); angles in
+    32-bit.  Defined here with torch operations: the framework only knows the `rotate` hook."""
+    rotates = True
+    graph_safe = False
+
+    def __init__(self, base: float):
+        self.base = base
+
+    def rotate(self, ctx, proj, n_heads, n_kv_heads, head_dim):
+        n = ctx.n_tokens
+        pos = ctx.positions[:n].to(torch.float32)
+        freq = self.base ** (-torch.arange(0, head_dim, 2, device=proj.device, dtype=torch.float32) / head_dim)
+        angle = pos[:, None] * freq[None, :]
+        cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+        heads = proj[:n, :(n_heads + n_kv_heads) * head_dim].view(n, n_heads + n_kv_heads, head_dim // 2, 2).to(torch.float32)
+        a, b = heads[..., 0], heads[..., 1]
+        turned = torch.stack((a * cos - b * sin, a * sin + b * cos), dim=-1)
+        proj[:n, :(n_heads + n_kv_heads) * head_dim] = turned.reshape(n, -1).to(proj.dtype)
+
+
+class ToyRoutedFeedForward(FeedForward):
+    """Every token goes to the one expert its router logit (32-bit) is largest for; an expert is up, GELU, down."""
+    graph_safe = False
+
+    def __init__(self, width, inner, experts):
+        self.width, self.inner, self.experts = width, inner, experts
+
+    def specs(self):
+        specs = {"router.weight": TensorSpec((self.width, self.experts), MATRIX, ("normal", 1.0))}
+        for e in range(self.experts):
+            specs[f"experts.{e}.up.weight"] = TensorSpec((self.width, self.inner), MATRIX, ("normal", 0.3))
+            specs[f"experts.{e}.down.weight"] = TensorSpec((self.inner, self.width), MATRIX, ("normal", 0.3))
+        return specs
+
+    def forward(self, ctx, x, residual):
+        n = ctx.n_tokens
+        rows = x[:n].float()
+        choice = (rows @ self.t_router_weight.float()).argmax(dim=1)
+        for e in range(self.experts):
+            mine = (choice == e).nonzero().flatten()
+            if mine.numel():
+                hidden = torch.nn.functional.gelu(rows[mine] @ getattr(self, f"t_experts_{e}_up_weight").float())
+                residual[mine] += hidden @ getattr(self, f"t_experts_{e}_down_weight").float()
+
+
+@dataclasses.dataclass
+class RoutedConfig(ModelConfig):
+    FAMILY: ClassVar[str] = "toy_routed"
+    MODEL_TYPES: ClassVar[tuple] = ("toy_routed",)
+    model_type: str = field("toy_routed")
+    vocab: int = field(40)
+    width: int = field(32)
+    heads: int = field(2)
+    kv_heads: int = field(1)
+    window: int = field(24)
+    experts: int = field(3)
+    rotary_base: float = field(100.0)
+    max_len: int = field(128)
+
+    def validate(self):
+        self._check_model_type(self.model_type)
+        self._check_extents(("vocab", "width", "heads", "kv_heads", "window", "experts", "max_len"))
+
+
+def build_routed(config: RoutedConfig) -> ModelPlan:
+    """Layer 0: rotated, windowed, grouped-head attention and a routed feed-forward.  Layer 1: plain attention over
+    all keys (no rotation) and a dense feed-forward: two groups of cache with different needs."""
+    emb = TokenEmbedding(config.vocab, config.width, 0.5)
+    rotation = ToyRotation(config.rotary_base)
+    final = LayerNorm(config.width, 1e-5)
+    hd = config.width // config.heads
+    mixers = [CausalSelfAttention(config.width, config.heads, config.kv_heads, hd, 0.3, window=config.window, bias=False,
+                                  init_std=0.4, positions=rotation),
+              CausalSelfAttention(config.width, config.heads, config.heads, hd, 0.3, bias=False, init_std=0.4)]
+    ffns = [ToyRoutedFeedForward(config.width, 2 * config.width, config.experts),
+            DenseFeedForward(config.width, 2 * config.width, "gelu", bias=False)]
+    names = {"embed.weight": (emb, "weight"), "final.weight": (final, "weight"), "final.bias": (final, "bias")}
+    blocks = []
+    for i in range(2):
+        n1, n2 = LayerNorm(config.width, 1e-5), LayerNorm(config.width, 1e-5)
+        blocks.append(PreNormBlock(n1, mixers[i], n2, ffns[i]))
+        for part_name, part in (("n1", n1), ("mixer", mixers[i]), ("n2", n2), ("ffn", ffns[i])):
+            for local in part.specs():
+                names[f"layers.{i}.{part_name}.{local}"] = (part, local)
+    return ModelPlan(config=config, embedding=emb, positions=rotation, blocks=blocks, schedule=[LayerCall(0), LayerCall(1)],
+                     final_norm=final, readout=TiedReadout(emb), names=names, vocab=config.vocab, width=config.width,
+                     max_context=config.max_len)
+
+
+def plain_routed(config, w, seq):
+    """The second toy model on a whole sequence in float64, written from its definition."""
+    s, d, heads, kvh = len(seq), config.width, config.heads, config.kv_heads
+    hd = d // heads
+    ln = lambda t, p: torch.nn.functional.layer_norm(t, (d,), w[p + ".weight"], w[p + ".bias"], 1e-5)
+    x = w["embed.weight"][seq]
+    pos = torch.arange(s, dtype=torch.float64)
+    freq = config.rotary_base ** (-torch.arange(0, hd, 2, dtype=torch.float64) / hd)
+    cos, sin = (pos[:, None] * freq).cos()[:, None, :], (pos[:, None] * freq).sin()[:, None, :]
+
+    def turn(t):                       # [s, h, hd]
+        a, b = t[..., 0::2], t[..., 1::2]
+        return torch.stack((a * cos - b * sin, a * sin + b * cos), dim=-1).reshape(t.shape)
+
+    for layer in range(2):
+        p = f"layers.{layer}."
+        n_kv = kvh if layer == 0 else heads
+        proj = ln(x, p + "n1") @ w[p + "mixer.qkv.weight"]
+        q = proj[:, :d].view(s, heads, hd)
+        k = proj[:, d:d + n_kv * hd].view(s, n_kv, hd)
+        v = proj[:, d + n_kv * hd:].view(s, n_kv, hd)
+        if layer == 0:
+            q, k = turn(q), turn(k)
+        hidden = torch.arange(s)[None, :] > torch.arange(s)[:, None]
+        if layer == 0:
+            hidden |= torch.arange(s)[None, :] <= torch.arange(s)[:, None] - config.window
+        out = torch.zeros(s, heads, hd, dtype=torch.float64)
+        for h in range(heads):
+            kh = h // (heads // n_kv)
+            out[:, h] = torch.softmax((q[:, h] @ k[:, kh].T * 0.3).masked_fill(hidden, -math.inf), -1) @ v[:, kh]
+        x = x + out.reshape(s, d) @ w[p + "mixer.out.weight"]
+        f = ln(x, p + "n2")
+        if layer == 0:
+            choice = (f @ w[p + "ffn.router.weight"]).argmax(dim=1)
+            for e in range(config.experts):
+                mine = (choice == e).nonzero().flatten()
+                x[mine] = x[mine] + torch.nn.functional.gelu(f[mine] @ w[p + f"ffn.experts.{e}.up.weight"]) \
+                    @ w[p + f"ffn.experts.{e}.down.weight"]
+        else:
+            x = x + torch.nn.functional.gelu(f @ w[p + "ffn.up.weight"]) @ w[p + "ffn.down.weight"]
+    return ln(x, "final") @ w["embed.weight"].T
+
+
+def test_toy_architecture_with_rotation_a_window_and_routed_experts(tmp_path):
+    """Parts the library does not have, defined here and registered without a change to its files: a position
+    encoding that turns queries and keys, a feed-forward that routes tokens to experts; the model's first layer keeps
+    a window of keys (a ring of pages) with shared key heads, its second all keys."""
+    register_architecture(Architecture("toy_routed", ("toy_routed",), RoutedConfig, build_routed), replace=True)
+    try:
+        config = RoutedConfig()
+        folder = bt.write_random_model(tmp_path, config, seed=8, storage="float32")
+        engine = bt.Engine.from_folder(folder, "float32", max_tokens=64 * 6)
+        assert not engine.plan.graph_safe
+        assert len(engine.cache.groups) == 2 and sorted(g.is_ring for g in engine.cache.groups) == [False, True]
+        import plain_gpt2
+        w = {k: torch.from_numpy(v).double() for k, v in plain_gpt2.read_safetensors(folder / "model.safetensors").items()}
+        rng = np.random.default_rng(1)
+        seqs = [rng.integers(0, config.vocab, n).tolist() for n in (90, 9, 40)]
+        want = [plain_routed(config, w, s) for s in seqs]
+        for round_ in range(2):
+            slots = [engine.new_sequence() for _ in seqs]
+            cut = [30, 1, 40]
+            got = engine.step([StepEntry(sl, s[:c], list(range(c))) for sl, s, c in zip(slots, seqs, cut)])
+            off = 0
+            for r, c in enumerate(cut):
+                assert rel(got[off:off + c], want[r][:c]) < 1e-4, (round_, r)
+                off += c
+            fed = list(cut)
+            while any(f < len(s) for f, s in zip(fed, seqs)):
+                live = [r for r in range(3) if fed[r] < len(seqs[r])]
+                got = engine.step([StepEntry(slots[r], [seqs[r][fed[r]]], [0]) for r in live])
+                for i, r in enumerate(live):
+                    assert rel(got[i], want[r][fed[r]]) < 1e-4, (round_, r, fed[r])
+                    fed[r] += 1
+            for sl in slots:
+                engine.release(sl)
+            engine.cache.check()
+    finally:
+        unregister_architecture("toy_routed")
