@@ -8,8 +8,10 @@
 // token selection.  Between phases the blocks meet at a grid barrier (an atomic counter; the launch is
 // cooperative, so all blocks are resident, and the spin is bounded: if it runs out every block records the
 // failure and returns).  Before it goes to the barrier a block already asks for what its next phase needs and
-// nobody writes during the step: its first weight tile (into registers), or its first pages of keys and values
-// (bulk copies into shared memory) -- so after the barrier the data is there.
+// nobody writes during the step: its first weight tiles (into registers) and the parameters of a LayerNorm, or
+// its pages of keys and values (tensor-map copies into shared memory) -- so after the barrier the data is there.
+// Attention is tensor-core work too (see the attention section below); the readout leaves per-block softmax
+// partials so that greedy selection does not read the logits again.
 //
 // Matrix products: a phase's output columns are dealt out in tiles of 8 to the blocks; the 8 warps of a block
 // split K, read their weights [N, K] straight into mma.sync B fragments (16 bytes per lane, see
