@@ -39,6 +39,9 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 // BT_NO_PDL=1 in the environment launches every kernel fully serialised (for measurements).
 bool pdl_enabled();
 
+// Streaming multiprocessors of the current device (looked up once per device); 0 if it cannot be read.
+int sm_count();
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               int cluster_x, Args... args) {

@@ -320,7 +320,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const TcParam
     configured = true;
   }
   const int n_tiles = ((p.N + BN - 1) / BN) * ((p.M + TC_BM - 1) / TC_BM);
-  const int blocks = n_tiles < 148 ? n_tiles : 148;     // one persistent block per SM
+  const int sms = sm_count() > 0 ? sm_count() : 148;
+  const int blocks = n_tiles < sms ? n_tiles : sms;     // one persistent block per SM
   kern<<<blocks, TC_THREADS, smem, stream>>>(ma, mw, p);
   BT_LAUNCH_OK("linear_tcgen05");
   return 0;

@@ -10,7 +10,14 @@ from ..weights.spec import MATRIX, VECTOR, TensorSpec
 from .base import Mixer
 from .linear import linear
 
-_SM_COUNT = 148
+_SM_COUNTS: dict = {}
+
+
+def _sm_count(device) -> int:
+    """Streaming multiprocessors of `device` (asked of the driver once)."""
+    if device not in _SM_COUNTS:
+        _SM_COUNTS[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNTS[device]
 
 
 class CausalSelfAttention(Mixer):
@@ -63,7 +70,7 @@ class CausalSelfAttention(Mixer):
         units = max(1, ctx.n_seqs * self.n_heads)
         span = ctx.ctx_bound if self.window is None else min(ctx.ctx_bound, self.window)
         pages = max(1, -(-span // PAGE_SIZE))
-        by_fill = -(-2 * _SM_COUNT // units)
+        by_fill = -(-2 * _sm_count(ctx.ws.device) // units)
         return int(max(1, min(by_fill, pages, 8)))
 
     def forward(self, ctx, x, residual, entry, owns_cache=True):
