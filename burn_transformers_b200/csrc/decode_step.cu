@@ -1187,11 +1187,12 @@ extern "C" long long bt_decode_step_smem_bytes(const void* phases_host, int n_ph
 
 // Which build of the kernel serves these phases (host copy of the program): 0 the general one, 1 products of 3 and
 // 12 blocks per warp (K in 513..768 and 1537..3072) with heads up to 64, 2 products of 4 blocks per warp and long
-// ones (K in 769..1024 and over 3072) with heads up to 64; both for greedy selection (or none) only.
+// ones (K in 769..1024 and over 3072) with heads up to 64; both for greedy selection (or none) only; 3 and 4: the
+// same two with the sampler.
 extern "C" int bt_decode_step_build(const void* phases_host, int n_phases) {
   using namespace bt;
   const Phase* ph = reinterpret_cast<const Phase*>(phases_host);
-  bool fits1 = true, fits2 = true;
+  bool fits1 = true, fits2 = true, samples = false;
   for (int i = 0; i < n_phases; ++i) {
     if (ph[i].type == PH_LINEAR) {
       const int pw = (((ph[i].K + 31) / 32) + DS_WARPS - 1) / DS_WARPS;
@@ -1201,10 +1202,10 @@ extern "C" int bt_decode_step_build(const void* phases_host, int n_phases) {
     } else if (ph[i].type == PH_ATTENTION && ph[i].head_dim > 64) {
       fits1 = fits2 = false;
     } else if (ph[i].type == PH_SAMPLE && (ph[i].do_sample || ph[i].partials == nullptr)) {
-      fits1 = fits2 = false;       // (those builds select greedily from the readout's partials and hold no sampler)
+      samples = true;              // (builds 1 and 2 select greedily from the readout's partials and hold no sampler)
     }
   }
-  return fits1 ? 1 : (fits2 ? 2 : 0);
+  return fits1 ? (samples ? 3 : 1) : (fits2 ? (samples ? 4 : 2) : 0);
 }
 
 // phases_dev: the program in device memory.  `build`: bt_decode_step_build of the program.  counter: one zero-initialised-per-launch unsigned (this call clears
@@ -1214,13 +1215,14 @@ extern "C" int bt_decode_step(const void* phases_dev, int n_phases, int build, l
                               int* status, long long* trace, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_phases >= 1 && smem_bytes <= 200 * 1024, "decode_step: %d phases need %lld bytes of shared memory", n_phases, smem_bytes);
-  BT_CHECK(build >= 0 && build <= 2, "decode_step: unknown build %d", build);
+  BT_CHECK(build >= 0 && build <= 4, "decode_step: unknown build %d", build);
   static int n_sms = 0;
-  static long long configured_all[3] = {-1, -1, -1};
+  static long long configured_all[5] = {-1, -1, -1, -1, -1};
   long long& configured = configured_all[build];
-  const void* kernel = build == 1 ? (const void*)decode_step_kernel<3, 12, 64, false>
-                                  : (build == 2 ? (const void*)decode_step_kernel<4, 0, 64, false>
-                                                : (const void*)decode_step_kernel<-1, -1, 128, true>);
+  const void* kernels[5] = {(const void*)decode_step_kernel<-1, -1, 128, true>, (const void*)decode_step_kernel<3, 12, 64, false>,
+                            (const void*)decode_step_kernel<4, 0, 64, false>, (const void*)decode_step_kernel<3, 12, 64, true>,
+                            (const void*)decode_step_kernel<4, 0, 64, true>};
+  const void* kernel = kernels[build];
   if (n_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
