@@ -19,6 +19,7 @@ import numpy as np
 import torch
 
 from .. import kernels
+from ..errors import KernelError
 from ..errors import GenerationError
 from .step import StepContext, Workspace
 
@@ -165,8 +166,14 @@ class DecodeGraph:
         """Runs the step on what the device copy of the integers holds.  The first call runs the kernels directly
         and then records them; later calls replay the recording."""
         if self.program is not None:
-            self.program.launch()
-            return self.logits
+            try:
+                self.program.launch()
+                return self.logits
+            except KernelError:
+                # the launch was refused (a cooperative launch needs every block resident at once, which a GPU that
+                # is shared with other work may not grant): this engine goes on with separate kernels
+                self.program = None
+                self._engine().use_fused_step = False
         if self.graph is not None:
             self.graph.replay()
             return self.logits

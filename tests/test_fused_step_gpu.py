@@ -132,3 +132,21 @@ def test_fused_and_separate_kernels_agree(case):
     scale = max(float(np.abs(r).max()) for r in ref)
     drift = max(float(np.abs(a[k] - b[k]).max()) for k in a) / scale
     assert drift < TOL_BF16
+
+
+def test_a_refused_launch_of_the_fused_step_falls_back_to_separate_kernels(case, monkeypatch):
+    """A cooperative launch can be refused (it needs every block resident at once).  The refusal is made here by hand
+    (the recorded program's launch raises): the engine goes on with a CUDA graph of separate kernels and gives the
+    same logits."""
+    from burn_transformers_b200 import KernelError
+    cfg, folder, seqs, ref = case
+    engine = Engine.from_folder(folder, "bfloat16", max_tokens=64 * 12)
+
+    def refuse(self, trace=None):
+        raise KernelError("decode_step: launch failed: too many blocks for a cooperative launch")
+
+    monkeypatch.setattr(step_program.DecodeProgram, "launch", refuse)
+    got = replay.tail_one_by_one(engine, seqs[:2], tail=5)
+    assert engine.use_fused_step is False and not fused_programs(engine)
+    err, where = replay.worst_error(got, ref)
+    assert err < TOL_BF16, f"after the refusal: {err:.3e} at {where}"
