@@ -191,6 +191,30 @@ def linear_skinny(a, w, bias, out, *, m, w_is_nk=False, activation=None, residua
                                       c_int(1 if out.dtype == torch.float32 else 0), c_int(split), _stream()))
 
 
+def linear_mid(a, w, bias, out, *, m, activation=None, residual=None, split=0):
+    """out[:m] = act(a[:m] @ w^T + bias) (+ residual) for at most 64 bfloat16 rows and weights stored [N, K]: the
+    shared-memory tile product made for 17 to 64 rows."""
+    n, k = w.shape
+    _need(w, "w", torch.bfloat16, (n, k))
+    _need(a, "a", torch.bfloat16, (None, k))
+    _need(out, "out", (torch.float32, torch.bfloat16), (None, n))
+    if a.shape[0] < m or out.shape[0] < m:
+        raise ShapeError(f"linear_mid: {m} rows asked of a[{a.shape[0]}], out[{out.shape[0]}]")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (n,))
+    if residual is not None:
+        _need(residual, "residual", torch.float32, (None, n))
+    if activation not in ACTIVATIONS:
+        raise ShapeError(f"linear_mid: unknown activation {activation!r}")
+    _check(library().bt_linear_mid(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), c_int(m), c_int(n), c_int(k),
+                                   c_int(ACTIVATIONS[activation]), c_int(1 if out.dtype == torch.float32 else 0),
+                                   c_int(split), _stream()))
+
+
+def linear_mid_supports(m, n, k) -> bool:
+    return _supports("bt_linear_mid_supports", m, n, k)
+
+
 _SUPPORTS: dict = {}
 
 
