@@ -42,8 +42,8 @@ int bt_attention_prefill_mma(const void* q, long long q_row_stride, const void* 
 long long bt_attention_decode_scratch_floats(int n_seqs, int n_heads, int head_dim, int n_splits);
 // out[M, N] = act(a[M, K] @ w[N, K]^T + bias) (+ residual) for at most 64 bfloat16 rows (made for 17..64).
 int bt_linear_mid_supports(int M, int N, int K);
-int bt_linear_mid(const void* a, const void* w, const float* bias, const float* residual, void* out, int M, int N, int K,
-                  int act, int out_is_f32, int split, cudaStream_t stream);
+int bt_linear_mid(const void* a, const void* w, const float* bias, const float* residual, void* out, int* status, int M, int N,
+                  int K, int act, int out_is_f32, int split, cudaStream_t stream);
 
 // Decode attention on tensor cores (bfloat16, head sizes 16..128 in steps of 16): arguments as bt_attention_decode,
 // plus the number of pages of the pools.

@@ -193,7 +193,8 @@ def linear_skinny(a, w, bias, out, *, m, w_is_nk=False, activation=None, residua
 
 def linear_mid(a, w, bias, out, *, m, activation=None, residual=None, split=0):
     """out[:m] = act(a[:m] @ w^T + bias) (+ residual) for at most 64 bfloat16 rows and weights stored [N, K]: the
-    shared-memory tile product made for 17 to 64 rows."""
+    product made for 17 to 64 rows (a block per 16 columns over the whole of K, operands through a ring of
+    tensor-map copies)."""
     n, k = w.shape
     _need(w, "w", torch.bfloat16, (n, k))
     _need(a, "a", torch.bfloat16, (None, k))
@@ -206,9 +207,9 @@ def linear_mid(a, w, bias, out, *, m, activation=None, residual=None, split=0):
         _need(residual, "residual", torch.float32, (None, n))
     if activation not in ACTIVATIONS:
         raise ShapeError(f"linear_mid: unknown activation {activation!r}")
-    _check(library().bt_linear_mid(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), c_int(m), c_int(n), c_int(k),
-                                   c_int(ACTIVATIONS[activation]), c_int(1 if out.dtype == torch.float32 else 0),
-                                   c_int(split), _stream()))
+    _check(library().bt_linear_mid(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), _ptr(kernel_status(a.device)),
+                                   c_int(m), c_int(n), c_int(k), c_int(ACTIVATIONS[activation]),
+                                   c_int(1 if out.dtype == torch.float32 else 0), c_int(split), _stream()))
 
 
 def linear_mid_supports(m, n, k) -> bool:
@@ -403,7 +404,8 @@ def kernel_status(device) -> torch.Tensor:
 _STATUS_TEXT = {1: "decode attention gave up waiting for a copy of cache pages",
                 2: "the tcgen05 matrix product gave up waiting for a stage of its pipeline",
                 3: "the fused decode step gave up at a grid barrier or waiting for cache pages",
-                4: "the fused decode step met a token id or position outside its table"}
+                4: "the fused decode step met a token id or position outside its table",
+                5: "the matrix product for 17 to 64 rows gave up waiting for a stage of its pipeline"}
 
 
 def check_status(device) -> None:

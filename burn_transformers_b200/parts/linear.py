@@ -32,9 +32,9 @@ def linear(ctx, a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=
     lazy = isinstance(a, LazyNorm)
     n = w.shape[0] if w_is_nk else w.shape[1]
     k = w.shape[1] if w_is_nk else w.shape[0]
-    if w.dtype == torch.bfloat16 and w_is_nk and 48 < m <= 64 and 2048 <= n < 8192 and k <= 1024 and kernels.linear_mid_supports(m, n, k):
-        # more than one 16-row tile: the shared-memory tile product (the weight-streaming kernels below spend an
-        # instruction stream per 16 rows)
+    if w.dtype == torch.bfloat16 and w_is_nk and 16 < m <= 64 and n < 8192 and kernels.linear_mid_supports(m, n, k):
+        # more than one 16-row tile: all rows of a block of 16 columns in one block, fed by tensor-map copies
+        # (the weight-streaming kernels below spend an instruction stream per 16 rows)
         if lazy:
             a = a.materialize(ctx)
         kernels.linear_mid(a, w, bias, out, m=m, activation=activation, residual=residual)

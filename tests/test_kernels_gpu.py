@@ -194,28 +194,49 @@ def test_linear_tcgen05(m, n, k):
 
 
 @pytest.mark.parametrize("m", [17, 33, 64])
-@pytest.mark.parametrize("n, k, split", [(768, 768, 0), (2304, 768, 4), (768, 3072, 8), (104, 240, 3), (200, 96, 0),
-                                         (777, 1600, 0), (1000, 72, 1), (64, 4096, 0)])
-def test_linear_mid(m, n, k, split):
-    """The shared-memory tile product for 17 to 64 rows: sizes that are no multiples of its tiles, every split."""
+@pytest.mark.parametrize("n, k", [(768, 768), (2304, 768), (768, 3072), (104, 240), (200, 96), (777, 1600), (1000, 72),
+                                  (64, 4096)])
+def test_linear_mid(m, n, k):
+    """The product for 17 to 64 rows: sizes that are no multiples of its tiles, K longer than its ring of stages."""
     a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
     bias, res = torch.randn(n, device=DEV), torch.randn(m, n, device=DEV)
     assert kernels.linear_mid_supports(m, n, k)
     product = a.double() @ w.double().T
     out = res.clone()
-    kernels.linear_mid(a, w, bias, out, m=m, activation="gelu_new", residual=out, split=split)
+    kernels.linear_mid(a, w, bias, out, m=m, activation="gelu_new", residual=out)
     want = torch.nn.functional.gelu(product + bias.double(), approximate="tanh") + res.double()
     assert rel(out, want) < 4 * math.sqrt(k) * 2.0 ** -24 + 1e-6
     low = torch.full((m + 2, n), 3.0, device=DEV, dtype=torch.bfloat16)
-    kernels.linear_mid(a, w, None, low, m=m, split=split)
+    kernels.linear_mid(a, w, None, low, m=m)
     assert rel(low[:m], product) < 4e-3 and float((low[m:].float() - 3.0).abs().max()) == 0.0
     # the same rows give the same result whatever else is in the call
     alone = torch.empty(1, n, device=DEV)
     both = torch.empty(m, n, device=DEV)
-    kernels.linear_mid(a[m - 1:].contiguous(), w, bias, alone, m=1, split=split)
-    kernels.linear_mid(a, w, bias, both, m=m, split=split)
+    kernels.linear_mid(a[m - 1:].contiguous(), w, bias, alone, m=1)
+    kernels.linear_mid(a, w, bias, both, m=m)
     assert torch.equal(alone[0], both[m - 1])
+    assert int(kernels.kernel_status(a.device)) == 0
+
+
+@pytest.mark.parametrize("split", [1, 2, 4, 8])
+@pytest.mark.parametrize("n, k", [(768, 3072), (1000, 72), (52, 1608)])
+def test_linear_mid_split_over_a_cluster(n, k, split):
+    """K cut over the blocks of a cluster (slices that end inside a stage, members without any k) gives the whole
+    sum, the same at every call."""
+    m = 41
+    a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    bias, res = torch.randn(n, device=DEV), torch.randn(m, n, device=DEV)
+    want = torch.nn.functional.gelu(a.double() @ w.double().T + bias.double(), approximate="tanh") + res.double()
+    outs = []
+    for _ in range(2):
+        out = res.clone()
+        kernels.linear_mid(a, w, bias, out, m=m, activation="gelu_new", residual=out, split=split)
+        outs.append(out)
+    assert rel(outs[0], want) < 4 * math.sqrt(k) * 2.0 ** -24 + 1e-6
+    assert torch.equal(outs[0], outs[1])
+    assert int(kernels.kernel_status(a.device)) == 0
 
 
 def test_linear_mid_refuses_what_it_cannot_do():
@@ -224,6 +245,10 @@ def test_linear_mid_refuses_what_it_cannot_do():
     with pytest.raises(KernelError, match="not supported"):
         kernels.linear_mid(torch.zeros(20, 100, device=DEV, dtype=torch.bfloat16),
                            torch.zeros(64, 100, device=DEV, dtype=torch.bfloat16), None, torch.zeros(20, 64, device=DEV), m=20)
+    with pytest.raises(KernelError, match="split"):
+        kernels.linear_mid(torch.zeros(20, 64, device=DEV, dtype=torch.bfloat16),
+                           torch.zeros(64, 64, device=DEV, dtype=torch.bfloat16), None, torch.zeros(20, 64, device=DEV), m=20,
+                           split=3)
 
 
 def test_linear_skinny_refuses_what_it_cannot_do():
