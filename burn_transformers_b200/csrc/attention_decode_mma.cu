@@ -1,10 +1,12 @@
 // Decode attention on tensor cores (bfloat16): one new token per sequence over that sequence's pages.
 //
-// grid (n_splits, n_heads, n_seqs), four warps a block.  A block owns a run of pages of one (sequence, head).  One
-// lane per page asks the tensor memory accelerator for them (a 64 x 64 box per tile, 128-byte swizzle) before the
-// kernel waits for its predecessor: old keys and values do not change during a step.  Each warp then takes 32- or
-// 16-key chunks of the landed pages by itself (scores and weighted values with mma.sync, the query as row 0 of
-// the 16-row tile, softmax in 32-bit); the warps are merged through shared memory and the splits of a
+// grid (n_splits, n_heads, n_seqs), four computing warps and a producer warp a block.  A block owns a run of pages
+// of one (sequence, head), which travel through a ring of slots in shared memory: the producer asks the tensor
+// memory accelerator for them (a 64 x 64 box per tile, 128-byte swizzle), the first ones before the kernel waits
+// for its predecessor (old keys and values do not change during a step), each further one when the warps that read
+// the slot have handed it back.  Each computing warp takes 32- or 16-key chunks of the landed pages by itself
+// (scores and weighted values with mma.sync, the query as row 0 of the 16-row tile, softmax in 32-bit); no
+// barrier of the whole block stands between pages.  The warps are merged through shared memory and the splits of a
 // (sequence, head) through distributed shared memory inside a thread-block cluster (at most 8 splits) or through
 // scratch memory, where the block that takes the last ticket merges.  Blocks are small (a few pages) so that many
 // are resident on an SM: a block is a chain of latencies, and it is the other blocks that hide them.
@@ -21,7 +23,8 @@ namespace cg = cooperative_groups;
 
 namespace bt {
 
-constexpr int DM_WARPS = 4;
+constexpr int DM_WARPS = 4;                     // warps that compute; one more warp asks for the pages
+constexpr int DM_THREADS = (DM_WARPS + 1) * 32;
 constexpr int DM_WAIT_LIMIT = 1 << 18;
 constexpr int DM_SMEM_BUDGET = 64 * 1024;      // for page slots: several blocks share an SM
 
@@ -46,11 +49,11 @@ struct DecodeMmaParams {
 };
 
 template <int I, int T>
-__global__ void __launch_bounds__(DM_WARPS * 32)
+__global__ void __launch_bounds__(DM_THREADS)
 attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, DecodeMmaParams p) {
   constexpr int CK = 8 * T, CPP = DS_PAGE / CK;
   extern __shared__ unsigned char dm_smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[16];
+  __shared__ __align__(8) unsigned long long full[16], empty[16];
   __shared__ float s_ml[DM_WARPS][2];
   __shared__ float c_ml[2];            // this block's (max, sum), read by its cluster peers
   __shared__ int s_flag;
@@ -77,40 +80,40 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   const int* table = p.table + (long long)seq * p.table_stride;
 
   if (tid == 0) {
-    for (int i = 0; i < p.slots; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ds_smem(&bars[i])));
+    for (int i = 0; i < p.slots; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ds_smem(&full[i])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(ds_smem(&empty[i])), "r"(CPP));
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     s_flag = 0;
   }
   __syncthreads();
-  // pages travel in waves of as many as there are slots; lane i of warp 0 asks for page i of a wave
-  auto issue_wave = [&](int w0) {
-    const int i = w0 + lane;
-    if (i < min(n_pages, w0 + p.slots)) {
-      const int slot = i % p.slots;
-      unsigned char* dst = ring + (size_t)slot * slot_bytes;
-      const unsigned bar = ds_smem(&bars[slot]);
-      const int page = table[(pg_first + i) % p.table_len];
-      const int row = (page * p.n_kv_heads + kv_head) * DS_PAGE;
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"((unsigned)slot_bytes) : "memory");
-      for (int cb = 0; cb < cbs; ++cb) {
-        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
-                         ds_smem(dst + cb * DS_PAGE * 128)),
-                     "l"(&k_map), "r"(cb * 64), "r"(row), "r"(bar)
-                     : "memory");
-        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
-                         ds_smem(dst + (cbs + cb) * DS_PAGE * 128)),
-                     "l"(&v_map), "r"(cb * 64), "r"(row), "r"(bar)
-                     : "memory");
-      }
+  // page i of the block's run travels into slot i % slots
+  auto ask = [&](int i, int page) {
+    const int slot = i % p.slots;
+    unsigned char* dst = ring + (size_t)slot * slot_bytes;
+    const unsigned bar = ds_smem(&full[slot]);
+    const int row = (page * p.n_kv_heads + kv_head) * DS_PAGE;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"((unsigned)slot_bytes) : "memory");
+    for (int cb = 0; cb < cbs; ++cb) {
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                       ds_smem(dst + cb * DS_PAGE * 128)),
+                   "l"(&k_map), "r"(cb * 64), "r"(row), "r"(bar)
+                   : "memory");
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                       ds_smem(dst + (cbs + cb) * DS_PAGE * 128)),
+                   "l"(&v_map), "r"(cb * 64), "r"(row), "r"(bar)
+                   : "memory");
     }
   };
-  if (warp == 0) issue_wave(0);
+  // the first pages at once, before the wait for the predecessor: old keys and values do not change during a step
+  if (warp == DM_WARPS && lane < min(n_pages, p.slots)) ask(lane, table[(pg_first + lane) % p.table_len]);
 
   pdl_wait();     // the projections of this step are complete from here on
   // the query and the new key and value come into shared memory
   {
     const int vecs = hd / 8, kinds = p.new_k ? 3 : 1;
-    for (int i = tid; i < kinds * vecs; i += DM_WARPS * 32) {
+    for (int i = tid; i < kinds * vecs; i += DM_THREADS) {
       const int r = i / vecs, c = i - r * vecs;
       const __nv_bfloat16* src = r == 0 ? p.q + (long long)seq * p.q_stride + head * hd
                                         : (r == 1 ? p.new_k : p.new_v) + (long long)seq * p.q_stride + kv_head * hd;
@@ -123,7 +126,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     const int pos = L - 1;
     const long long page = table[(pos / DS_PAGE) % p.table_len];
     const long long off = (page * p.n_kv_heads + kv_head) * (long long)(DS_PAGE * hd) + (long long)(pos % DS_PAGE) * hd;
-    for (int c = tid; c < hd / 8; c += DM_WARPS * 32) {
+    for (int c = tid; c < hd / 8; c += DM_THREADS) {
       *reinterpret_cast<uint4*>(p.k_pool + off + c * 8) = *reinterpret_cast<const uint4*>(rows + hd + c * 8);
       *reinterpret_cast<uint4*>(p.v_pool + off + c * 8) = *reinterpret_cast<const uint4*>(rows + 2 * hd + c * 8);
     }
@@ -140,33 +143,53 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   for (int n = 0; n < I * 4; ++n)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
-  bool ok = true;
-  for (int w0 = 0; w0 < n_pages; w0 += p.slots) {
-    if (w0 > 0) {            // everyone is done with the slots: the next wave can come
-      __syncthreads();
-      if (warp == 0) {
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        issue_wave(w0);
+  if (warp == DM_WARPS) {
+    // ---- the producer warp: each further page as soon as the warps that read its slot's last page have handed
+    // the slot back ----
+    bool dead = false;
+    for (int base = p.slots; base < n_pages; base += 32) {
+      const int mine = base + lane < n_pages ? table[(pg_first + base + lane) % p.table_len] : 0;
+      const int n = min(32, n_pages - base);
+      for (int j = 0; j < n; ++j) {
+        const int page = __shfl_sync(0xffffffffu, mine, j), i = base + j;
+        if (lane == 0 && !dead) {
+          const unsigned parity = (unsigned)(i / p.slots - 1) & 1u;
+          bool freed = false;
+          for (int t = 0; t < DM_WAIT_LIMIT && !freed; ++t) {
+            unsigned done;
+            asm volatile(
+                "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                : "=r"(done) : "r"(ds_smem(&empty[i % p.slots])), "r"(parity) : "memory");
+            freed = done != 0;
+          }
+          if (freed) {
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            ask(i, page);
+          } else {
+            dead = true;      // the warps that wait for this page give up by themselves and report it
+          }
+        }
       }
     }
-    const int c_lo = w0 * CPP, c_hi = min(n_pages, w0 + p.slots) * CPP;
-    for (int c = c_lo + ((warp - c_lo) & (DM_WARPS - 1)); c < c_hi; c += DM_WARPS) {
-      const int i = c / CPP, h = c % CPP;
-      const int key0 = (pg_first + i) * DS_PAGE + h * CK;
-      if (key0 >= hi || key0 + CK <= lo) continue;
-      const int slot = i % p.slots;
-      unsigned char* Kt = ring + (size_t)slot * slot_bytes;
-      const unsigned Ks = ds_smem(Kt), Vs = Ks + (unsigned)(cbs * DS_PAGE * 128);
-      const unsigned parity = (unsigned)(i / p.slots) & 1u;
-      bool landed = false;
-      for (int t = 0; t < DM_WAIT_LIMIT && !landed; ++t) {
-        unsigned done;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(done) : "r"(ds_smem(&bars[slot])), "r"(parity) : "memory");
-        landed = done != 0;
-      }
-      if (!landed) ok = false;
+  }
+  bool ok = true;
+  for (int c = warp; c < n_pages * CPP && warp < DM_WARPS; c += DM_WARPS) {
+    const int i = c / CPP, h = c % CPP;
+    const int key0 = (pg_first + i) * DS_PAGE + h * CK;
+    const int slot = i % p.slots;
+    unsigned char* Kt = ring + (size_t)slot * slot_bytes;
+    const unsigned Ks = ds_smem(Kt), Vs = Ks + (unsigned)(cbs * DS_PAGE * 128);
+    const unsigned parity = (unsigned)(i / p.slots) & 1u;
+    bool landed = false;      // (a chunk outside the range waits as well: a slot is handed back once per use by each reader)
+    for (int t = 0; t < DM_WAIT_LIMIT && !landed; ++t) {
+      unsigned done;
+      asm volatile(
+          "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+          : "=r"(done) : "r"(ds_smem(&full[slot])), "r"(parity) : "memory");
+      landed = done != 0;
+    }
+    if (!landed) ok = false;
+    if (key0 < hi && key0 + CK > lo) {
       if (p.new_k && L - 1 >= key0 && L - 1 < key0 + CK) {
         // the newest key and value are not in their page yet (or only just): they come from the projections.
         // (No other warp touches this chunk's rows; the rows beyond are masked and hold old, finite numbers.)
@@ -180,12 +203,16 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       }
       ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, p.scale_log2, m, l, acc);
     }
+    if (i + p.slots < n_pages) {      // the slot's next page may come
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(ds_smem(&empty[slot])) : "memory");
+    }
   }
   if (!ok) s_flag = 1;
   // the four lanes of a row each summed their own keys' weights; lane q of row 0 holds dims 8 n + 2 q + {0, 1}
   l += __shfl_xor_sync(0xffffffffu, l, 1);
   l += __shfl_xor_sync(0xffffffffu, l, 2);
-  if (g == 0) {
+  if (g == 0 && warp < DM_WARPS) {
 #pragma unroll
     for (int n = 0; n < I * 4; ++n) {
       const int d = 8 * n + 2 * q;
@@ -211,7 +238,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   }
   if (block_failed) Lsum = NAN;        // a result that cannot be mistaken for a good one
   const long long unit = (long long)seq * p.n_heads + head;
-  for (int c = tid; c < hd; c += DM_WARPS * 32) {
+  for (int c = tid; c < hd; c += DM_THREADS) {
     float o = 0.f;
 #pragma unroll
     for (int w = 0; w < DM_WARPS; ++w) o += s_acc[w * hd + c] * wg[w];
@@ -247,7 +274,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       Lall += wj[j] != 0.f || pl[j] != pl[j] ? pl[j] * wj[j] : 0.f;
     }
     // rank r finishes the channels c with c % n_splits == r
-    for (int c = split + tid * n_splits; c < hd; c += DM_WARPS * 32 * n_splits) {
+    for (int c = split + tid * n_splits; c < hd; c += DM_THREADS * n_splits) {
       float o = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j)
@@ -276,7 +303,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     const float ms = __ldcg(&p.part_ml[(unit * n_splits + s2) * 2]);
     if (ms != -INFINITY) Lall += __ldcg(&p.part_ml[(unit * n_splits + s2) * 2 + 1]) * ds_exp2(ms - Mx);
   }
-  for (int c = tid; c < hd; c += DM_WARPS * 32) {
+  for (int c = tid; c < hd; c += DM_THREADS) {
     float o = 0.f;
     for (int s2 = 0; s2 < n_splits; ++s2) {
       const float ms = __ldcg(&p.part_ml[(unit * n_splits + s2) * 2]);
@@ -304,7 +331,7 @@ static int launch_decode_mma(const CUtensorMap& km, const CUtensorMap& vm, Decod
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   BT_CHECK(e == cudaSuccess, "attention_decode: cannot reserve %zu bytes of shared memory", smem);
   const int cluster = p.use_cluster ? n_splits : 1;
-  BT_PDL_OK("attention_decode_mma", launch_pdl(kern, dim3(n_splits, p.n_heads, n_seqs), dim3(DM_WARPS * 32), smem, stream, cluster, km, vm, p));
+  BT_PDL_OK("attention_decode_mma", launch_pdl(kern, dim3(n_splits, p.n_heads, n_seqs), dim3(DM_THREADS), smem, stream, cluster, km, vm, p));
   return 0;
 }
 
