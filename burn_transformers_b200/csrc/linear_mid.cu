@@ -26,9 +26,10 @@ namespace bt {
 
 constexpr int LM_WARPS = 4;                           // consumer warps (16 rows each); one more warp produces
 constexpr int LM_THREADS = (LM_WARPS + 1) * 32;
-constexpr int LM_BM = 64, LM_BN = 16, LM_BK = 64;     // rows, columns, k of one stage
-constexpr int LM_STAGES = 8;
-constexpr int LM_A_BYTES = LM_BM * LM_BK * 2, LM_W_BYTES = LM_BN * LM_BK * 2;
+constexpr int LM_BM = 64, LM_BK = 64;                 // rows and k of one stage; its columns BN are 16 or 64
+constexpr int LM_MAX_STAGES = 8;
+constexpr int LM_A_BYTES = LM_BM * LM_BK * 2;
+constexpr int lm_stages(int bn) { return bn == 16 ? 8 : 6; }
 constexpr int LM_WAIT_LIMIT = 1 << 20;
 
 struct MidParams {
@@ -68,18 +69,21 @@ __device__ __forceinline__ void lm_tma(void* dst, const CUtensorMap* map, int co
                : "memory");
 }
 
+template <int LM_BN>
 __global__ void __launch_bounds__(LM_THREADS)
 linear_mid_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, MidParams p) {
+  constexpr int LM_STAGES = lm_stages(LM_BN), LM_W_BYTES = LM_BN * LM_BK * 2;
   extern __shared__ unsigned char lm_smem_raw[];
-  __shared__ __align__(8) unsigned long long full[LM_STAGES], empty[LM_STAGES];
+  __shared__ __align__(8) unsigned long long full[LM_MAX_STAGES], empty[LM_MAX_STAGES];
   __shared__ int failed;
-  __shared__ __align__(16) float part[LM_BM * LM_BN];      // this block's partial sums, read by its cluster peers
   pdl_trigger();
   cg::cluster_group cluster = cg::this_cluster();
   const int split = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n0 = blockIdx.y * LM_BN;
-  unsigned char* tiles = lm_smem_raw + ((1024u - (lm_smem(lm_smem_raw) & 1023u)) & 1023u);     // [stage][A 8 KB | W 2 KB]
+  unsigned char* tiles = lm_smem_raw + ((1024u - (lm_smem(lm_smem_raw) & 1023u)) & 1023u);     // [stage][A 8 KB | W]
+  // behind the ring, in a cluster only: this block's partial sums [64][BN], read by its cluster peers
+  float* part = reinterpret_cast<float*>(tiles + (size_t)LM_STAGES * (LM_A_BYTES + LM_W_BYTES));
   const int k_begin = rank * p.k_slice, k_end = min(p.K, k_begin + p.k_slice);
   const int k_blocks = k_end > k_begin ? (k_end - k_begin + LM_BK - 1) / LM_BK : 0;
   if (tid == 0) {
@@ -120,9 +124,9 @@ linear_mid_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   } else {
     // ---- consumers: warp w owns rows 16 w .. 16 w + 15 and the block's 16 columns ----
     pdl_wait();
-    float acc[2][4];
+    float acc[LM_BN / 8][4];
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int j = 0; j < LM_BN / 8; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
     // ldmatrix.x4: lane L gives the address of row L % 8 of block L / 8.  A: blocks (rows 0-7 | 8-15) x (k 0-7 | 8-15);
@@ -139,11 +143,15 @@ linear_mid_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       const unsigned a_base = lm_smem(tiles + (size_t)s * (LM_A_BYTES + LM_W_BYTES)), w_base = a_base + LM_A_BYTES;
 #pragma unroll
       for (int ks = 0; ks < LM_BK / 16; ++ks) {
-        unsigned af[4], bf[4];
+        unsigned af[4];
         lm_ldmatrix_x4(af, a_base + lm_swizzled(warp * 16 + (blk & 1) * 8 + r8, ks * 2 + (blk >> 1)));
-        lm_ldmatrix_x4(bf, w_base + lm_swizzled((blk >> 1) * 8 + r8, ks * 2 + (blk & 1)));
-        lm_mma(acc[0], af[0], af[1], af[2], af[3], bf[0], bf[1]);
-        lm_mma(acc[1], af[0], af[1], af[2], af[3], bf[2], bf[3]);
+#pragma unroll
+        for (int nb = 0; nb < LM_BN / 16; ++nb) {
+          unsigned bf[4];
+          lm_ldmatrix_x4(bf, w_base + lm_swizzled(nb * 16 + (blk >> 1) * 8 + r8, ks * 2 + (blk & 1)));
+          lm_mma(acc[2 * nb], af[0], af[1], af[2], af[3], bf[0], bf[1]);
+          lm_mma(acc[2 * nb + 1], af[0], af[1], af[2], af[3], bf[2], bf[3]);
+        }
       }
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(lm_smem(&empty[s])) : "memory");
@@ -153,13 +161,13 @@ linear_mid_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (split > 1) {
       // (a block that failed leaves NaN, which its peers' sums keep)
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+      for (int j = 0; j < LM_BN / 8; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e)
           part[(warp * 16 + g + (e >> 1) * 8) * LM_BN + j * 8 + 2 * q + (e & 1)] = ok ? acc[j][e] : NAN;
     } else if (ok) {
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+      for (int j = 0; j < LM_BN / 8; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int r = warp * 16 + g + (e >> 1) * 8, col = n0 + j * 8 + 2 * q + (e & 1);
@@ -220,11 +228,13 @@ extern "C" int bt_linear_mid(const void* a, const void* w, const float* bias, co
   BT_CHECK(bt_linear_mid_supports(M, N, K), "linear_mid: sizes M=%d N=%d K=%d are not supported", M, N, K);
   BT_CHECK(act >= 0 && act <= 2, "linear_mid: unknown activation %d", act);
   BT_CHECK(!(residual && !out_is_f32), "linear_mid: a residual needs a 32-bit output");
-  const int n_tiles = (N + LM_BN - 1) / LM_BN;
+  // wide outputs (a readout) take 64 columns a block, so that the rows are read from L2 a quarter as often
+  const int bn = N >= 8192 ? 64 : 16;
+  const int n_tiles = (N + bn - 1) / bn;
   const int rows16 = (M + 15) / 16 * 16;
   CUtensorMap ma, mw;
   if (int rc = tensor_map_2d_bf16(&ma, a, (unsigned long long)M, (unsigned long long)K, (unsigned long long)K, rows16)) return rc;
-  if (int rc = tensor_map_2d_bf16(&mw, w, (unsigned long long)N, (unsigned long long)K, (unsigned long long)K, LM_BN)) return rc;
+  if (int rc = tensor_map_2d_bf16(&mw, w, (unsigned long long)N, (unsigned long long)K, (unsigned long long)K, bn)) return rc;
   const int k_blocks = (K + LM_BK - 1) / LM_BK;
   if (split <= 0) {
     split = 1;
@@ -234,14 +244,19 @@ extern "C" int bt_linear_mid(const void* a, const void* w, const float* bias, co
   BT_CHECK(split == 1 || split == 2 || split == 4 || split == 8, "linear_mid: split %d is not 1, 2, 4 or 8", split);
   const int k_slice = (k_blocks + split - 1) / split * LM_BK;
   MidParams p{bias, residual, out, status, M, N, K, k_slice, act, out_is_f32, rows16};
-  const size_t smem = (size_t)LM_STAGES * (LM_A_BYTES + LM_W_BYTES) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(linear_mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    BT_CHECK(e == cudaSuccess, "linear_mid: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    configured = true;
-  }
   BT_CHECK(n_tiles <= 65535, "linear_mid: N=%d needs too many column tiles", N);
-  BT_PDL_OK("linear_mid", launch_pdl(linear_mid_kernel, dim3(split, n_tiles), dim3(LM_THREADS), smem, stream, split, ma, mw, p));
-  return 0;
+  auto launch = [&](auto kernel, int bn_) -> int {
+    const size_t smem = (size_t)lm_stages(bn_) * (LM_A_BYTES + bn_ * LM_BK * 2) + 1024 + (split > 1 ? (size_t)LM_BM * bn_ * 4 : 0);
+    static bool configured[2] = {false, false};
+    if (!configured[bn_ == 64]) {
+      const size_t most = (size_t)lm_stages(bn_) * (LM_A_BYTES + bn_ * LM_BK * 2) + 1024 + (size_t)LM_BM * bn_ * 4;
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
+      BT_CHECK(e == cudaSuccess, "linear_mid: cannot reserve %zu bytes of shared memory: %s", most, cudaGetErrorString(e));
+      configured[bn_ == 64] = true;
+    }
+    BT_PDL_OK("linear_mid", launch_pdl(kernel, dim3(split, n_tiles), dim3(LM_THREADS), smem, stream, split, ma, mw, p));
+    return 0;
+  };
+  if (bn == 64) return launch(linear_mid_kernel<64>, 64);
+  return launch(linear_mid_kernel<16>, 16);
 }

@@ -32,7 +32,7 @@ def linear(ctx, a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=
     lazy = isinstance(a, LazyNorm)
     n = w.shape[0] if w_is_nk else w.shape[1]
     k = w.shape[1] if w_is_nk else w.shape[0]
-    if w.dtype == torch.bfloat16 and w_is_nk and 16 < m <= 64 and n < 8192 and kernels.linear_mid_supports(m, n, k):
+    if w.dtype == torch.bfloat16 and w_is_nk and 16 < m <= 64 and kernels.linear_mid_supports(m, n, k):
         # more than one 16-row tile: all rows of a block of 16 columns in one block, fed by tensor-map copies
         # (the weight-streaming kernels below spend an instruction stream per 16 rows)
         if lazy:

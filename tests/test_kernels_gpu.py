@@ -195,7 +195,7 @@ def test_linear_tcgen05(m, n, k):
 
 @pytest.mark.parametrize("m", [17, 33, 64])
 @pytest.mark.parametrize("n, k", [(768, 768), (2304, 768), (768, 3072), (104, 240), (200, 96), (777, 1600), (1000, 72),
-                                  (64, 4096)])
+                                  (64, 4096), (8237, 136)])
 def test_linear_mid(m, n, k):
     """The product for 17 to 64 rows: sizes that are no multiples of its tiles, K longer than its ring of stages."""
     a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
