@@ -337,15 +337,50 @@ def attention_prefill_simt(q_proj, out, seq_start, past_len, n_seqs, max_new, n_
         c_int(_code(q_proj.dtype)), _stream()))
 
 
-def attention_prefill(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale, **kw):
-    """Attention of several new tokens per sequence: on tensor cores for bfloat16 and the head sizes that kernel is
-    built for, else with the plain 32-bit kernel.  Arguments as attention_prefill_simt."""
+def attention_prefill(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale, *,
+                      impl=None, **kw):
+    """Attention of several new tokens per sequence.  bfloat16 with a head size the kernels are built for runs on
+    tensor cores (tcgen05 with the scores in tensor memory, else mma.sync), everything else with the plain 32-bit
+    kernel.  `impl` ("tcgen05", "mma", "simt") asks for one kernel by name.  Arguments as attention_prefill_simt."""
     lib = library()
-    if q_proj.dtype == torch.bfloat16 and _supports("bt_attention_prefill_mma_supports", head_dim, PAGE_SIZE):
+    bf16 = q_proj.dtype == torch.bfloat16
+    if impl is None:
+        if bf16 and _supports("bt_attention_prefill_tcgen05_supports", head_dim, PAGE_SIZE):
+            impl = "tcgen05"
+        elif bf16 and _supports("bt_attention_prefill_mma_supports", head_dim, PAGE_SIZE):
+            impl = "mma"
+        else:
+            impl = "simt"
+    if impl == "tcgen05":
+        return _attention_prefill_tcgen05(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads,
+                                          head_dim, scale, **kw)
+    if impl == "mma":
         return _attention_prefill_call(lib.bt_attention_prefill_mma, False, q_proj, out, seq_start, past_len, n_seqs,
                                        max_new, n_heads, n_kv_heads, head_dim, scale, **kw)
     return attention_prefill_simt(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim,
                                   scale, **kw)
+
+
+def _attention_prefill_tcgen05(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale,
+                               *, causal=True, window=0, k_pool=None, v_pool=None, table=None, table_len=0,
+                               k_offset=None, v_offset=None):
+    _need(q_proj, "q_proj", torch.bfloat16)
+    _need(out, "out", torch.bfloat16, (None, n_heads * head_dim))
+    stride = q_proj.shape[1]
+    if table is None:
+        k_ptr = c_void_p(q_proj.data_ptr() + k_offset * 2)
+        v_ptr = c_void_p(q_proj.data_ptr() + v_offset * 2)
+        t_ptr, t_stride, pages = c_void_p(0), 0, 0
+    else:
+        _need(k_pool, "k_pool", torch.bfloat16)
+        _need(v_pool, "v_pool", torch.bfloat16)
+        _need(table, "table", torch.int32)
+        k_ptr, v_ptr, t_ptr, t_stride, pages = _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0]
+    _check(library().bt_attention_prefill_tcgen05(
+        _ptr(q_proj), c_longlong(q_proj.shape[0]), c_longlong(stride), k_ptr, v_ptr, c_longlong(pages), t_ptr,
+        c_int(t_stride), c_int(table_len), c_int(PAGE_SIZE), _ptr(out), _ptr(kernel_status(q_proj.device)),
+        _ptr(seq_start), _ptr(past_len), c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv_heads),
+        c_int(head_dim), c_float(scale), c_int(1 if causal else 0), c_int(window), _stream()))
 
 
 def _attention_prefill_call(fn, with_dtype, q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads,
@@ -405,7 +440,9 @@ _STATUS_TEXT = {1: "decode attention gave up waiting for a copy of cache pages",
                 2: "the tcgen05 matrix product gave up waiting for a stage of its pipeline",
                 3: "the fused decode step gave up at a grid barrier or waiting for cache pages",
                 4: "the fused decode step met a token id or position outside its table",
-                5: "the matrix product for 17 to 64 rows gave up waiting for a stage of its pipeline"}
+                5: "the matrix product for 17 to 64 rows gave up waiting for a stage of its pipeline",
+                6: "the tcgen05 prefill attention gave up waiting for a stage of its pipeline (or found its shared memory "
+                   "misaligned)"}
 
 
 def check_status(device) -> None:

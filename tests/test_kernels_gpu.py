@@ -423,6 +423,57 @@ def test_attention_prefill_packed_and_paged(dtype, hq, hkv, hd, window, causal):
         assert rel(got, want) < TOL[dtype] * 2, f"paged, sequence {s}"
 
 
+@pytest.mark.parametrize("impl", ["tcgen05", "mma"])
+@pytest.mark.parametrize("hq, hkv, hd, window, causal", [(3, 3, 64, 0, True), (4, 2, 64, 150, True), (2, 1, 128, 0, True),
+                                                         (2, 2, 128, 300, True), (2, 2, 64, 0, False)])
+def test_attention_prefill_long_sequences_on_tensor_cores(impl, hq, hkv, hd, window, causal):
+    """Both tensor-core kernels by name, over sequences of several key tiles (stages of the pipeline are used
+    again), lengths at and beside the tile edges, packed and paged."""
+    dtype = torch.bfloat16
+    news = [700, 129, 128, 1, 257]
+    width = (hq + 2 * hkv) * hd
+    n_tok = sum(news)
+    proj = torch.randn(n_tok, width, device=DEV).to(dtype)
+    seq_start = torch.tensor([0] + list(np.cumsum(news)), dtype=torch.int32, device=DEV)
+    out = torch.full((n_tok, hq * hd), 7.0, device=DEV, dtype=dtype)
+    scale = 0.2
+    kernels.attention_prefill(proj, out, seq_start, torch.zeros(len(news), dtype=torch.int32, device=DEV),
+                              len(news), max(news), hq, hkv, hd, scale, causal=causal, window=window,
+                              k_offset=hq * hd, v_offset=(hq + hkv) * hd, impl=impl)
+    assert int(kernels.kernel_status(proj.device)) == 0
+    p64 = proj.double().cpu()
+    for s, n in enumerate(news):
+        rows = p64[int(seq_start[s]):int(seq_start[s]) + n]
+        q = rows[:, :hq * hd].view(n, hq, hd)
+        k = rows[:, hq * hd:(hq + hkv) * hd].view(n, hkv, hd)
+        v = rows[:, (hq + hkv) * hd:].view(n, hkv, hd)
+        want = attend(q, k, v, scale, torch.arange(n), window, causal)
+        got = out[int(seq_start[s]):int(seq_start[s]) + n].view(n, hq, hd)
+        assert rel(got, want) < TOL[dtype] * 2, f"packed, sequence {s}"
+    if not causal or window:
+        return
+    pasts = [100, 64, 3, 500, 0]
+    lengths = [p + n for p, n in zip(pasts, news)]
+    k_pool, v_pool, table, dk, dv = make_paged(lengths, hkv, hd, dtype)
+    positions = torch.cat([torch.arange(p, p + n) for p, n in zip(pasts, news)]).to(torch.int32).to(DEV)
+    token_seq = torch.cat([torch.full((n,), s) for s, n in enumerate(news)]).to(torch.int32).to(DEV)
+    ctx_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    kernels.kv_append(proj, hq * hd, (hq + hkv) * hd, positions, token_seq, ctx_len, table, table.shape[1], k_pool,
+                      v_pool, n_tok, hkv, hd)
+    out.fill_(7.0)
+    kernels.attention_prefill(proj, out, seq_start, torch.tensor(pasts, dtype=torch.int32, device=DEV),
+                              len(news), max(news), hq, hkv, hd, scale, causal=True, window=window,
+                              k_pool=k_pool, v_pool=v_pool, table=table, table_len=table.shape[1], impl=impl)
+    assert int(kernels.kernel_status(proj.device)) == 0
+    for s, n in enumerate(news):
+        rows = p64[int(seq_start[s]):int(seq_start[s]) + n]
+        k = torch.cat([dk[s][:pasts[s]], rows[:, hq * hd:(hq + hkv) * hd].view(n, hkv, hd)])
+        v = torch.cat([dv[s][:pasts[s]], rows[:, (hq + hkv) * hd:].view(n, hkv, hd)])
+        want = attend(rows[:, :hq * hd].view(n, hq, hd), k, v, scale, torch.arange(pasts[s], pasts[s] + n), window)
+        got = out[int(seq_start[s]):int(seq_start[s]) + n].view(n, hq, hd)
+        assert rel(got, want) < TOL[dtype] * 2, f"paged, sequence {s}"
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hd", [32, 64])
 def test_attention_prefill_never_looks_ahead(dtype, hd):
