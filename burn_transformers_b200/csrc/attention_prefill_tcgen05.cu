@@ -2,15 +2,22 @@
 // tensor cores: both products of a tile, S = Q K^T and O += P V, are tcgen05.mma with accumulators in tensor
 // memory (TMEM); the S x S score plane is never stored.
 //
-// A block owns 128 queries of one (sequence, head) and walks over that sequence's keys in tiles of 128.
-//   warps 0-3  softmax: thread r owns query row r, which is TMEM lane r.  It reads its row of S with tcgen05.ld,
-//              keeps the running maximum and sum in 32-bit (scores in base 2), writes P = exp2(S - max) as
+// A block (one per multiprocessor) owns 128 queries of one (sequence, head) and walks over that sequence's keys in
+// tiles of 128.
+//   warps 0-7  softmax: query row r is TMEM lane r, and two threads share it (a warp reaches the lanes of quarter
+//              warp % 4; warps 0-3 take keys 0-63 of a tile and the lower half of the output channels, warps 4-7
+//              the rest).  A thread reads its part of S with tcgen05.ld, the pair agree on the row's maximum through
+//              shared memory, keep running maximum and sum in 32-bit (scores in base 2), write P = exp2(S - max) as
 //              bfloat16 into shared memory in the layout the tensor core reads (K-major, 128-byte swizzle), then
-//              adds the tile's P V, read from TMEM, to its row of the output, which lives in registers;
-//   warp 4     one lane asks the tensor memory accelerator (TMA) for the queries once and for each tile's keys and
-//              values (64 x 64 boxes, 128-byte swizzle): two stages of keys, one of values;
-//   warp 5     one lane issues the products: S = Q K^T (both operands K-major) when a tile has landed, O_tile = P V
-//              (P K-major, V as it lies in memory: "MN-major", head channels contiguous) when P is written.
+//              add the tile's P V, read from TMEM, to their part of the row of the output, which lives in registers;
+//   warp 8     one lane asks the tensor memory accelerator (TMA) for the queries once and for each tile's keys and
+//              values (64 x 64 boxes, 128-byte swizzle) into two stages each;
+//   warp 9     one lane issues the products: S = Q K^T (both operands K-major) into one of two accumulators, so that
+//              the next tile's scores are computed while this tile's are weighed, and O_tile = P V (P K-major, V as
+//              it lies in memory: "MN-major", head channels contiguous) when P is written.  P and O_tile are
+//              double too: the softmax warps take a tile's P V only after they have written the next tile's P, so
+//              that the product runs while they compute.
+// Blocks are numbered by falling length (every sequence and head of the last query tile first).
 // Keys and values come either from the rows of the step's own projections (sequences that start at position 0)
 // or from the pages of the cache (a page is one 64-row box).  Query t of sequence s sits at position
 // past[s] + (t - seq_start[s]); key j is visible when j <= position (causal) and j > position - window
@@ -25,9 +32,9 @@
 namespace bt {
 
 constexpr int TA_BQ = 128, TA_BK = 128;
-constexpr int TA_SOFTMAX_WARPS = 4;
+constexpr int TA_SOFTMAX_WARPS = 8;              // two threads per query row
 constexpr int TA_THREADS = (TA_SOFTMAX_WARPS + 2) * 32;
-constexpr int TA_STAGES = 2;
+constexpr int TA_STAGES = 2;                     // (the issuer's code is written out for two)
 constexpr int TA_WAIT_LIMIT = 1 << 22;
 constexpr int TA_BOX_BYTES = 64 * 128;            // a 64-row x 64-column bfloat16 box
 
@@ -144,52 +151,54 @@ __device__ __forceinline__ unsigned ta_pack(float lo, float hi) {
 __device__ __forceinline__ void ta_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void ta_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 
-// Tensor-memory columns of a block: S (128) and the tile's P V (HD), rounded up to a power of two.
-template <int HD>
-constexpr int ta_tmem_cols() { return TA_BK + HD <= 256 ? 256 : 512; }
+// Tensor memory of a block: two S accumulators (2 x 128 columns) and the tile's P V (HD columns): 512 columns, the
+// whole of a multiprocessor's, which one block has to itself.
+constexpr int TA_TMEM_COLS = 512;
 
 // Shared memory (the dynamic region, which must start on a 1024-byte boundary):
 //   Q      [HD / 64][128 rows][128 bytes]
-//   K      [stage][HD / 64][128 keys][128 bytes]      (two stages: the next tile's keys land while this one is weighed)
-//   V      [HD / 64][128 keys][128 bytes]             (one: it is free again long before the next P is written)
-//   P      [2][128 rows][128 bytes]    (keys 0-63 | 64-127 of the tile)
+//   K, V   [stage][HD / 64][128 keys][128 bytes] each, two stages
+//   P      [tile parity][2][128 rows][128 bytes]    (keys 0-63 | 64-127 of the tile)
+//   the row maxima the two threads of a row exchange [tile parity][2 halves][128] (at the end: their sums)
 //   barriers, the tensor-memory address, the failure flag
-// With head size 64 that is 96 KB, so that two blocks share a multiprocessor (and its 512 tensor-memory columns).
 template <int HD>
 constexpr size_t ta_smem_bytes() {
-  return (size_t)(HD / 64) * 2 * TA_BOX_BYTES * (2 + TA_STAGES) + 2 * 2 * TA_BOX_BYTES + 128;
+  return (size_t)(HD / 64) * 2 * TA_BOX_BYTES * (1 + 2 * TA_STAGES) + 2 * 2 * 2 * TA_BOX_BYTES + 4 * 128 * 4 + 256;
 }
 
 template <int HD>
-__global__ void __launch_bounds__(TA_THREADS, HD == 64 ? 2 : 1)
+__global__ void __launch_bounds__(TA_THREADS, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                                  const __grid_constant__ CUtensorMap v_map, TaParams p) {
   constexpr int CB = HD / 64;                              // 64-column boxes per row of a head
   constexpr int TILE_BYTES = CB * 2 * TA_BOX_BYTES;        // 128 rows of a head
-  constexpr int TCOLS = ta_tmem_cols<HD>();
+  constexpr int HH = HD / 2;                               // output channels of one of the two threads of a row
   extern __shared__ __align__(1024) unsigned char ta_raw[];
   unsigned char* Qs = ta_raw;
   unsigned char* Ks = Qs + TILE_BYTES;                     // [stage]
-  unsigned char* Vs = Ks + TA_STAGES * TILE_BYTES;
-  unsigned char* Ps = Vs + TILE_BYTES;
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(Ps + 2 * 2 * TA_BOX_BYTES);
+  unsigned char* Vs = Ks + TA_STAGES * TILE_BYTES;         // [stage]
+  unsigned char* Ps = Vs + TA_STAGES * TILE_BYTES;                         // [tile parity][2 boxes]
+  float* x_max = reinterpret_cast<float*>(Ps + 2 * 2 * 2 * TA_BOX_BYTES);  // [tile parity][half][row]
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(x_max + 4 * 128);
   unsigned long long* q_full = bars;                       // 1
   unsigned long long* k_full = bars + 1;                   // [stage]
-  unsigned long long* k_empty = bars + 1 + TA_STAGES;      // [stage]
-  unsigned long long* s_full = bars + 1 + 2 * TA_STAGES;
-  unsigned long long* p_ready = s_full + 1;
-  unsigned long long* o_full = s_full + 2;
-  unsigned long long* o_free = s_full + 3;
-  unsigned long long* v_full = s_full + 4;
-  unsigned long long* v_empty = s_full + 5;
-  unsigned* tmem_base = reinterpret_cast<unsigned*>(s_full + 6);
+  unsigned long long* k_empty = k_full + TA_STAGES;        // [stage]
+  unsigned long long* v_full = k_empty + TA_STAGES;        // [stage]
+  unsigned long long* v_empty = v_full + TA_STAGES;        // [stage]
+  unsigned long long* s_full = v_empty + TA_STAGES;        // [2]: the two S accumulators
+  unsigned long long* p_ready = s_full + 2;                // [2]: the two P tiles
+  unsigned long long* o_full = p_ready + 2;                // [2]: the two P V accumulators
+  unsigned long long* o_free = o_full + 2;                 // [2]
+  unsigned* tmem_base = reinterpret_cast<unsigned*>(o_free + 2);
   int* failed = reinterpret_cast<int*>(tmem_base + 1);
 
-  const int seq = blockIdx.y, head = blockIdx.z;
+  // blocks are numbered by falling length: every (sequence, head) of the last query tile first, so that the
+  // multiprocessors that finish early pick up the short ones
+  const int seq = (int)blockIdx.x / p.n_heads, head = (int)blockIdx.x % p.n_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // (sequence starts and lengths were written before the previous kernel started: safe to read before the wait)
   const int t0 = p.seq_start[seq], n_new = p.seq_start[seq + 1] - t0;
-  const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;              // longest tiles first
+  const int q_tile = (int)gridDim.y - 1 - (int)blockIdx.y;
   const int q0 = q_tile * TA_BQ;
   if (q0 >= n_new) return;
   if ((ta_smem(ta_raw) & 1023u) != 0) {      // the swizzled layouts need the alignment: refuse rather than compute nonsense
@@ -212,27 +221,30 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
     for (int s = 0; s < TA_STAGES; ++s) {
       ta_bar_init(&k_full[s], 1);
       ta_bar_init(&k_empty[s], 1);
+      ta_bar_init(&v_full[s], 1);
+      ta_bar_init(&v_empty[s], 1);
     }
-    ta_bar_init(v_full, 1);
-    ta_bar_init(v_empty, 1);
-    ta_bar_init(s_full, 1);
-    ta_bar_init(p_ready, TA_SOFTMAX_WARPS);
-    ta_bar_init(o_full, 1);
-    ta_bar_init(o_free, TA_SOFTMAX_WARPS);
+    ta_bar_init(&s_full[0], 1);
+    ta_bar_init(&s_full[1], 1);
+    for (int b = 0; b < 2; ++b) {
+      ta_bar_init(&p_ready[b], TA_SOFTMAX_WARPS);
+      ta_bar_init(&o_full[b], 1);
+      ta_bar_init(&o_free[b], TA_SOFTMAX_WARPS);
+    }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 5) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(ta_smem(tmem_base)), "r"(TCOLS) : "memory");
+  if (warp == TA_SOFTMAX_WARPS + 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(ta_smem(tmem_base)), "r"(TA_TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   ta_fence_before();
   __syncthreads();
   ta_fence_after();
-  const unsigned tmem_s = *tmem_base, tmem_o = tmem_s + TA_BK;
+  const unsigned tmem_s = *tmem_base, tmem_o = tmem_s + 2 * TA_BK;
   pdl_wait();      // the projections (and the pages) of this step are complete from here on
 
-  if (warp == 4) {
+  if (warp == TA_SOFTMAX_WARPS) {
     if (lane == 0) {
       // ---- producer ----
       ta_bar_expect(q_full, TILE_BYTES);
@@ -254,178 +266,213 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
           col_v = p.v_col + kv_head * HD;
         }
       };
-      auto load_k = [&](int it) {
+      auto load = [&](int it, bool values) {
         const int s = it % TA_STAGES;
-        ta_bar_expect(&k_full[s], TILE_BYTES);
+        unsigned long long* bar = values ? &v_full[s] : &k_full[s];
+        unsigned char* dst = (values ? Vs : Ks) + s * TILE_BYTES;
+        ta_bar_expect(bar, TILE_BYTES);
         for (int h = 0; h < 2; ++h) {
           int row, col_k, col_v;
           where(it, h, row, col_k, col_v);
           for (int cb = 0; cb < CB; ++cb)
-            ta_tma(Ks + s * TILE_BYTES + cb * 2 * TA_BOX_BYTES + h * TA_BOX_BYTES, &k_map, col_k + cb * 64, row, &k_full[s]);
+            ta_tma(dst + cb * 2 * TA_BOX_BYTES + h * TA_BOX_BYTES, values ? &v_map : &k_map, (values ? col_v : col_k) + cb * 64, row, bar);
         }
       };
-      auto load_v = [&](int it) {
-        ta_bar_expect(v_full, TILE_BYTES);
-        for (int h = 0; h < 2; ++h) {
-          int row, col_k, col_v;
-          where(it, h, row, col_k, col_v);
-          for (int cb = 0; cb < CB; ++cb)
-            ta_tma(Vs + cb * 2 * TA_BOX_BYTES + h * TA_BOX_BYTES, &v_map, col_v + cb * 64, row, v_full);
+      for (int it = 0; it < min(n_tiles, TA_STAGES); ++it) {
+        load(it, false);
+        load(it, true);
+      }
+      // a stage of K is free when S of its tile is computed, a stage of V when its P V is
+      for (int it = 0; it + TA_STAGES < n_tiles; ++it) {
+        const int s = it % TA_STAGES;
+        const unsigned parity = (unsigned)(it / TA_STAGES) & 1u;
+        if (!ta_bar_wait(&k_empty[s], parity)) {
+          *failed = 1;
+          break;
         }
-      };
-      load_k(0);
-      load_v(0);
-      if (n_tiles > 1) load_k(1);
-      // in the order in which the places come free: K's stage when S of tile `it` is computed, V when its P V is
-      for (int it = 0; it < n_tiles; ++it) {
-        if (it + TA_STAGES < n_tiles) {
-          if (!ta_bar_wait(&k_empty[it % TA_STAGES], (it / TA_STAGES) & 1)) {
-            *failed = 1;
-            break;
-          }
-          load_k(it + TA_STAGES);
+        load(it + TA_STAGES, false);
+        if (!ta_bar_wait(&v_empty[s], parity)) {
+          *failed = 1;
+          break;
         }
-        if (it + 1 < n_tiles) {
-          if (!ta_bar_wait(v_empty, it & 1)) {
-            *failed = 1;
-            break;
-          }
-          load_v(it + 1);
-        }
+        load(it + TA_STAGES, true);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == TA_SOFTMAX_WARPS + 1) {
     if (lane == 0) {
       // ---- issuer ----
       // instruction descriptors: 32-bit accumulator, bfloat16 operands, M = 128; S: N = 128, both K-major;
       // P V: N = HD, the second operand MN-major
       const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TA_BK >> 3) << 17) | ((unsigned)(TA_BQ >> 4) << 24);
       const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(TA_BQ >> 4) << 24);
+      // S of tile `it` = Q K^T into accumulator it % 2, when the tile's keys have landed.  (The accumulator is free:
+      // the softmax warps had read tile it - 2's before they announced its P.)
+      // operand descriptors, made once: Q and K per 16 channels, P per 16 keys, V per 16 keys (and stage)
+      unsigned long long dq[HD / 16], dk[TA_STAGES][HD / 16], dp[TA_BK / 16], dv[TA_STAGES][TA_BK / 16];
+#pragma unroll
+      for (int k = 0; k < HD / 16; ++k) {
+        dq[k] = ta_desc(Qs + (k / 4) * 2 * TA_BOX_BYTES, 16) + 2ull * (k % 4);
+#pragma unroll
+        for (int s = 0; s < TA_STAGES; ++s) dk[s][k] = ta_desc(Ks + s * TILE_BYTES + (k / 4) * 2 * TA_BOX_BYTES, 16) + 2ull * (k % 4);
+      }
+#pragma unroll
+      for (int j = 0; j < TA_BK / 16; ++j) {
+        dp[j] = ta_desc(Ps + (j / 4) * 2 * TA_BOX_BYTES, 16) + 2ull * (j % 4);      // (the second P tile: 32 KB further)
+        // 16 keys further: 16 rows of 128 bytes; the next 64 channels: a whole 128-row box further
+#pragma unroll
+        for (int s = 0; s < TA_STAGES; ++s) dv[s][j] = ta_desc(Vs + s * TILE_BYTES + j * 16 * 128, 2 * TA_BOX_BYTES);
+      }
+      auto scores = [&](int it) -> bool {
+        const int s = it % TA_STAGES;
+        if (!ta_bar_wait(&k_full[s], (it / TA_STAGES) & 1)) return false;
+        ta_fence_after();
+        const unsigned d = tmem_s + (unsigned)((it & 1) * TA_BK);
+        if (s == 0) {
+#pragma unroll
+          for (int k = 0; k < HD / 16; ++k) ta_mma(d, dq[k], dk[0][k], idesc_s, k > 0 ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int k = 0; k < HD / 16; ++k) ta_mma(d, dq[k], dk[1][k], idesc_s, k > 0 ? 1u : 0u);
+        }
+        ta_commit(&s_full[it & 1]);
+        ta_commit(&k_empty[s]);
+        return true;
+      };
       bool ok = ta_bar_wait(q_full, 0);
+      ok = ok && scores(0);
+      if (n_tiles > 1) ok = ok && scores(1);
       for (int it = 0; it < n_tiles && ok; ++it) {
         const int s = it % TA_STAGES;
-        if (!ta_bar_wait(&k_full[s], (it / TA_STAGES) & 1)) {
+        // O_tile = P V into accumulator it % 2, when P and V lie in shared memory and that accumulator's last
+        // contents (tile it - 2) have been taken
+        if (!ta_bar_wait(&v_full[s], (it / TA_STAGES) & 1) || !ta_bar_wait(&p_ready[it & 1], (it >> 1) & 1) ||
+            (it >= 2 && !ta_bar_wait(&o_free[it & 1], ((it - 2) >> 1) & 1))) {
           ok = false;
           break;
         }
         ta_fence_after();
-        // S = Q K^T.  (S is free: the softmax warps had read the last tile's before they announced its P.)
+        if (s == 0) {
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const unsigned long long a = ta_desc(Qs + (k / 4) * 2 * TA_BOX_BYTES, 16) + 2ull * (k % 4);
-          const unsigned long long b = ta_desc(Ks + s * TILE_BYTES + (k / 4) * 2 * TA_BOX_BYTES, 16) + 2ull * (k % 4);
-          ta_mma(tmem_s, a, b, idesc_s, k > 0 ? 1u : 0u);
-        }
-        ta_commit(s_full);
-        ta_commit(&k_empty[s]);
-        // O_tile = P V, when P and V lie in shared memory and the last tile's O has been taken
-        if (!ta_bar_wait(v_full, it & 1) || !ta_bar_wait(p_ready, it & 1) || (it > 0 && !ta_bar_wait(o_free, (it - 1) & 1))) {
-          ok = false;
-          break;
-        }
-        ta_fence_after();
+          for (int j = 0; j < TA_BK / 16; ++j) ta_mma(tmem_o, dp[j], dv[0][j], idesc_o, j > 0 ? 1u : 0u);      // (tile parity 0)
+        } else {
 #pragma unroll
-        for (int j = 0; j < TA_BK / 16; ++j) {
-          const unsigned long long a = ta_desc(Ps + (j / 4) * 2 * TA_BOX_BYTES, 16) + 2ull * (j % 4);
-          // 16 keys further: 16 rows of 128 bytes; the next 64 channels: a whole 128-row box further
-          const unsigned long long b = ta_desc(Vs + j * 16 * 128, 2 * TA_BOX_BYTES);
-          ta_mma(tmem_o, a, b, idesc_o, j > 0 ? 1u : 0u);
+          for (int j = 0; j < TA_BK / 16; ++j)
+            ta_mma(tmem_o + (unsigned)HD, dp[j] + (unsigned long long)((2 * 2 * TA_BOX_BYTES) >> 4), dv[1][j], idesc_o, j > 0 ? 1u : 0u);
         }
-        ta_commit(o_full);
-        ta_commit(v_empty);
+        ta_commit(&o_full[it & 1]);
+        ta_commit(&v_empty[s]);
+        if (it + 2 < n_tiles) ok = scores(it + 2);      // its accumulator was read before P of tile `it` was announced
       }
       if (!ok) *failed = 1;
     }
   } else {
-    // ---- softmax: thread r = 32 * warp + lane owns query row r ----
-    const int r = warp * 32 + lane;
+    // ---- softmax: two threads per query row.  Warp w reaches the TMEM lanes of quarter w % 4 (rows 32 (w % 4) ..);
+    // warps 0-3 take keys 0-63 of a tile and the lower half of the output channels, warps 4-7 the rest ----
+    const int half = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
     const int pos = past + q0 + r;
-    const unsigned lane_base = (unsigned)(warp * 32) << 16;
+    const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
     float m = -INFINITY, l = 0.f;
-    float o[HD];
+    float o[HH];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    for (int i = 0; i < HH; ++i) o[i] = 0.f;
     bool ok = true;
-    for (int it = 0; it < n_tiles && ok; ++it) {
-      const int key0 = (kt_lo + it) * TA_BK;
-      if (!ta_bar_wait(s_full, it & 1)) {
-        ok = false;
-        break;
+    // adds the P V of tile `t` (accumulator t % 2) to this thread's channels and hands the accumulator back
+    auto take_o = [&](int t) {
+      unsigned a[32], b[32];
+      const unsigned addr = tmem_o + (unsigned)((t & 1) * HD) + lane_base + (unsigned)(half * HH);
+      if constexpr (HH == 32) {
+        ta_ld32_issue(addr, a);
+        ta_ld32_issue(addr, b);
+        ta_ld_wait(a, b);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] += __uint_as_float(a[i]);
+      } else {
+        ta_ld32_issue(addr, a);
+        ta_ld32_issue(addr + 32u, b);
+        ta_ld_wait(a, b);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          o[i] += __uint_as_float(a[i]);
+          o[32 + i] += __uint_as_float(b[i]);
+        }
       }
+      ta_fence_before();
+      __syncwarp();
+      if (lane == 0) ta_bar_arrive(&o_free[t & 1]);
+    };
+    // (after a wait has run out the remaining waits are skipped, but every warp still runs every tile: the two
+    // warps of a row meet at a barrier in each)
+    for (int it = 0; it < n_tiles; ++it) {
+      const int key0 = (kt_lo + it) * TA_BK;
+      const unsigned s_addr = tmem_s + lane_base + (unsigned)((it & 1) * TA_BK + half * 64);
+      if (ok && !ta_bar_wait(&s_full[it & 1], (it >> 1) & 1)) ok = false;
       ta_fence_after();
       // every key of the tile visible to every query of the block?  Then nothing is masked (the common tile).
       const bool whole = key0 + TA_BK <= kv_len && (!p.causal || key0 + TA_BK - 1 <= pos_first) &&
                          (p.window <= 0 || key0 > pos_last - p.window) && p.scale_log2 > 0.f;
-      int vis_lo = 0, vis_hi = kv_len - 1;          // this row's visible keys, then relative to the tile
-      if (p.causal) vis_hi = min(vis_hi, pos);
-      if (p.window > 0) vis_lo = max(0, pos - p.window + 1);
-      vis_lo -= key0;
-      vis_hi -= key0;
-      // first pass: the row's maximum over the tile
+      int lo = 0, hi = kv_len - 1;          // this row's visible keys, then relative to this thread's 64 keys
+      if (p.causal) hi = min(hi, pos);
+      if (p.window > 0) lo = max(0, pos - p.window + 1);
+      lo -= key0 + half * 64;
+      hi -= key0 + half * 64;
+      unsigned a[32], b[32];
+      ta_ld32_issue(s_addr, a);
+      ta_ld32_issue(s_addr + 32u, b);
+      ta_ld_wait(a, b);
+      // the row's maximum over this thread's keys, then over the row (the other thread's through shared memory)
       float tile_max = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < TA_BK; c0 += 64) {
-        unsigned a[32], b[32];
-        ta_ld32_issue(tmem_s + lane_base + (unsigned)c0, a);
-        ta_ld32_issue(tmem_s + lane_base + (unsigned)(c0 + 32), b);
-        ta_ld_wait(a, b);
-        if (whole) {
+      if (whole) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, fmaxf(__uint_as_float(a[i]), __uint_as_float(b[i])));
-        } else {
-          const int lo = vis_lo - c0, hi = vis_hi - c0;
+        for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, fmaxf(__uint_as_float(a[i]), __uint_as_float(b[i])));
+        tile_max *= p.scale_log2;       // (the scale is positive on this path)
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            tile_max = fmaxf(tile_max, (i >= lo && i <= hi) ? __uint_as_float(a[i]) * p.scale_log2 : -INFINITY);
-            tile_max = fmaxf(tile_max, (i + 32 >= lo && i + 32 <= hi) ? __uint_as_float(b[i]) * p.scale_log2 : -INFINITY);
-          }
+        for (int i = 0; i < 32; ++i) {
+          tile_max = fmaxf(tile_max, (i >= lo && i <= hi) ? __uint_as_float(a[i]) * p.scale_log2 : -INFINITY);
+          tile_max = fmaxf(tile_max, (i + 32 >= lo && i + 32 <= hi) ? __uint_as_float(b[i]) * p.scale_log2 : -INFINITY);
         }
       }
-      if (whole) tile_max *= p.scale_log2;       // (the scale is positive on this path)
+      x_max[((it & 1) * 2 + half) * 128 + r] = tile_max;
+      // the two warps of a quarter meet at a barrier of their own (64 threads); both run every tile, see below
+      asm volatile("bar.sync %0, 64;\n" ::"r"(1 + (warp & 3)) : "memory");
+      tile_max = fmaxf(tile_max, x_max[((it & 1) * 2 + (half ^ 1)) * 128 + r]);
       const float m_new = fmaxf(m, tile_max);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = ta_exp2(m - m_use);         // 0 for a row that had seen nothing yet
-      // second pass: weights, their sum, and P in shared memory
+      // weights, their sum, and P in shared memory: this thread's 64 keys are one box's row of 128 bytes
       float sum = 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < TA_BK; c0 += 64) {
-        unsigned a[32], b[32];
-        ta_ld32_issue(tmem_s + lane_base + (unsigned)c0, a);
-        ta_ld32_issue(tmem_s + lane_base + (unsigned)(c0 + 32), b);
-        ta_ld_wait(a, b);
-        float va[32], vb[32];
-        if (whole) {
+      float va[32], vb[32];
+      if (whole) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            va[i] = ta_exp2(fmaf(__uint_as_float(a[i]), p.scale_log2, -m_use));
-            vb[i] = ta_exp2(fmaf(__uint_as_float(b[i]), p.scale_log2, -m_use));
-            sum += va[i] + vb[i];
-          }
-        } else {
-          const int lo = vis_lo - c0, hi = vis_hi - c0;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            va[i] = (i >= lo && i <= hi) ? ta_exp2(fmaf(__uint_as_float(a[i]), p.scale_log2, -m_use)) : 0.f;
-            vb[i] = (i + 32 >= lo && i + 32 <= hi) ? ta_exp2(fmaf(__uint_as_float(b[i]), p.scale_log2, -m_use)) : 0.f;
-            sum += va[i] + vb[i];
-          }
+        for (int i = 0; i < 32; ++i) {
+          va[i] = ta_exp2(fmaf(__uint_as_float(a[i]), p.scale_log2, -m_use));
+          vb[i] = ta_exp2(fmaf(__uint_as_float(b[i]), p.scale_log2, -m_use));
+          sum += va[i] + vb[i];
         }
-        // keys c0 .. c0 + 63 are one box of P: this row's 128 bytes, 16-byte chunks XOR-ed with the row number
-        unsigned char* box = Ps + (c0 / 64) * 2 * TA_BOX_BYTES + r * 128;
+      } else {
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint4 x, y;
-          x.x = ta_pack(va[8 * ch], va[8 * ch + 1]);
-          x.y = ta_pack(va[8 * ch + 2], va[8 * ch + 3]);
-          x.z = ta_pack(va[8 * ch + 4], va[8 * ch + 5]);
-          x.w = ta_pack(va[8 * ch + 6], va[8 * ch + 7]);
-          y.x = ta_pack(vb[8 * ch], vb[8 * ch + 1]);
-          y.y = ta_pack(vb[8 * ch + 2], vb[8 * ch + 3]);
-          y.z = ta_pack(vb[8 * ch + 4], vb[8 * ch + 5]);
-          y.w = ta_pack(vb[8 * ch + 6], vb[8 * ch + 7]);
-          *reinterpret_cast<uint4*>(box + ((ch ^ (r & 7)) << 4)) = x;
-          *reinterpret_cast<uint4*>(box + (((ch + 4) ^ (r & 7)) << 4)) = y;
+        for (int i = 0; i < 32; ++i) {
+          va[i] = (i >= lo && i <= hi) ? ta_exp2(fmaf(__uint_as_float(a[i]), p.scale_log2, -m_use)) : 0.f;
+          vb[i] = (i + 32 >= lo && i + 32 <= hi) ? ta_exp2(fmaf(__uint_as_float(b[i]), p.scale_log2, -m_use)) : 0.f;
+          sum += va[i] + vb[i];
         }
+      }
+      // (this P tile is free: its last products, of tile it - 2, were waited for before that tile's O was taken)
+      unsigned char* box = Ps + (it & 1) * 2 * 2 * TA_BOX_BYTES + half * 2 * TA_BOX_BYTES + r * 128;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint4 x, y;
+        x.x = ta_pack(va[8 * ch], va[8 * ch + 1]);
+        x.y = ta_pack(va[8 * ch + 2], va[8 * ch + 3]);
+        x.z = ta_pack(va[8 * ch + 4], va[8 * ch + 5]);
+        x.w = ta_pack(va[8 * ch + 6], va[8 * ch + 7]);
+        y.x = ta_pack(vb[8 * ch], vb[8 * ch + 1]);
+        y.y = ta_pack(vb[8 * ch + 2], vb[8 * ch + 3]);
+        y.z = ta_pack(vb[8 * ch + 4], vb[8 * ch + 5]);
+        y.w = ta_pack(vb[8 * ch + 6], vb[8 * ch + 7]);
+        *reinterpret_cast<uint4*>(box + ((ch ^ (r & 7)) << 4)) = x;
+        *reinterpret_cast<uint4*>(box + (((ch + 4) ^ (r & 7)) << 4)) = y;
       }
       l = l * alpha + sum;
       m = m_new;
@@ -433,36 +480,32 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       ta_fence_before();
       __syncwarp();
-      if (lane == 0) ta_bar_arrive(p_ready);
-#pragma unroll
-      for (int i = 0; i < HD; ++i) o[i] *= alpha;
-      if (!ta_bar_wait(o_full, it & 1)) {
-        ok = false;
-        break;
+      if (lane == 0) ta_bar_arrive(&p_ready[it & 1]);
+      // the last tile's P V was computed while this tile's weights were: take it now, then age the sum by this
+      // tile's factor
+      if (it > 0) {
+        if (ok && !ta_bar_wait(&o_full[(it - 1) & 1], ((it - 1) >> 1) & 1)) ok = false;
+        ta_fence_after();
+        take_o(it - 1);
       }
-      ta_fence_after();
 #pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 64) {
-        unsigned a[32], b[32];
-        ta_ld32_issue(tmem_o + lane_base + (unsigned)c0, a);
-        ta_ld32_issue(tmem_o + lane_base + (unsigned)(c0 + 32), b);
-        ta_ld_wait(a, b);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          o[c0 + i] += __uint_as_float(a[i]);
-          o[c0 + 32 + i] += __uint_as_float(b[i]);
-        }
-      }
-      ta_fence_before();
-      __syncwarp();
-      if (lane == 0) ta_bar_arrive(o_free);
+      for (int i = 0; i < HH; ++i) o[i] *= alpha;
     }
+    if (ok && !ta_bar_wait(&o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) ok = false;
+    ta_fence_after();
+    take_o(n_tiles - 1);
+    // the row's sum is the two threads' (both hold the same maximum)
+    // (through the exchange buffer that the last tile did not use: nobody reads that one any more)
+    float* x_sum = x_max + (n_tiles & 1) * 2 * 128;
+    x_sum[half * 128 + r] = l;
+    asm volatile("bar.sync %0, 64;\n" ::"r"(1 + (warp & 3)) : "memory");
+    l += x_sum[(half ^ 1) * 128 + r];
     if (!ok) *failed = 1;
     if (ok && r < nq) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = p.out + (long long)(t0 + q0 + r) * ((long long)p.n_heads * HD) + head * HD;
+      __nv_bfloat16* dst = p.out + (long long)(t0 + q0 + r) * ((long long)p.n_heads * HD) + head * HD + half * HH;
 #pragma unroll
-      for (int c = 0; c < HD; c += 8) {
+      for (int c = 0; c < HH; c += 8) {
         uint4 x;
         x.x = ta_pack(o[c] * inv, o[c + 1] * inv);
         x.y = ta_pack(o[c + 2] * inv, o[c + 3] * inv);
@@ -476,9 +519,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   pdl_trigger();
   ta_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == TA_SOFTMAX_WARPS + 1) {
     ta_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(TCOLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(TA_TMEM_COLS) : "memory");
   }
   if (threadIdx.x == 0 && *failed && p.status) atomicExch(p.status, 6);
 }
@@ -492,11 +535,11 @@ static int launch_ta(const CUtensorMap& qm, const CUtensorMap& km, const CUtenso
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     BT_CHECK(e == cudaSuccess, "attention_prefill_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    // two blocks of head size 64 share a multiprocessor only with the largest shared-memory carve-out
-    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
-  dim3 grid((max_new + TA_BQ - 1) / TA_BQ, n_seqs, p.n_heads);
+  const int q_tiles = (max_new + TA_BQ - 1) / TA_BQ;
+  BT_CHECK(q_tiles <= 65535, "attention_prefill_tcgen05: %d new tokens in one sequence are too many for one launch", max_new);
+  dim3 grid(n_seqs * p.n_heads, q_tiles);
   BT_PDL_OK("attention_prefill_tcgen05", launch_pdl(kern, grid, dim3(TA_THREADS), smem, stream, 1, qm, km, vm, p));
   return 0;
 }
