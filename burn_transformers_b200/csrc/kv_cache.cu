@@ -13,6 +13,8 @@ __global__ void kv_append_kernel(const T* __restrict__ proj, long long row_strid
                                  const int* __restrict__ ctx_len, const int* __restrict__ table, int table_stride,
                                  int table_len, int page_size, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                  int n_kv_heads, int head_dim) {
+  pdl_trigger();
+  pdl_wait();      // (every block, also one that has nothing to file: the next kernel's wait rests on this one's)
   const int t = blockIdx.x;
   const int seq = token_seq[t];
   const int pos = positions[t];
@@ -47,15 +49,15 @@ extern "C" int bt_kv_append(const void* proj, long long row_stride, int k_offset
   BT_CHECK(table_len > 0 && page_size > 0, "kv_append: bad table_len %d or page_size %d", table_len, page_size);
   if (n_tokens == 0) return 0;
   if (dtype == kF32)
-    kv_append_kernel<float><<<n_tokens, 128, 0, stream>>>((const float*)proj, row_stride, k_offset, v_offset, positions,
-                                                         token_seq, ctx_len, table, table_stride, table_len, page_size,
-                                                         (float*)k_pool, (float*)v_pool, n_kv_heads, head_dim);
+    BT_PDL_OK("kv_append", launch_pdl(kv_append_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, 1, (const float*)proj, row_stride,
+                                      k_offset, v_offset, positions, token_seq, ctx_len, table, table_stride, table_len,
+                                      page_size, (float*)k_pool, (float*)v_pool, n_kv_heads, head_dim));
   else if (dtype == kBF16)
-    kv_append_kernel<__nv_bfloat16><<<n_tokens, 128, 0, stream>>>(
-        (const __nv_bfloat16*)proj, row_stride, k_offset, v_offset, positions, token_seq, ctx_len, table, table_stride,
-        table_len, page_size, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_kv_heads, head_dim);
+    BT_PDL_OK("kv_append", launch_pdl(kv_append_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, stream, 1,
+                                      (const __nv_bfloat16*)proj, row_stride, k_offset, v_offset, positions, token_seq, ctx_len,
+                                      table, table_stride, table_len, page_size, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+                                      n_kv_heads, head_dim));
   else
     return fail("kv_append: unknown dtype %d", dtype);
-  BT_LAUNCH_OK("kv_append");
   return 0;
 }

@@ -12,6 +12,8 @@
 //             the segment with 16-byte stores, 32-bit or bfloat16.  There are two accumulators, so this runs
 //             while the next tile's products are already being issued.
 // Both operands are K-major (K contiguous): A as the activations are stored, W as [N, K].
+// The kernel is launched as a programmatic dependent: it sets itself up (barriers, tensor memory) and asks for its
+// first tiles of W while its predecessor still runs, and waits for it only before it touches activations.
 // Stages hand over through mbarriers; every wait is bounded, and a wait that runs out marks the call as failed
 // (status word) instead of hanging: the block still frees its tensor memory and returns.
 // Rows and columns beyond M, N, K are zero-filled by the TMA on the way in and skipped on the way out.
@@ -138,6 +140,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2;
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<unsigned long long>(tc_smem_raw) + 1023ull) & ~1023ull);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();     // the next kernel may set itself up (and fetch its weights) while this one runs
   const int tiles_m = (p.M + TC_BM - 1) / TC_BM, tiles_n = (p.N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + TC_BK - 1) / TC_BK;
@@ -166,10 +169,24 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
   if (warp == 0) {
     if (lane == 0) {
+      // The first stages' tiles of W are asked for before the kernel waits for its predecessor (programmatic dependent
+      // launch): nothing of a step writes weights, so they travel while the previous kernel finishes.  Their tiles
+      // of A follow after the wait.
+      const int pre = (int)blockIdx.x < n_tiles ? (k_blocks < STAGES ? k_blocks : STAGES) : 0;
+      {
+        const int m0 = ((int)blockIdx.x % tiles_m) * TC_BM, n0 = ((int)blockIdx.x / tiles_m) * BN;
+        for (int kb = 0; kb < pre; ++kb) {
+          tc_bar_expect(&full[kb], A_BYTES + W_BYTES);
+          tc_tma_load(tiles + (size_t)kb * (A_BYTES + W_BYTES) + A_BYTES, &map_w, kb * TC_BK, n0, &full[kb]);
+        }
+        pdl_wait();
+        for (int kb = 0; kb < pre; ++kb) tc_tma_load(tiles + (size_t)kb * (A_BYTES + W_BYTES), &map_a, kb * TC_BK, m0, &full[kb]);
+      }
       int it = 0;                          // k-blocks loaded so far, over all tiles
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          if (it < pre) continue;          // asked for above
           const int s = it % STAGES;
           if (it >= STAGES && !tc_bar_wait(&empty[s], ((it / STAGES) - 1) & 1)) {
             failed = 1;
@@ -221,6 +238,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     // of a quarter take half of the tile's columns each.  A thread holds 32 consecutive columns of its row: bias,
     // activation and residual are applied there and the row segment is written with 16-byte stores.
     const int quarter = warp & 3, half = (warp - 2) >> 2;
+    pdl_wait();      // the residual is read and the output written only when the previous kernel has finished
     const bool vec_ok = p.out_is_f32 ? (p.N % 4 == 0) : (p.N % 8 == 0);
     int local = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
@@ -322,8 +340,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const TcParam
   const int n_tiles = ((p.N + BN - 1) / BN) * ((p.M + TC_BM - 1) / TC_BM);
   const int sms = sm_count() > 0 ? sm_count() : 148;
   const int blocks = n_tiles < sms ? n_tiles : sms;     // one persistent block per SM
-  kern<<<blocks, TC_THREADS, smem, stream>>>(ma, mw, p);
-  BT_LAUNCH_OK("linear_tcgen05");
+  BT_PDL_OK("linear_tcgen05", launch_pdl(kern, dim3(blocks), dim3(TC_THREADS), smem, stream, 1, ma, mw, p));
   return 0;
 }
 
