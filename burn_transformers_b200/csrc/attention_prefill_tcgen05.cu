@@ -194,6 +194,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
 
   // blocks are numbered by falling length: every (sequence, head) of the last query tile first, so that the
   // multiprocessors that finish early pick up the short ones
+  // the next kernel's blocks come in once every block of this one has started; on multiprocessors that have run out
+  // of query tiles they set themselves up while the longest tiles are still being worked on
+  pdl_trigger();
   const int seq = (int)blockIdx.x / p.n_heads, head = (int)blockIdx.x % p.n_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // (sequence starts and lengths were written before the previous kernel started: safe to read before the wait)
@@ -515,8 +518,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
       }
     }
   }
-  // (the next kernel's blocks would only hold shared and tensor memory while they wait: they are let in late)
-  pdl_trigger();
   ta_fence_before();
   __syncthreads();
   if (warp == TA_SOFTMAX_WARPS + 1) {
