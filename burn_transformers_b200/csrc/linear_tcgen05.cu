@@ -8,9 +8,10 @@
 //             lives in tensor memory (TMEM), and commits each stage back to the producer when it has been read;
 //   warps 2-9 wait for a tile's last commit and read the accumulator with tcgen05.ld (a warp reaches the 32 TMEM lanes
 //             of its quarter; the two warps of a quarter take half of the columns each).  A thread then holds 32
-//             consecutive columns of one row: it adds the bias, applies GELU, adds the 32-bit residual and writes
-//             the segment with 16-byte stores, 32-bit or bfloat16.  There are two accumulators, so this runs
-//             while the next tile's products are already being issued.
+//             consecutive columns of one row: it adds the bias, applies GELU and writes the segment with 16-byte
+//             stores (bfloat16 or 32-bit); with a 32-bit residual the warp first turns its patch through shared
+//             memory, so that four lanes read and write 64 contiguous bytes of a row.  There are two
+//             accumulators, so this runs while the next tile's products are already being issued.
 // Both operands are K-major (K contiguous): A as the activations are stored, W as [N, K].
 // The kernel is launched as a programmatic dependent: it sets itself up (barriers, tensor memory) and asks for its
 // first tiles of W while its predecessor still runs, and waits for it only before it touches activations.
@@ -27,6 +28,7 @@ constexpr int TC_BK = 64;                 // bfloat16 per stage row: 128 bytes, 
 constexpr int TC_EPI_WARPS = 8;                    // two per quarter of the accumulator's rows, half the columns each
 constexpr int TC_THREADS = (2 + TC_EPI_WARPS) * 32;
 constexpr int TC_WAIT_LIMIT = 1 << 22;    // polls of an mbarrier before giving up
+constexpr int TC_PATCH_STRIDE = 20;       // floats between rows of an epilogue warp's 32 x 16 patch in shared memory
 
 struct TcParams {
   const float* bias;        // [N] or null
@@ -128,7 +130,7 @@ __device__ __forceinline__ void tc_bar_arrive(unsigned long long* bar) {
 
 // Persistent: a block walks over output tiles (tile, tile + grid, ...).  The accumulator is double-buffered in
 // tensor memory (2 x BN columns), so the epilogue of one tile runs while the products of the next are issued.
-// Shared memory: STAGES x (A tile 128 x 64, W tile BN x 64), each tile 1024-byte aligned, then a 32 x 33 float
+// Shared memory: STAGES x (A tile 128 x 64, W tile BN x 64), each tile 1024-byte aligned, then a 32 x 20 float
 // patch per epilogue warp through which accumulator rows are turned into coalesced global rows.
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
@@ -238,6 +240,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     // of a quarter take half of the tile's columns each.  A thread holds 32 consecutive columns of its row: bias,
     // activation and residual are applied there and the row segment is written with 16-byte stores.
     const int quarter = warp & 3, half = (warp - 2) >> 2;
+    float* patch = reinterpret_cast<float*>(tiles + (size_t)STAGES * (A_BYTES + W_BYTES)) + (warp - 2) * (32 * TC_PATCH_STRIDE);
     pdl_wait();      // the residual is read and the output written only when the previous kernel has finished
     const bool vec_ok = p.out_is_f32 ? (p.N % 4 == 0) : (p.N % 8 == 0);
     int local = 0;
@@ -259,7 +262,41 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int col0 = n0 + c0;
         if (col0 >= p.N) continue;                 // (uniform in the warp; the load above is collective)
         const long long o0 = (long long)row * p.N + col0;
-        if (vec_ok && col0 + 32 <= p.N) {
+        if (vec_ok && col0 + 32 <= p.N && p.residual != nullptr) {
+          // 32-bit output with a residual (the residual stream itself, as a rule): the warp's patch goes through
+          // shared memory, 16 columns at a time, so that global memory is reached row by row: a thread writes its
+          // row (rows 20 floats apart: no bank conflicts for 16-byte accesses), then lane 4 r + c takes columns
+          // 4 c .. 4 c + 3 of rows r, r + 8, ..., so that four lanes cover 64 contiguous bytes of a row of the
+          // residual and of the output.  (With a lane per row every instruction touches 32 lines, and the
+          // load/store unit takes them one by one: 1.8 us per 32 columns each way.)
+          const int cq = lane & 3, rq = lane >> 2;
+          const int row_base = m0 + quarter * 32 + rq;
+#pragma unroll
+          for (int h16 = 0; h16 < 2; ++h16) {
+            const long long o_base = (long long)row_base * p.N + col0 + 16 * h16 + 4 * cq;
+            float4 res[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              if (row_base + 8 * k < p.M) res[k] = *reinterpret_cast<const float4*>(p.residual + o_base + (long long)(8 * k) * p.N);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<float4*>(patch + lane * TC_PATCH_STRIDE + 4 * j) =
+                  make_float4(v[16 * h16 + 4 * j], v[16 * h16 + 4 * j + 1], v[16 * h16 + 4 * j + 2], v[16 * h16 + 4 * j + 3]);
+            __syncwarp();
+            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p.bias) b4 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + 16 * h16 + 4 * cq));
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              float4 x = *reinterpret_cast<const float4*>(patch + (rq + 8 * k) * TC_PATCH_STRIDE + 4 * cq);
+              x.x = tc_activation(x.x + b4.x, p.act, true) + res[k].x;
+              x.y = tc_activation(x.y + b4.y, p.act, true) + res[k].y;
+              x.z = tc_activation(x.z + b4.z, p.act, true) + res[k].z;
+              x.w = tc_activation(x.w + b4.w, p.act, true) + res[k].w;
+              if (row_base + 8 * k < p.M) *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o_base + (long long)(8 * k) * p.N) = x;
+            }
+            __syncwarp();      // the patch is free again
+          }
+        } else if (vec_ok && col0 + 32 <= p.N) {
           float4 res[8];
           if (p.residual && row_ok) {
             // the whole segment of the residual first, so that the latencies overlap (the output may be the
@@ -329,7 +366,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const TcParams& p, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+  constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + (size_t)TC_EPI_WARPS * 32 * TC_PATCH_STRIDE * 4;
   auto kern = linear_tcgen05_kernel<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
