@@ -314,8 +314,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           const bool exact = p.residual != nullptr || p.out_is_f32 != 0;
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = tc_activation(v[i], p.act, exact);
-          if (!row_ok) continue;
           if (p.out_is_f32) {
+            if (!row_ok) continue;
             float* dst = reinterpret_cast<float*>(p.out) + o0;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -324,7 +324,10 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
               *reinterpret_cast<float4*>(dst + 4 * j) = x;
             }
           } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + o0;
+            // bfloat16: the thread's 64-byte row goes into the patch (rows 80 bytes apart: no bank conflicts), then
+            // lane 4 r + c writes 16 bytes of rows r, r + 8, r + 16, r + 24: four lanes cover a row's 64 bytes,
+            // an instruction 8 lines instead of 32
+            unsigned char* patch8 = reinterpret_cast<unsigned char*>(patch);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 x;
@@ -332,8 +335,17 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
               x.y = tc_pack(v[8 * j + 2], v[8 * j + 3]);
               x.z = tc_pack(v[8 * j + 4], v[8 * j + 5]);
               x.w = tc_pack(v[8 * j + 6], v[8 * j + 7]);
-              *reinterpret_cast<uint4*>(dst + 8 * j) = x;
+              *reinterpret_cast<uint4*>(patch8 + lane * (TC_PATCH_STRIDE * 4) + 16 * j) = x;
             }
+            __syncwarp();
+            const int cq = lane & 3, rq = lane >> 2;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int r = rq + 8 * k, grow = m0 + quarter * 32 + r;
+              const uint4 x = *reinterpret_cast<const uint4*>(patch8 + r * (TC_PATCH_STRIDE * 4) + 16 * cq);
+              if (grow < p.M) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)grow * p.N + col0 + 8 * cq) = x;
+            }
+            __syncwarp();      // the patch is free again
           }
         } else if (row_ok) {
           // a ragged edge, or rows that are no multiple of 16 bytes: one element at a time
