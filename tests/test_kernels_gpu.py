@@ -474,6 +474,35 @@ def test_attention_prefill_long_sequences_on_tensor_cores(impl, hq, hkv, hd, win
         assert rel(got, want) < TOL[dtype] * 2, f"paged, sequence {s}"
 
 
+@pytest.mark.parametrize("impl", ["tcgen05", "mma"])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attention_prefill_far_key_future_key_and_window_edge(impl, hd):
+    """One key among hundreds answers a late query: in another key tile far back it must be found, one position in
+    the future it must not be seen, and with a window it is seen at the window's first position and not one before."""
+    n, query = 600, 517
+    base = (torch.randn(n, 3 * hd, device=DEV) * 0.05).to(torch.bfloat16)
+    seq_start = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    past = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty(n, hd, device=DEV, dtype=torch.bfloat16)
+
+    def run(key, window):
+        proj = base.clone()
+        proj[query, :hd] = 2.0
+        proj[key, hd:2 * hd] = 2.0
+        proj[key, 2 * hd:] = 50.0
+        kernels.attention_prefill(proj, out, seq_start, past, 1, n, 1, 1, hd, 1.0, window=window, k_offset=hd,
+                                  v_offset=2 * hd, impl=impl)
+        return out[query].float()
+
+    assert float(run(3, 0).min()) > 45.0                       # far back, in the first key tile
+    assert float(run(query, 0).min()) > 45.0                   # the query's own position
+    assert float(run(query + 1, 0).abs().max()) < 2.0          # one position in the future
+    window = 200
+    assert float(run(query - window + 1, window).min()) > 45.0    # the window's first position
+    assert float(run(query - window, window).abs().max()) < 2.0   # one before the window
+    assert int(kernels.kernel_status(base.device)) == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hd", [32, 64])
 def test_attention_prefill_never_looks_ahead(dtype, hd):
