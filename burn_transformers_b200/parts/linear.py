@@ -23,8 +23,9 @@ def linear(ctx, a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=
     """out[:m] = act(a[:m] @ w + bias) (+ residual[:m]);  w is [K, N], or [N, K] when `w_is_nk`.
 
     32-bit operands always take the plain fused-multiply-add kernel: the 32-bit path has no reduced-precision
-    matrix mode.  bfloat16 products of at most 64 rows take a weight-streaming kernel, which can also normalise
-    its rows on the way in; with more rows (and [N, K] weights) they run on the tcgen05 tensor cores."""
+    matrix mode.  bfloat16 products of at most 16 rows take a weight-streaming kernel, which can also normalise
+    its rows on the way in; 17 to 64 rows ([N, K] weights) take the kernel that is fed by tensor-map copies; with
+    more rows they run on the tcgen05 tensor cores."""
     program = getattr(ctx, "program", None)
     if program is not None:      # a fused decode step is being recorded: this product becomes one of its phases
         program.add_linear(a, w, bias, out, m=m, w_is_nk=w_is_nk, activation=activation, residual=residual)
