@@ -170,7 +170,7 @@ def test_linear_stream(m, n, k, warps_k):
 
 
 @pytest.mark.parametrize("m, n, k", [(128, 128, 64), (2048, 2304, 768), (300, 768, 3072), (1000, 3072, 768), (65, 200, 96),
-                                     (129, 50257, 64), (2, 8, 8), (513, 776, 1000)])
+                                     (129, 50257, 64), (2, 8, 8), (513, 776, 1000), (2048, 768, 768), (1900, 3000, 136)])
 def test_linear_tcgen05(m, n, k):
     a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
