@@ -137,8 +137,8 @@ __device__ __forceinline__ unsigned ta_pack(float lo, float hi) {
 __device__ __forceinline__ void ta_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void ta_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 
-// Tensor memory of a block: two S accumulators (2 x 128 columns) and the tile's P V (HD columns): 512 columns, the
-// whole of a multiprocessor's, which one block has to itself.
+// Tensor memory of a block: two S accumulators (2 x 128 columns) and two P V accumulators (2 x HD columns), at most
+// 512 columns: the whole of a multiprocessor's, which one block has to itself.
 constexpr int TA_TMEM_COLS = 512;
 
 // Shared memory (the dynamic region, which must start on a 1024-byte boundary):
@@ -178,11 +178,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   unsigned* tmem_base = reinterpret_cast<unsigned*>(o_free + 2);
   int* failed = reinterpret_cast<int*>(tmem_base + 1);
 
-  // blocks are numbered by falling length: every (sequence, head) of the last query tile first, so that the
-  // multiprocessors that finish early pick up the short ones
-  // the next kernel's blocks come in once every block of this one has started; on multiprocessors that have run out
-  // of query tiles they set themselves up while the longest tiles are still being worked on
+  // The next kernel's blocks come in once every block of this one has started; on multiprocessors that have run out
+  // of query tiles they set themselves up while the longest tiles are still being worked on.
   pdl_trigger();
+  // Blocks are numbered by falling length: every (sequence, head) of the last query tile first, so that the
+  // multiprocessors that finish early pick up the short ones.
   const int seq = (int)blockIdx.x / p.n_heads, head = (int)blockIdx.x % p.n_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // (sequence starts and lengths were written before the previous kernel started: safe to read before the wait)
@@ -294,8 +294,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
       // P V: N = HD, the second operand MN-major
       const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TA_BK >> 3) << 17) | ((unsigned)(TA_BQ >> 4) << 24);
       const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(TA_BQ >> 4) << 24);
-      // S of tile `it` = Q K^T into accumulator it % 2, when the tile's keys have landed.  (The accumulator is free:
-      // the softmax warps had read tile it - 2's before they announced its P.)
       // operand descriptors, made once: Q and K per 16 channels, P per 16 keys, V per 16 keys (and stage)
       unsigned long long dq[HD / 16], dk[TA_STAGES][HD / 16], dp[TA_BK / 16], dv[TA_STAGES][TA_BK / 16];
 #pragma unroll
@@ -311,6 +309,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
 #pragma unroll
         for (int s = 0; s < TA_STAGES; ++s) dv[s][j] = ta_desc(Vs + s * TILE_BYTES + j * 16 * 128, 2 * TA_BOX_BYTES);
       }
+      // S of tile `it` = Q K^T into accumulator it % 2, when the tile's keys have landed.  (The accumulator is free:
+      // the softmax warps had read tile it - 2's before they announced its P.)
       auto scores = [&](int it) -> bool {
         const int s = it % TA_STAGES;
         if (!ta_bar_wait(&k_full[s], (it / TA_STAGES) & 1)) return false;
