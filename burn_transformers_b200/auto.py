@@ -55,6 +55,8 @@ class CausalGenerationRequest:
     prompt: list[list[int]]
     generation: GenerationConfig = dataclasses.field(default_factory=GenerationConfig)
     max_batch: int | None = None
+    # the most tokens of a prompt one step brings; None: whole prompts in one step (src/generation/causal.rs:49-59)
+    prefill_chunk_size: int | None = None
 
 
 @dataclasses.dataclass
@@ -63,13 +65,14 @@ class CausalGenerationOutput:
 
 
 def generate_causal(model: Engine, request: CausalGenerationRequest) -> CausalGenerationOutput:
-    return CausalGenerationOutput(generate(model, request.prompt, request.generation, max_batch=request.max_batch))
+    return CausalGenerationOutput(generate(model, request.prompt, request.generation, max_batch=request.max_batch,
+                                           prefill_chunk_size=request.prefill_chunk_size))
 
 
 def generate_causal_streaming(model: Engine, request: CausalGenerationRequest,
                               on_token: Callable[[GenerationToken], None]) -> CausalGenerationOutput:
     return CausalGenerationOutput(generate(model, request.prompt, request.generation, max_batch=request.max_batch,
-                                           on_token=on_token))
+                                           on_token=on_token, prefill_chunk_size=request.prefill_chunk_size))
 
 
 def cache_tokens_for(prompt_lengths: list[int], max_new_tokens: int) -> int:

@@ -74,6 +74,16 @@ class CacheBank:
                 self._entry_group[entry] = (len(self.groups), layer)
             self.groups.append(group)
 
+    @property
+    def max_continued_run(self) -> int | None:
+        """The most tokens one step may add to a sequence that already holds some; None: no limit.
+
+        A windowed group keeps a ring of `table_len` pages.  The step's keys are filed before its queries attend, so
+        the newest token's key must not overwrite a key the step's first token still sees: a run of n tokens is
+        safe while n <= ring - window + 1.  Groups that keep every key have no such limit."""
+        runs = [g.table_len * PAGE_SIZE - g.spec.window + 1 for g in self.groups if g.is_ring]
+        return max(1, min(runs)) if runs else None
+
     # ---- slots -------------------------------------------------------------------------
     def acquire(self) -> int:
         slot = self.slots.take()

@@ -44,6 +44,8 @@ def main(argv=None) -> int:
     parser.add_argument("--eos-token-ids", type=str, default=None, help="comma-separated ids")
     parser.add_argument("--stop-sequences", type=str, default=None, help='"1,2;3" = two stop sequences')
     parser.add_argument("--max-batch", type=int, default=None)
+    parser.add_argument("--prefill-chunk-size", type=int, default=None,
+                        help="the most tokens of a prompt one step brings (default: whole prompts in one step)")
     parser.add_argument("--json", action="store_true", help="print one JSON object per sequence")
     args = parser.parse_args(argv)
     if args.max_new_tokens <= 0:
@@ -74,7 +76,8 @@ def main(argv=None) -> int:
             generation.eos_token_ids = [int(x) for x in args.eos_token_ids.split(",") if x.strip()]
         if args.stop_sequences is not None:
             generation.stop_sequences = parse_prompts(args.stop_sequences)
-        output = generate_causal(loaded.model, CausalGenerationRequest(prompts, generation, args.max_batch))
+        output = generate_causal(loaded.model, CausalGenerationRequest(prompts, generation, args.max_batch,
+                                                                      args.prefill_chunk_size))
     except BurnTransformersError as error:
         print(f"generate: {error}", file=sys.stderr)
         return 1

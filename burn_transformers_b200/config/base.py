@@ -23,11 +23,6 @@ MAX_LAYERS = 1 << 18         # src/models/config.rs:908
 I32_MAX = (1 << 31) - 1
 
 
-def _repair_infinity(text: str) -> str:
-    """Python's json already reads Infinity/NaN; kept as a hook for strict parsers."""
-    return text
-
-
 def read_json_object(path: Path) -> dict:
     path = Path(path)
     if not path.is_file():
@@ -35,7 +30,7 @@ def read_json_object(path: Path) -> dict:
     if path.stat().st_size > MAX_CONFIG_BYTES:
         raise ConfigError("config", "config.json", f"larger than {MAX_CONFIG_BYTES} bytes")
     try:
-        data = json.loads(_repair_infinity(path.read_text()))
+        data = json.loads(path.read_text())      # (json reads Infinity and NaN as they stand)
     except json.JSONDecodeError as error:
         raise ConfigError("config", "config.json", f"not valid JSON: {error}") from None
     if not isinstance(data, dict):

@@ -33,11 +33,6 @@ int bt_attention_prefill_simt(const void* q, long long q_row_stride, const void*
                               int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim, float scale,
                               int causal, int window, int dtype, cudaStream_t stream);
 
-int bt_attention_prefill_mma_supports(int head_dim, int page_size);
-int bt_attention_prefill_mma(const void* q, long long q_row_stride, const void* k, const void* v, const int* kv_table,
-                             int table_stride, int table_len, int page_size, long long kv_row_stride, void* out,
-                             const int* seq_start, const int* past_len, int n_seqs, int max_new, int n_heads,
-                             int n_kv_heads, int head_dim, float scale, int causal, int window, cudaStream_t stream);
 int bt_attention_prefill_tcgen05_supports(int head_dim, int page_size);
 int bt_attention_prefill_tcgen05(const void* q, long long q_rows, long long q_row_stride, const void* k, const void* v,
                                  long long pool_pages, const int* kv_table, int table_stride, int table_len, int page_size,

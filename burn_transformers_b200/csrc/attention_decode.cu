@@ -137,7 +137,9 @@ attention_decode_kernel(DecodeParams p) {
   // lengths and page tables were written before the previous kernel started: safe to read before the wait
   const int L = p.ctx_len[seq];                     // keys 0..L-1; the query sits at L-1
   const int lo = p.window > 0 ? max(0, L - p.window) : 0;
-  const int pg_first = lo / PS, pg_last = (L - 1) / PS;
+  // a sequence without keys (L <= 0: an empty or finished request that still rides in the batch) owns no page,
+  // files nothing and yields zeros; its block still takes part in the cluster and ticket hand-overs
+  const int pg_first = lo / PS, pg_last = L > 0 ? (L - 1) / PS : pg_first - 1;
   const int n_pg = pg_last - pg_first + 1;
   const int per = (n_pg + n_splits - 1) / n_splits;
   const int my_first = pg_first + split * per;
@@ -180,7 +182,7 @@ attention_decode_kernel(DecodeParams p) {
   const T* q = reinterpret_cast<const T*>(p.q) + (long long)seq * p.q_row_stride + head * head_dim;
   const T* new_k = p.new_k ? reinterpret_cast<const T*>(p.new_k) + (long long)seq * p.q_row_stride + kv_head * head_dim : nullptr;
   const T* new_v = p.new_v ? reinterpret_cast<const T*>(p.new_v) + (long long)seq * p.q_row_stride + kv_head * head_dim : nullptr;
-  if (new_k && split == 0 && head == kv_head * group) {
+  if (new_k && L > 0 && split == 0 && head == kv_head * group) {
     // this block also files the new token's key and value in the sequence's page
     const int pos = L - 1;
     const long long page = table[(pos / PS) % p.table_len];
@@ -220,7 +222,7 @@ attention_decode_kernel(DecodeParams p) {
     __syncthreads();
     const int pa = my_first + r * p.round_pages, pb = min(my_end, pa + p.round_pages);
     const int key_lo = max(lo, pa * PS), key_hi = min(L, pb * PS);
-    if (new_k && key_hi == L) {
+    if (new_k && key_hi == L && L > 0) {
       // the newest key is not in its page yet (or only just): take it from the projections
       const int row = (L - 1) - pa * PS;
       for (int c = tid; c < n_chunks; c += blockDim.x) {
@@ -503,12 +505,16 @@ constexpr int kMaxDevices = 64;
 // it zero again.
 constexpr int kStaticTickets = 1 << 14;
 static __device__ int g_decode_static_tickets[kStaticTickets];
+// Set to 1 by a block whose bounded wait for its copies ran out (its rows are then NaN); read and cleared by
+// bt_attention_decode_static_status.
+static __device__ int g_decode_static_status;
 static float* g_decode_static_ptr[kMaxDevices] = {nullptr};
 static int* g_decode_static_ticket_ptr[kMaxDevices] = {nullptr};
+static int* g_decode_static_status_ptr[kMaxDevices] = {nullptr};
 static std::mutex g_decode_static_mutex;
 
 // Device address of the scratch array on the current device; looked up once per device.
-static int decode_static_scratch(float** ptr, int** tickets) {
+static int decode_static_scratch(float** ptr, int** tickets, int** status) {
   int device = -1;
   cudaError_t e = cudaGetDevice(&device);
   BT_CHECK(e == cudaSuccess, "attention_decode_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
@@ -524,11 +530,17 @@ static int decode_static_scratch(float** ptr, int** tickets) {
     e = cudaGetSymbolAddress((void**)&found_tickets, g_decode_static_tickets);
     BT_CHECK(e == cudaSuccess && found_tickets != nullptr,
              "attention_decode_static: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
+    int* found_status = nullptr;
+    e = cudaGetSymbolAddress((void**)&found_status, g_decode_static_status);
+    BT_CHECK(e == cudaSuccess && found_status != nullptr,
+             "attention_decode_static: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
     g_decode_static_ptr[device] = found;
     g_decode_static_ticket_ptr[device] = found_tickets;
+    g_decode_static_status_ptr[device] = found_status;
   }
   *ptr = g_decode_static_ptr[device];
   *tickets = g_decode_static_ticket_ptr[device];
+  *status = g_decode_static_status_ptr[device];
   return 0;
 }
 
@@ -540,7 +552,13 @@ extern "C" int bt_attention_decode_static(const void* q, long long q_row_stride,
                                           int n_kv_heads, int head_dim, float scale, int window, int n_splits,
                                           int dtype, cudaStream_t stream) {
   using namespace bt;
-  BT_CHECK(n_seqs >= 0 && n_heads > 0 && head_dim > 0 && n_splits >= 1, "attention_decode_static: bad sizes");
+  // ranges first, so that the products below cannot wrap
+  BT_CHECK(n_seqs >= 0 && n_seqs <= 65535 && n_heads > 0 && n_heads <= 65535 && n_splits >= 1 && n_splits <= 65535 &&
+               head_dim > 0 && head_dim <= 256,
+           "attention_decode_static: sizes out of range (sequences %d, heads %d, splits %d, head_dim %d)", n_seqs, n_heads,
+           n_splits, head_dim);
+  BT_CHECK(table_len > 0 && page_size > 0 && page_size <= (1 << 20), "attention_decode_static: bad table_len %d or page_size %d",
+           table_len, page_size);
   const long long need = (long long)n_seqs * n_heads * n_splits * (head_dim + 2);
   BT_CHECK(need <= (long long)BT_DECODE_STATIC_SCRATCH_FLOATS,
            "attention_decode_static: %d sequences x %d heads x %d splits x (%d + 2) = %lld floats of scratch exceed the "
@@ -551,11 +569,30 @@ extern "C" int bt_attention_decode_static(const void* q, long long q_row_stride,
            kStaticTickets);
   float* scratch = nullptr;
   int* tickets = nullptr;
-  if (int rc = decode_static_scratch(&scratch, &tickets)) return rc;
+  int* status = nullptr;
+  if (int rc = decode_static_scratch(&scratch, &tickets, &status)) return rc;
   // the longest context the page table can describe sizes the shared memory of a block
-  const int max_ctx = table_len * page_size;
+  long long span = (long long)table_len * page_size;
+  const int max_ctx = span > (1 << 30) ? (1 << 30) : (int)span;
   return bt_attention_decode(q, q_row_stride, nullptr, nullptr, const_cast<void*>(k_pool), const_cast<void*>(v_pool),
-                             kv_table, table_stride, table_len, page_size, out, scratch, tickets, nullptr, ctx_len,
+                             kv_table, table_stride, table_len, page_size, out, scratch, tickets, status, ctx_len,
                              n_seqs, n_heads, n_kv_heads, head_dim, scale, window, n_splits, max_ctx, /*merge=*/1, dtype,
                              stream);
+}
+
+extern "C" int bt_attention_decode_static_status(int* status_out) {
+  using namespace bt;
+  BT_CHECK(status_out != nullptr, "attention_decode_static_status: needs a place for the answer");
+  float* scratch = nullptr;
+  int* tickets = nullptr;
+  int* status = nullptr;
+  if (int rc = decode_static_scratch(&scratch, &tickets, &status)) return rc;
+  // a blocking copy of one int out of the library's own word, then the word is cleared: no allocation either way
+  cudaError_t e = cudaMemcpy(status_out, status, sizeof(int), cudaMemcpyDeviceToHost);
+  BT_CHECK(e == cudaSuccess, "attention_decode_static_status: reading the status failed: %s", cudaGetErrorString(e));
+  if (*status_out != 0) {
+    e = cudaMemset(status, 0, sizeof(int));
+    BT_CHECK(e == cudaSuccess, "attention_decode_static_status: clearing the status failed: %s", cudaGetErrorString(e));
+  }
+  return 0;
 }

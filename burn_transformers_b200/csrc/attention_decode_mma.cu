@@ -72,7 +72,8 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   // lengths and page tables were written before the previous kernel started: safe to read before the wait
   const int L = p.ctx_len[seq];                     // keys 0..L-1; the query sits at L-1
   const int lo_all = p.window > 0 ? max(0, L - p.window) : 0;
-  const int first = lo_all / DS_PAGE, last = (L - 1) / DS_PAGE;
+  // (a sequence without keys, L <= 0, owns no page, files nothing and yields zeros)
+  const int first = lo_all / DS_PAGE, last = L > 0 ? (L - 1) / DS_PAGE : first - 1;
   const int per = (last - first + 1 + n_splits - 1) / n_splits;
   const int pg_first = first + split * per, pg_end = min(last + 1, pg_first + per);
   const int n_pages = pg_end > pg_first ? pg_end - pg_first : 0;
@@ -121,7 +122,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
   }
   __syncthreads();
-  if (p.new_k && split == 0 && head == kv_head * (p.n_heads / p.n_kv_heads)) {
+  if (p.new_k && L > 0 && split == 0 && head == kv_head * (p.n_heads / p.n_kv_heads)) {
     // this block also files the new token's key and value in the sequence's page
     const int pos = L - 1;
     const long long page = table[(pos / DS_PAGE) % p.table_len];

@@ -24,8 +24,13 @@
 //  * All calls on a device share the one array, and the array keeps whatever the last call left in it.  The
 //    kernels write every partial result they later read, so the partial results need no clearing.  The ticket
 //    counters must be zero when a call starts: they are zero when the library is loaded, and the block that
-//    merges a (sequence, head) sets its counter back to zero, so a completed call leaves them zero.  Two calls that overlap on the GPU (different streams, no ordering between them) race on the
-//    array and give wrong results: order them, or use bt_attention_decode with separate scratch buffers.
+//    merges a (sequence, head) sets its counter back to zero, so a completed call leaves them zero.  Two calls
+//    that overlap on the GPU (different streams, no ordering between them) race on the array and give wrong
+//    results: order them, or use bt_attention_decode with separate scratch buffers.
+//  * The kernel's only wait (for its copies of cache pages to land) is bounded.  A block whose wait runs out
+//    writes NaN as its result, still takes its ticket (so the counters return to zero) and sets a status word
+//    that also lives inside the library.  bt_attention_decode_static_status copies that word to the host with
+//    a blocking cudaMemcpy (0 = every wait was met) and clears it; it allocates nothing either.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -36,3 +41,7 @@ extern "C" int bt_attention_decode_static(const void* q, long long q_row_stride,
                                           int page_size, void* out, const int* ctx_len, int n_seqs, int n_heads,
                                           int n_kv_heads, int head_dim, float scale, int window, int n_splits,
                                           int dtype, cudaStream_t stream);
+
+// Reads (and clears) the status word of this device's bt_attention_decode_static calls into *status_out.
+// Blocks until the device has finished the work queued before it.
+extern "C" int bt_attention_decode_static_status(int* status_out);

@@ -134,8 +134,8 @@ extern "C" int bt_attention_prefill_simt(const void* q, long long q_row_stride, 
                                          int head_dim, float scale, int causal, int window, int dtype,
                                          cudaStream_t stream) {
   using namespace bt;
-  BT_CHECK(head_dim > 0 && head_dim % 8 == 0 && head_dim <= 32 * PF_MAXI,
-           "attention_prefill_simt: head_dim %d must be a multiple of 8 and at most %d", head_dim, 32 * PF_MAXI);
+  BT_CHECK(head_dim > 0 && head_dim <= 32 * PF_MAXI,
+           "attention_prefill_simt: head_dim %d must be at least 1 and at most %d", head_dim, 32 * PF_MAXI);
   BT_CHECK(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
            "attention_prefill_simt: %d query heads cannot share %d key heads", n_heads, n_kv_heads);
   BT_CHECK(n_seqs <= 65535 && n_heads <= 65535, "attention_prefill_simt: too many sequences or heads for one launch");

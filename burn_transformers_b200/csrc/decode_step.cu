@@ -780,7 +780,8 @@ __device__ __forceinline__ AttnItem ds_attn_item(const Phase& ph, const StepShar
   it.seq = unit / ph.n_heads;
   it.L = ds_ctx_len(ph, sh, it.seq);
   it.lo = ph.window > 0 ? max(0, it.L - ph.window) : 0;
-  const int first = it.lo / DS_PAGE, last = (it.L - 1) / DS_PAGE;
+  // (a sequence without keys, L <= 0, owns no page, files nothing and yields zeros)
+  const int first = it.lo / DS_PAGE, last = it.L > 0 ? (it.L - 1) / DS_PAGE : first - 1;
   const int per = (last - first + 1 + S - 1) / S;
   it.pg_first = first + it.split * per;
   it.pg_end = min(last + 1, it.pg_first + per);
@@ -921,7 +922,7 @@ __device__ bool ds_attention_items(const Phase& ph, const Phase* maps, unsigned 
       const int d = 16 * (j >> 1) + 8 * (j & 1) + 2 * q;
       qa[j] = (g == 0 && d < hd) ? *reinterpret_cast<const unsigned*>(my_rows + d) : 0u;
     }
-    if (ph.new_k && it.split == 0 && it.head == kv_head * (ph.n_heads / ph.n_kv_heads)) {
+    if (ph.new_k && it.L > 0 && it.split == 0 && it.head == kv_head * (ph.n_heads / ph.n_kv_heads)) {
       // this block also files the new token's key and value in the sequence's page
       const __nv_bfloat16* nk = my_rows + hd;
       const __nv_bfloat16* nv = my_rows + 2 * hd;
@@ -1216,19 +1217,14 @@ extern "C" int bt_decode_step(const void* phases_dev, int n_phases, int build, l
   using namespace bt;
   BT_CHECK(n_phases >= 1 && smem_bytes <= 200 * 1024, "decode_step: %d phases need %lld bytes of shared memory", n_phases, smem_bytes);
   BT_CHECK(build >= 0 && build <= 4, "decode_step: unknown build %d", build);
-  static int n_sms = 0;
+  const int n_sms = sm_count();      // (of the current device)
+  BT_CHECK(n_sms > 0, "decode_step: cannot read the number of multiprocessors of the current device");
   static long long configured_all[5] = {-1, -1, -1, -1, -1};
   long long& configured = configured_all[build];
   const void* kernels[5] = {(const void*)decode_step_kernel<-1, -1, 128, true>, (const void*)decode_step_kernel<3, 12, 64, false>,
                             (const void*)decode_step_kernel<4, 0, 64, false>, (const void*)decode_step_kernel<3, 12, 64, true>,
                             (const void*)decode_step_kernel<4, 0, 64, true>};
   const void* kernel = kernels[build];
-  if (n_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-    BT_CHECK(n_sms > 0, "decode_step: cannot read the number of SMs");
-  }
   if (configured < smem_bytes) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
     BT_CHECK(e == cudaSuccess, "decode_step: cannot reserve %lld bytes of shared memory: %s", smem_bytes, cudaGetErrorString(e));

@@ -305,7 +305,8 @@ extern "C" int bt_linear_skinny(const void* a, const float* x32, const int* rows
   if (split <= 0) {
     // enough blocks to fill the GPU about once, slices of at least 64 and at most 1024 k
     split = 1;
-    const int sms = sm_count() > 0 ? sm_count() : 148;
+    const int sms = sm_count();
+  BT_CHECK(sms > 0, "linear_skinny: cannot read the number of multiprocessors of the current device");
     while (split < 8 && n_tiles * split < sms && K / (split * 2) >= 64) split *= 2;
     while ((K + split - 1) / split > 1024 && split < 8) split *= 2;
   }

@@ -251,7 +251,8 @@ extern "C" int bt_linear_stream(const void* a, const float* x32, const int* rows
   if (warps_k <= 0) {
     // one block per 8 columns unless that makes many more blocks than the GPU holds at once
     const int groups = (N + 7) / 8;
-    const int sms = sm_count() > 0 ? sm_count() : 148;
+    const int sms = sm_count();
+  BT_CHECK(sms > 0, "linear_stream: cannot read the number of multiprocessors of the current device");
     warps_k = groups >= sms * 8 ? 1 : (groups >= sms * 4 ? 2 : 4);
     while (warps_k > 1 && K / warps_k < 32 * LS_UNROLL) warps_k /= 2;
   }

@@ -391,7 +391,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const TcParam
     configured = true;
   }
   const int n_tiles = ((p.N + BN - 1) / BN) * ((p.M + TC_BM - 1) / TC_BM);
-  const int sms = sm_count() > 0 ? sm_count() : 148;
+  const int sms = sm_count();
+  BT_CHECK(sms > 0, "linear_tcgen05: cannot read the number of multiprocessors of the current device");
   const int blocks = n_tiles < sms ? n_tiles : sms;     // one persistent block per SM
   BT_PDL_OK("linear_tcgen05", launch_pdl(kern, dim3(blocks), dim3(TC_THREADS), smem, stream, 1, ma, mw, p));
   return 0;
@@ -414,7 +415,8 @@ extern "C" int bt_linear_tcgen05(const void* a, const void* w, const float* bias
   // idle multiprocessors and fewer rounds.  Cost of a width = rounds of tiles over the multiprocessors x the time of
   // a k-block at that width (measured: 0.31 us at 128 columns, 0.55 us at 256: about 37 + width); ties go to the wider.
   const long long rows = (M + TC_BM - 1) / TC_BM;
-  const int sms = sm_count() > 0 ? sm_count() : 148;
+  const int sms = sm_count();
+  BT_CHECK(sms > 0, "linear_tcgen05: cannot read the number of multiprocessors of the current device");
   int bn = 256;
   long long best = -1;
   for (int width : {256, 192, 128, 96, 64}) {

@@ -44,6 +44,23 @@ __device__ __forceinline__ int block_sum_i(int v, int* scratch) {
   return scratch[32];
 }
 
+__device__ __forceinline__ int block_max_i(int v, int* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < (int)(blockDim.x >> 5) ? scratch[lane] : (int)0x80000000;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) w = max(w, __shfl_xor_sync(0xffffffffu, w, o));
+    if (lane == 0) scratch[32] = w;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
 struct SampleShared {
   float fs[33];
   int is[33];
@@ -144,9 +161,13 @@ __device__ void select_row(const float* __restrict__ z, int vocab, int do_sample
   const int chunk = (vocab + NT - 1) / NT;
   const int lo = min(vocab, tid * chunk), hi = min(vocab, lo + chunk);
   float mine = 0.f;
+  int last_kept = -1;              // the largest index of this thread's chunk that survived the filters
   for (int i = lo; i < hi; ++i) {
     const float v = value(i);
-    if (ordered_key(v) >= thr) mine += expf(v - zmax);
+    if (ordered_key(v) >= thr) {
+      mine += expf(v - zmax);
+      last_kept = i;
+    }
   }
   float incl = mine;
 #pragma unroll
@@ -181,7 +202,11 @@ __device__ void select_row(const float* __restrict__ z, int vocab, int do_sample
     }
   }
   __syncthreads();
-  const int id = min(block_sum_i(below, sh.is), vocab - 1);
+  // The threshold u * total and the running sums are rounded differently (a scan of per-thread sums against serial
+  // additions), so with u within a few units in the last place of 1 the last survivor's running sum can stay below
+  // the threshold: the count then runs past it, onto indices the filters removed.  The last survivor bounds it.
+  const int last_survivor = block_max_i(last_kept, sh.is);
+  const int id = min(block_sum_i(below, sh.is), max(last_survivor, 0));
   if (tid == 0) {
     *out_id = id;
     *out_logp = (value(id) - zmax) - logf(total);

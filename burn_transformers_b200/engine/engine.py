@@ -90,6 +90,7 @@ class Engine:
             raise ShapeError("a step needs at least one sequence")
         seen = set()
         vocab = self.plan.vocab
+        longest_run = self.cache.max_continued_run
         for e in entries:
             if e.slot in seen:
                 raise ShapeError(f"slot {e.slot} appears twice in one step")
@@ -100,6 +101,9 @@ class Engine:
             if past + len(e.tokens) > self.cache_config.max_context:
                 raise CacheError(f"slot {e.slot}: {past} + {len(e.tokens)} tokens exceed the longest sequence of "
                                  f"{self.cache_config.max_context}")
+            if longest_run is not None and past > 0 and len(e.tokens) > longest_run:
+                raise CacheError(f"slot {e.slot}: a step may add at most {longest_run} tokens to a sequence that already "
+                                 f"holds some (the ring of pages of a windowed layer keeps one window only)")
             lo, hi = min(e.tokens), max(e.tokens)
             if lo < 0 or hi >= vocab:
                 bad = lo if lo < 0 else hi

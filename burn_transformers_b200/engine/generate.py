@@ -80,8 +80,43 @@ def _emit(t: SequenceTracker, token: int, logp: float, on_token):
     return reason
 
 
+def prefill_prompts(engine, trackers: list[SequenceTracker], slots: dict, chunk: int | None):
+    """Runs the batch's prompts and returns the logits at each prompt's last token, one row per tracker.
+
+    Without a chunk size all prompts run in ONE step.  With one, every step brings at most `chunk` tokens of each
+    prompt that still has some (src/generation/causal.rs:49-59, 341-396 of the reference: prompts are cut by columns;
+    a sequence whose prompt has ended sits out the later portions); only the portion that ends a prompt asks for
+    logits, so the rows come from different steps and are gathered here.  Chunked and one-shot prefill give the same
+    logits beyond rounding."""
+    if chunk is None or chunk >= max(len(t.prompt) for t in trackers):
+        return engine.step([StepEntry(slots[t.request], t.prompt, [len(t.prompt) - 1]) for t in trackers])
+    gathered = None
+    for start in range(0, max(len(t.prompt) for t in trackers), chunk):
+        entries, ending = [], []
+        for row, t in enumerate(trackers):
+            if start >= len(t.prompt):
+                continue
+            piece = t.prompt[start:start + chunk]
+            ends = start + len(piece) == len(t.prompt)
+            entries.append(StepEntry(slots[t.request], piece, [len(piece) - 1] if ends else []))
+            if ends:
+                ending.append(row)
+        logits = engine.step(entries)
+        if not ending:
+            continue
+        if hasattr(logits, "new_empty"):
+            if gathered is None:
+                gathered = logits.new_empty((len(trackers), logits.shape[1]))
+            gathered[ending] = logits        # (the step's logits lie in scratch memory the next step reuses)
+        else:                                # a stand-in engine's rows (tests of the loop's decisions)
+            gathered = gathered or [None] * len(trackers)
+            for row, value in zip(ending, logits):
+                gathered[row] = value
+    return gathered
+
+
 def run_batch(engine, sampler, trackers: list[SequenceTracker], on_token: Callable | None = None,
-              session=None) -> None:
+              session=None, prefill_chunk_size: int | None = None) -> None:
     """Serves one batch to its end.  `engine` needs new_sequence/step/release; `sampler` needs select.
     With a `session` (engine.graphs.DecodeSession) the one-token steps run from a recorded CUDA graph with
     the selected tokens fed forward on the device."""
@@ -91,7 +126,7 @@ def run_batch(engine, sampler, trackers: list[SequenceTracker], on_token: Callab
             slots[t.request] = engine.new_sequence()
         for row, t in enumerate(trackers):
             t.row_in_batch = row
-        logits = engine.step([StepEntry(slots[t.request], t.prompt, [len(t.prompt) - 1]) for t in trackers])
+        logits = prefill_prompts(engine, trackers, slots, prefill_chunk_size)
         active = list(trackers)
         batch_rows = len(trackers)
         while active:
@@ -112,12 +147,21 @@ def run_batch(engine, sampler, trackers: list[SequenceTracker], on_token: Callab
 
 
 def generate(engine, prompts: list[list[int]], config: GenerationConfig, *, max_batch: int | None = None,
-             on_token: Callable | None = None, sampler=None) -> list[GeneratedSequence]:
-    """Generates a continuation for every prompt; results come in the order of the prompts."""
+             on_token: Callable | None = None, sampler=None,
+             prefill_chunk_size: int | None = None) -> list[GeneratedSequence]:
+    """Generates a continuation for every prompt; results come in the order of the prompts.
+    `prefill_chunk_size`: the most tokens of a prompt one step brings (None: whole prompts in one step)."""
     vocab = engine.plan.vocab
     config.validate(vocab)
     if not prompts:
         raise GenerationError("generation needs at least one prompt")
+    if prefill_chunk_size is not None:
+        if prefill_chunk_size <= 0:
+            raise GenerationError("prefill_chunk_size must be greater than zero")
+        longest_run = getattr(getattr(engine, "cache", None), "max_continued_run", None)
+        if longest_run is not None and prefill_chunk_size > longest_run:
+            raise GenerationError(f"prefill_chunk_size {prefill_chunk_size} exceeds the {longest_run} tokens a step may "
+                                  f"add to a sequence that already holds some (the model has windowed layers)")
     cache = engine.cache_config
     batches = plan_batches([len(p) for p in prompts], config.max_new_tokens, max_tokens=cache.max_tokens,
                            max_slots=cache.max_slots, max_context=cache.max_context, max_batch=max_batch)
@@ -131,7 +175,7 @@ def generate(engine, prompts: list[list[int]], config: GenerationConfig, *, max_
         if DecodeSession.usable(engine, config):
             session = DecodeSession(engine, config, max(len(b) for b in batches))
     for batch in batches:
-        run_batch(engine, sampler, [trackers[i] for i in batch], on_token, session)
+        run_batch(engine, sampler, [trackers[i] for i in batch], on_token, session, prefill_chunk_size)
     if session is not None:
         engine.last_session = session
     return [t.output for t in trackers]

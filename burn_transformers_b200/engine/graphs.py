@@ -21,7 +21,7 @@ import torch
 from .. import kernels
 from ..errors import KernelError
 from ..errors import GenerationError
-from .step import StepContext, Workspace
+from .step import PinnedStaging, StepContext, Workspace
 
 
 def _align4(n: int) -> int:
@@ -46,13 +46,14 @@ class DecodeMeta:
             total += _align4(n * table_width)
         self.total = total
         self.sizes = sizes
-        self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
-        self.host_np = self.host.numpy()
+        # two pinned buffers in turn: the host never rewrites integers whose copy to the device has not run yet
+        self.staging = PinnedStaging(total)
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)
         ar = np.arange(n + 1, dtype=np.int32)
-        self._set("token_seq", ar[:n])
-        self._set("seq_start", ar)
-        self._set("want_rows", ar[:n])
+        for self.host_np in self.staging.arrays:      # the sections that never change, in both buffers
+            self._set("token_seq", ar[:n])
+            self._set("seq_start", ar)
+            self._set("want_rows", ar[:n])
         # results of the selection kernel: ids, then the log-probabilities' bits
         self.out = torch.zeros(2 * n, dtype=torch.int32, device=device)
         self.seeds = torch.zeros(n, dtype=torch.int64, device=device)
@@ -71,6 +72,7 @@ class DecodeMeta:
 
     def fill(self, tokens, pasts, slots, tables, counters=None):
         """tables: per group, a list of page lists (one per sequence)."""
+        _, self.host_np = self.staging.next_buffer()
         pasts = np.asarray(pasts, dtype=np.int32)
         self._set("tokens", np.asarray(tokens, dtype=np.int32))
         self._set("positions", pasts)
@@ -87,7 +89,7 @@ class DecodeMeta:
             self.host_np[off:off + self.n * self.table_width] = flat.reshape(-1)
 
     def upload(self):
-        self.dev.copy_(self.host, non_blocking=True)
+        self.staging.copy_to(self.dev, self.total)
         return self.total * 4
 
 

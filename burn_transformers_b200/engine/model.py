@@ -44,6 +44,9 @@ class ModelPlan:
     probe: str | None = None
     ignored: frozenset[str] = frozenset()
     tied: dict[str, str] = dataclasses.field(default_factory=dict)
+    # for a name of `names` whose tensor is not stored under that name and as the part uses it: how it is made from
+    # the checkpoint's tensors (weights.spec.Stored / Split / Concat); the name is then only the model's own
+    sources: dict = dataclasses.field(default_factory=dict)
 
     def __post_init__(self):
         for index, call in enumerate(self.schedule):
@@ -58,7 +61,7 @@ class ModelPlan:
         tensors: dict[str, TensorSpec] = {}
         for name, (part, local) in self.names.items():
             tensors[name] = part.specs()[local]
-        return WeightPlan(tensors, self.namespaces, self.probe, self.ignored, dict(self.tied))
+        return WeightPlan(tensors, self.namespaces, self.probe, self.ignored, dict(self.tied), dict(self.sources))
 
     def cache_needs(self) -> list[CacheNeed]:
         """One entry per call of the schedule; readers of another call's cache need nothing."""

@@ -87,6 +87,40 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
+class PinnedStaging:
+    """Two pinned host buffers of int32, used in turn, each with the event of its last copy to the device.
+
+    A copy from pinned memory is asynchronous: it runs when the stream reaches it, which may be long after the call
+    returned (a step whose logits nobody reads is never waited for).  The host must not write the next step's
+    integers into a buffer whose copy has not run yet, or the earlier step would run with the later step's
+    tokens, positions and page tables.  `next_buffer` therefore waits for the buffer's last copy before handing it
+    out; with two buffers the host may run two steps ahead of the device before it waits at all."""
+
+    def __init__(self, count: int, pinned: bool = True):
+        self.count = count
+        self.pinned = pinned
+        self.buffers = [torch.zeros(count, dtype=torch.int32, pin_memory=pinned) for _ in range(2)]
+        self.arrays = [b.numpy() for b in self.buffers]
+        self.events = [None, None]
+        self.turn = 0
+
+    def next_buffer(self):
+        """(tensor, numpy view) of the buffer to fill now; waits until its previous copy has run."""
+        self.turn ^= 1
+        event = self.events[self.turn]
+        if event is not None:
+            event.synchronize()
+        return self.buffers[self.turn], self.arrays[self.turn]
+
+    def copy_to(self, device_tensor: torch.Tensor, count: int) -> None:
+        """Queues the copy of the current buffer's first `count` integers and remembers when it has run."""
+        device_tensor[:count].copy_(self.buffers[self.turn][:count], non_blocking=True)
+        if self.pinned:
+            if self.events[self.turn] is None:
+                self.events[self.turn] = torch.cuda.Event()
+            self.events[self.turn].record()
+
+
 class StepBuilder:
     """Turns a step's entries into a StepContext: packs the tokens, computes positions from the cache's
     lengths, and sends all integer tables of the step to the device in one copy from pinned memory."""
@@ -117,12 +151,12 @@ class StepBuilder:
         for size in sizes:
             offsets.append(total)
             total += _align4(max(1, size))
-        if self._host is None or self._host.numel() < total:
+        if self._host is None or self._host.count < total:
             cap = max(total, 4096)
-            self._host = torch.zeros(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
-            self._host_np = self._host.numpy()
+            # (the old buffers stay alive until their copies have run: torch keeps pinned memory of a queued copy)
+            self._host = PinnedStaging(cap, pinned=self.device.type == "cuda")
             self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
-        h = self._host_np
+        _, h = self._host.next_buffer()
         for i, e in enumerate(entries):
             lo, hi = seq_start[i], seq_start[i + 1]
             h[offsets[0] + lo:offsets[0] + hi] = e.tokens
@@ -136,7 +170,7 @@ class StepBuilder:
             for i, e in enumerate(entries):
                 row = cache.table_row(g, e.slot)
                 h[base + i * width:base + i * width + len(row)] = row
-        self._dev[:total].copy_(self._host[:total], non_blocking=True)
+        self._host.copy_to(self._dev, total)
         self.h2d_bytes_last = total * 4
         dev = self._dev
         view = lambda i: dev[offsets[i]:offsets[i] + max(1, sizes[i])]

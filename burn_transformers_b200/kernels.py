@@ -340,23 +340,17 @@ def attention_prefill_simt(q_proj, out, seq_start, past_len, n_seqs, max_new, n_
 def attention_prefill(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale, *,
                       impl=None, **kw):
     """Attention of several new tokens per sequence.  bfloat16 with a head size the kernels are built for runs on
-    tensor cores (tcgen05 with the scores in tensor memory, else mma.sync), everything else with the plain 32-bit
-    kernel.  `impl` ("tcgen05", "mma", "simt") asks for one kernel by name.  Arguments as attention_prefill_simt."""
-    lib = library()
+    tensor cores (tcgen05 with the scores in tensor memory), everything else with the plain 32-bit kernel.
+    `impl` ("tcgen05", "simt") asks for one kernel by name.  Arguments as attention_prefill_simt."""
     bf16 = q_proj.dtype == torch.bfloat16
     if impl is None:
         if bf16 and _supports("bt_attention_prefill_tcgen05_supports", head_dim, PAGE_SIZE):
             impl = "tcgen05"
-        elif bf16 and _supports("bt_attention_prefill_mma_supports", head_dim, PAGE_SIZE):
-            impl = "mma"
         else:
             impl = "simt"
     if impl == "tcgen05":
         return _attention_prefill_tcgen05(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads,
                                           head_dim, scale, **kw)
-    if impl == "mma":
-        return _attention_prefill_call(lib.bt_attention_prefill_mma, False, q_proj, out, seq_start, past_len, n_seqs,
-                                       max_new, n_heads, n_kv_heads, head_dim, scale, **kw)
     return attention_prefill_simt(q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim,
                                   scale, **kw)
 
@@ -383,29 +377,10 @@ def _attention_prefill_tcgen05(q_proj, out, seq_start, past_len, n_seqs, max_new
         c_int(head_dim), c_float(scale), c_int(1 if causal else 0), c_int(window), _stream()))
 
 
-def _attention_prefill_call(fn, with_dtype, q_proj, out, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads,
-                            head_dim, scale, *, causal=True, window=0, k_pool=None, v_pool=None, table=None,
-                            table_len=0, k_offset=None, v_offset=None):
-    _need(q_proj, "q_proj", (torch.float32, torch.bfloat16))
-    _need(out, "out", q_proj.dtype, (None, n_heads * head_dim))
-    stride = q_proj.shape[1]
-    es = q_proj.element_size()
-    if table is None:
-        k_ptr = c_void_p(q_proj.data_ptr() + k_offset * es)
-        v_ptr = c_void_p(q_proj.data_ptr() + v_offset * es)
-        t_ptr, t_stride = c_void_p(0), 0
-    else:
-        _need(k_pool, "k_pool", q_proj.dtype)
-        _need(v_pool, "v_pool", q_proj.dtype)
-        _need(table, "table", torch.int32)
-        k_ptr, v_ptr, t_ptr, t_stride = _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1]
-    args = [_ptr(q_proj), c_longlong(stride), k_ptr, v_ptr, t_ptr, c_int(t_stride), c_int(table_len), c_int(PAGE_SIZE),
-            c_longlong(stride), _ptr(out), _ptr(seq_start), _ptr(past_len), c_int(n_seqs), c_int(max_new), c_int(n_heads),
-            c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(1 if causal else 0), c_int(window)]
-    if with_dtype:
-        args.append(c_int(_code(q_proj.dtype)))
-    args.append(_stream())
-    _check(fn(*args))
+def attention_decode_supports(head_dim: int, row_stride: int, dtype) -> bool:
+    """Whether the decode-attention kernels take this head size: they move rows as 16-byte pieces, so a head and a
+    projection row must be whole pieces (8 bfloat16 or, as the kernel is built, 8 floats), at most 256 wide."""
+    return head_dim % 8 == 0 and row_stride % 8 == 0 and 0 < head_dim <= 256
 
 
 def attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits) -> int:

@@ -12,6 +12,7 @@ import math
 
 from ..config.gpt2 import Gpt2Config
 from ..config.registry import Architecture, register_architecture
+from ..errors import ConfigError
 from ..engine.model import LayerCall, ModelPlan
 from ..parts import (CausalSelfAttention, DenseFeedForward, LayerNorm, LearnedPositions, PreNormBlock, TiedReadout,
                      TokenEmbedding)
@@ -19,6 +20,14 @@ from ..parts import (CausalSelfAttention, DenseFeedForward, LayerNorm, LearnedPo
 
 def build_gpt2(config: Gpt2Config) -> ModelPlan:
     config.validate()
+    # what the configuration allows but this engine does not run is refused here, by field, before anything is built
+    if config.head_dim > CausalSelfAttention.MAX_HEAD_DIM:
+        raise ConfigError("gpt2", "n_head", f"n_embd / n_head = {config.head_dim} exceeds the largest head size the "
+                                            f"attention kernels take ({CausalSelfAttention.MAX_HEAD_DIM})")
+    if not config.causal:
+        # (the reference's `causal` is a knob of its stateless forward, src/models/gpt2/model.rs:22-24; with a cache a
+        # token never sees later ones, so a non-causal forward cannot be reproduced step by step)
+        raise ConfigError("gpt2", "causal", "an engine with a cache decodes causally; `causal: false` is not executable")
     d, std = config.n_embd, config.initializer_range
     # projections that write into the residual stream start narrower (src/models/gpt2.rs:188-222)
     residual_std = std / math.sqrt(2.0 * config.n_layer)

@@ -5,7 +5,7 @@ import torch
 
 from .. import kernels
 from ..cache.spec import PAGE_SIZE, CacheNeed, KvSpec
-from ..errors import CacheError
+from ..errors import CacheError, ShapeError
 from ..weights.spec import MATRIX, VECTOR, TensorSpec
 from .base import Mixer
 from .linear import linear
@@ -33,14 +33,16 @@ class CausalSelfAttention(Mixer):
 
     accepts_lazy_norm = True
     linear_weights = ("qkv.weight", "out.weight")
+    MAX_HEAD_DIM = 256      # every head size up to this runs (the kernels made for 16-byte pieces where they fit)
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, *,
                  causal: bool = True, window: int | None = None, bias: bool = True,
                  init_std: float = 0.02, out_init_std: float | None = None, positions=None):
-        if n_heads % n_kv_heads:
-            raise ValueError(f"{n_heads} query heads cannot share {n_kv_heads} key heads")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"head_dim {head_dim} must be a multiple of 16 and at most 256")
+        if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
+            raise ShapeError(f"{n_heads} query heads cannot share {n_kv_heads} key heads")
+        if not 1 <= head_dim <= self.MAX_HEAD_DIM:
+            raise ShapeError(f"head_dim {head_dim} is outside 1..{self.MAX_HEAD_DIM}, the head sizes the attention "
+                             f"kernels take")
         self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
         self.scale, self.causal, self.window, self.has_bias = float(scale), causal, window, bias
         # a position encoding that rotates (parts.base.PositionEncoding.rotates): applied to the new queries and
@@ -101,7 +103,15 @@ class CausalSelfAttention(Mixer):
                    residual=residual, w_is_nk=self.nk_out_weight)
             return
         mixed = ctx.ws.take((n, self.q_width), dtype)
-        if ctx.is_decode:
+        if ctx.is_decode and not kernels.attention_decode_supports(self.head_dim, proj.shape[1], dtype):
+            # a head size whose rows are no whole 16-byte pieces: the step's keys and values are filed first, then
+            # the kernel that reads element by element attends over the pages (one new token per sequence)
+            kernels.kv_append(proj, self.q_width, self.q_width + self.kv_width, ctx.positions, ctx.token_seq,
+                              ctx.ctx_len, table, group.table_len, k_pool, v_pool, n, self.n_kv_heads, self.head_dim)
+            kernels.attention_prefill(proj, mixed, ctx.seq_start, ctx.past_len, ctx.n_seqs, 1, self.n_heads,
+                                      self.n_kv_heads, self.head_dim, self.scale, causal=self.causal, window=window,
+                                      k_pool=k_pool, v_pool=v_pool, table=table, table_len=group.table_len)
+        elif ctx.is_decode:
             splits = self._splits(ctx)
             kernels.attention_decode(proj, mixed, k_pool, v_pool, table, group.table_len, ctx.ctx_len, ctx.n_seqs,
                                      self.n_heads, self.n_kv_heads, self.head_dim, self.scale, window=window,
@@ -114,9 +124,10 @@ class CausalSelfAttention(Mixer):
                                            causal=self.causal, window=window,
                                            k_offset=self.q_width, v_offset=self.q_width + self.kv_width)
         else:
-            if group.is_ring:
-                raise CacheError("a step that brings several tokens to sequences that already hold some is not "
-                                 "supported for windowed layers: their ring of pages keeps one window only")
+            if group.is_ring and ctx.max_new > group.table_len * PAGE_SIZE - self.window + 1:
+                # (the engine refuses such a step before the cache changes; this guards direct users of the part)
+                raise CacheError("a step that brings this many tokens to sequences that already hold some would "
+                                 "overwrite keys of a windowed layer's ring that its first tokens still see")
             kernels.attention_prefill(proj, mixed, ctx.seq_start, ctx.past_len, ctx.n_seqs, ctx.max_new,
                                            self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
                                            causal=self.causal, window=window, k_pool=k_pool, v_pool=v_pool,

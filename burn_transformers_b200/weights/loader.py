@@ -15,7 +15,8 @@ import torch
 
 from ..errors import CheckpointError
 from . import safetensors_io as st
-from .spec import MATRIX, TABLE, VECTOR, WeightPlan
+from .spec import MATRIX, TABLE, VECTOR, Stored, WeightPlan, resolve
+from .spec import stored_shapes as stored_shapes_of
 
 SINGLE = "model.safetensors"
 INDEX = "model.safetensors.index.json"
@@ -71,12 +72,13 @@ def check(plan: WeightPlan, entries: dict[str, st.TensorEntry]) -> tuple[str, di
             local[name[len(prefix):]] = entry
         else:
             outside.append(name)
-    missing = sorted(n for n in plan.tensors if n not in local)
-    unexpected = sorted(n for n in local if n not in plan.tensors and n not in plan.ignored and n not in plan.tied)
+    wanted = plan.stored()        # (stored name -> shape and kind: the model's tensors seen through their sources)
+    missing = sorted(n for n in wanted if n not in local)
+    unexpected = sorted(n for n in local if n not in wanted and n not in plan.ignored and n not in plan.tied)
     # names outside the namespace are unexpected unless they are a tied alias (lm_head.weight next to transformer.*)
     unexpected += sorted(n for n in outside if n not in plan.tied)
     mismatched = []
-    for name, spec in plan.tensors.items():
+    for name, spec in wanted.items():
         entry = local.get(name)
         if entry is None:
             continue
@@ -112,7 +114,7 @@ def check(plan: WeightPlan, entries: dict[str, st.TensorEntry]) -> tuple[str, di
         if st.read_raw(entry) != st.read_raw(other):
             raise CheckpointError(f"tied tensor `{alias}` differs from `{plan.tied[alias]}`",
                                   mismatched=[f"{alias}: bytes differ from {plan.tied[alias]}"])
-    return prefix, {name: local[name] for name in plan.tensors}
+    return prefix, {name: local[name] for name in wanted}
 
 
 def keep_dtype(kind: str, compute_dtype: torch.dtype) -> torch.dtype:
@@ -131,13 +133,26 @@ def load_weights(folder, plan: WeightPlan, dtype: str, device) -> tuple[dict[str
         raise CheckpointError(f"dtype must be one of {sorted(COMPUTE_DTYPES)}, found `{dtype}`")
     compute = COMPUTE_DTYPES[dtype]
     _, entries = check(plan, discover(folder))
+    stored_host: dict[str, torch.Tensor] = {}
     tensors, report = {}, []
-    for name, entry in entries.items():
-        spec = plan.tensors[name]
+    for name, spec in plan.tensors.items():
+        source = plan.source_of(name)
         target = keep_dtype(spec.kind, compute)
-        host = st.read_tensor(entry)
+        if isinstance(source, Stored) and not source.transposed:
+            host = st.read_tensor(entries[source.name])          # (read, used and dropped: one tensor at a time)
+            action = "map"
+        else:
+            for stored_name, _ in stored_shapes_of(source, spec.shape):
+                if stored_name not in stored_host:
+                    stored_host[stored_name] = st.read_tensor(entries[stored_name])
+            host = resolve(source, stored_host)
+            action = type(source).__name__.lower() if not isinstance(source, Stored) else "transpose"
         kept = host.to(target).contiguous().to(device)
+        if tuple(kept.shape) != tuple(spec.shape):
+            raise CheckpointError(f"{name}: its source makes shape {list(kept.shape)}, the model wants {list(spec.shape)}")
         tensors[name] = kept
-        report.append(dict(name=name, shape=list(entry.shape), stored=entry.dtype,
-                           kept=str(target).replace("torch.", ""), bytes=kept.numel() * kept.element_size()))
+        stored_dtypes = sorted({entries[n].dtype for n, _ in stored_shapes_of(source, spec.shape)})
+        report.append(dict(name=name, shape=list(spec.shape), stored="/".join(stored_dtypes),
+                           kept=str(target).replace("torch.", ""), bytes=kept.numel() * kept.element_size(),
+                           action=action))
     return tensors, report

@@ -63,10 +63,11 @@ def standard_normal(seed: int, name: str, count: int) -> np.ndarray:
 
 
 def random_tensors(plan: WeightPlan, seed: int, *, storage: str = "bfloat16", loud: bool = False) -> dict[str, torch.Tensor]:
-    """Host tensors for every name of the plan.  Matrices are stored in `storage`, vectors in float32."""
+    """Host tensors for every tensor a checkpoint of the plan stores (under its stored name and in its stored
+    layout).  Matrices are stored in `storage`, vectors in float32."""
     matrix_dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[storage]
     tensors = {}
-    for name, spec in plan.tensors.items():
+    for name, spec in plan.stored().items():
         count = int(np.prod(spec.shape)) if spec.shape else 1
         kind = spec.init[0]
         if kind == "normal":

@@ -87,3 +87,26 @@ def test_plan_has_every_tensor_once():
     assert names["h.0.mlp.c_fc.weight"].shape == (64, 256)
     assert names["wpe.weight"].shape == (128, 64)
     assert [c.block for c in plan.schedule] == [0, 1]
+
+
+@pytest.mark.parametrize("patch, field", [
+    ({"n_embd": 1028, "n_head": 2}, "n_head"),      # head size 514: more than the attention kernels take
+    ({"causal": False}, "causal"),                   # a cached engine decodes causally
+])
+def test_what_the_engine_does_not_run_is_refused_by_field_when_the_model_is_built(patch, field):
+    """config.json may ask for things that parse and validate but that this engine cannot execute; the builder
+    refuses them as a configuration error that names the field, never as a bare exception from a part."""
+    from burn_transformers_b200.models.gpt2 import build_gpt2
+    config = Gpt2Config.from_dict(dict({"model_type": "gpt2", "n_layer": 1, "vocab_size": 32, "n_positions": 16}, **patch))
+    with pytest.raises(ConfigError) as info:
+        build_gpt2(config)
+    assert info.value.field == field and str(info.value).startswith(f"gpt2.{field}: ")
+
+
+@pytest.mark.parametrize("n_embd, n_head", [(12, 3), (15, 3), (7, 1), (36, 3), (40, 5)])
+def test_every_head_size_the_configuration_allows_builds(n_embd, n_head):
+    """The reference asks only that n_head divide n_embd (src/models/gpt2.rs:258-318); its own fixture has head size 4."""
+    from burn_transformers_b200.models.gpt2 import build_gpt2
+    plan = build_gpt2(Gpt2Config.from_dict({"model_type": "gpt2", "n_layer": 1, "vocab_size": 19, "n_positions": 16,
+                                            "n_embd": n_embd, "n_head": n_head}))
+    assert plan.blocks[0].mixer.head_dim == n_embd // n_head

@@ -174,3 +174,27 @@ def test_random_streams():
     assert interior_unit_f32(0) == 2.0 ** -24 and interior_unit_f32((1 << 64) - 1) == 1 - 2.0 ** -24
     assert uniform(5, 3) == interior_unit_f32(splitmix64(5, 3))
     assert sequence_stream(5, 0) != sequence_stream(5, 1)
+
+
+def test_chunked_prefill_cuts_prompts_by_columns_and_asks_logits_only_where_a_prompt_ends():
+    """With a chunk size every step brings at most that many tokens of each prompt that still has some; a prompt
+    that has ended sits out the later portions; logits are wanted only at each prompt's last token
+    (src/generation/causal.rs:341-396 of the reference)."""
+    engine = FakeEngine()
+    script = {0: [1, 2], 1: [5, 6], 2: [9, 10]}
+    out = generate(engine, [[1, 2, 3], [4], [5, 6, 7, 8, 9]], GenerationConfig(max_new_tokens=2),
+                   sampler=ScriptedSampler(script), prefill_chunk_size=2)
+    assert [o.token_ids for o in out] == [[1, 2], [5, 6], [9, 10]]
+    assert engine.steps[0] == [(0, [1, 2], []), (1, [4], [0]), (2, [5, 6], [])]
+    assert engine.steps[1] == [(0, [3], [0]), (2, [7, 8], [])]
+    assert engine.steps[2] == [(2, [9], [0])]
+    assert engine.steps[3] == [(0, [1], [0]), (1, [5], [0]), (2, [9], [0])]      # then one token each
+    assert len(engine.steps) == 4 and not engine.live
+    # a chunk as long as the longest prompt is the one-shot prefill
+    engine = FakeEngine()
+    generate(engine, [[1, 2, 3], [4]], GenerationConfig(max_new_tokens=1), sampler=ScriptedSampler({0: [1], 1: [2]}),
+             prefill_chunk_size=3)
+    assert engine.steps == [[(0, [1, 2, 3], [2]), (1, [4], [0])]]
+    with pytest.raises(GenerationError, match="prefill_chunk_size"):
+        generate(FakeEngine(), [[1]], GenerationConfig(max_new_tokens=1), sampler=ScriptedSampler({0: [1]}),
+                 prefill_chunk_size=0)

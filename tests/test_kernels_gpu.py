@@ -377,7 +377,9 @@ def test_attention_decode_window_edge(dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hq, hkv, hd, window, causal", [
     (4, 4, 16, 0, True), (5, 5, 48, 0, True), (6, 3, 80, 0, True), (2, 1, 128, 40, True), (2, 2, 256, 0, True),
-    (3, 3, 64, 0, False), (3, 3, 64, 0, True), (4, 2, 64, 70, True), (2, 2, 128, 0, True)])
+    (3, 3, 64, 0, False), (3, 3, 64, 0, True), (4, 2, 64, 70, True), (2, 2, 128, 0, True),
+    # head sizes whose rows are no whole 16-byte pieces: copied and read element by element
+    (3, 3, 4, 0, True), (2, 1, 7, 30, True), (5, 5, 20, 0, True), (2, 2, 1, 0, True), (2, 1, 100, 0, True)])
 def test_attention_prefill_packed_and_paged(dtype, hq, hkv, hd, window, causal):
     """Several new tokens per sequence: from the step's own projections (sequences that start at 0) and from
     the pages (sequences that already hold tokens), with unequal lengths."""
@@ -423,7 +425,7 @@ def test_attention_prefill_packed_and_paged(dtype, hq, hkv, hd, window, causal):
         assert rel(got, want) < TOL[dtype] * 2, f"paged, sequence {s}"
 
 
-@pytest.mark.parametrize("impl", ["tcgen05", "mma"])
+@pytest.mark.parametrize("impl", ["tcgen05"])
 @pytest.mark.parametrize("hq, hkv, hd, window, causal", [(3, 3, 64, 0, True), (4, 2, 64, 150, True), (2, 1, 128, 0, True),
                                                          (2, 2, 128, 300, True), (2, 2, 64, 0, False)])
 def test_attention_prefill_long_sequences_on_tensor_cores(impl, hq, hkv, hd, window, causal):
@@ -474,7 +476,7 @@ def test_attention_prefill_long_sequences_on_tensor_cores(impl, hq, hkv, hd, win
         assert rel(got, want) < TOL[dtype] * 2, f"paged, sequence {s}"
 
 
-@pytest.mark.parametrize("impl", ["tcgen05", "mma"])
+@pytest.mark.parametrize("impl", ["tcgen05"])
 @pytest.mark.parametrize("hd", [64, 128])
 def test_attention_prefill_far_key_future_key_and_window_edge(impl, hd):
     """One key among hundreds answers a late query: in another key tile far back it must be found, one position in
@@ -524,8 +526,8 @@ def test_attention_prefill_never_looks_ahead(dtype, hd):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_kv_append_pages_and_ring(dtype):
-    hkv, hd = 3, 16
+@pytest.mark.parametrize("hkv, hd", [(3, 16), (3, 4), (2, 7), (1, 1), (2, 100)])
+def test_kv_append_pages_and_ring(dtype, hkv, hd):
     news, pasts = [70, 1], [60, 127]
     lengths = [p + n for p, n in zip(pasts, news)]
     n_tok = sum(news)
@@ -644,3 +646,53 @@ def test_logit_edits():
                          1.0, 1.0, 3.0, 0.0], device=DEV)
     kernels.logit_edits(z, rows, toks, vals, 4)
     assert z.cpu().tolist() == [[0.5, -4.0, 3.0, -math.inf, 0.5], [1.0, 1.0, 1.0, 1.0, -1.0]]
+
+
+@pytest.mark.parametrize("vocab", [777, 50257])
+def test_a_uniform_next_to_one_selects_the_last_survivor_never_a_filtered_token(vocab):
+    """The threshold u * total and the running sums round differently; with u a few units in the last place below 1 the
+    count of sums below the threshold may run past the last token that survived the filters.  Whatever the rounding,
+    the selected token must be one of the survivors: here the top 3 of each row, none of them the last index."""
+    g = torch.Generator().manual_seed(vocab)
+    z = (torch.randn(64, vocab, generator=g) * 2).to(DEV)
+    z[:, vocab - 1] = -30.0                      # the token the count would end on is filtered out
+    top = torch.topk(z, 3, dim=-1).indices.cpu()
+    for u in (1.0 - 2.0 ** -24, 1.0 - 2.0 ** -23, 0.999999):
+        uniforms = torch.full((64,), u, dtype=torch.float32, device=DEV)
+        ids, logp = run_sample(z, do_sample=True, temperature=0.7, top_k=3, uniforms=uniforms)
+        for r, token in enumerate(ids):
+            assert token in top[r].tolist(), (u, r, token)
+            assert token == int(top[r].max()), "the largest uniform selects the survivor with the largest index"
+        assert all(np.isfinite(logp))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("splits, new_kv", [(1, False), (3, False), (2, True)])
+def test_attention_decode_with_an_empty_sequence_in_the_batch(dtype, splits, new_kv):
+    """ctx_len 0 (an empty or finished request that still rides in the batch): zeros for that row, no page touched
+    (with `new_kv` the kernel would otherwise file a key at position -1), the other rows as usual."""
+    hq, hkv, hd = 4, 2, 64
+    lengths = [130, 0, 64]
+    k_pool, v_pool, table, dk, dv = make_paged([130, 1, 64], hkv, hd, dtype)
+    q = torch.randn(3, (hq + 2 * hkv) * hd, device=DEV).to(dtype)
+    ctx_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    pools_before = (k_pool.clone(), v_pool.clone())
+    offsets = (hq * hd, (hq + hkv) * hd) if new_kv else None
+    scratch = torch.empty(max(1, kernels.attention_decode_scratch_floats(3, hq, hd, splits)), device=DEV)
+    for in_scratch, tensor_cores in ((False, True), (True, False)):
+        out = torch.full((3, hq * hd), float("nan"), device=DEV, dtype=dtype)
+        kernels.attention_decode(q, out, k_pool, v_pool, table, table.shape[1], ctx_len, 3, hq, hkv, hd, 0.2,
+                                 n_splits=splits, scratch=scratch, max_ctx=130, merge_in_scratch=in_scratch,
+                                 tensor_cores=tensor_cores, new_kv_offsets=offsets)
+        torch.cuda.synchronize()
+        assert float(out[1].float().abs().max()) == 0.0
+        page = int(table[1, 0])
+        assert torch.equal(k_pool[page], pools_before[0][page]) and torch.equal(v_pool[page], pools_before[1][page])
+        for s in (0, 2):
+            keys, values = dk[s].clone(), dv[s].clone()
+            if new_kv:      # the newest key and value come from the projection row
+                keys[-1] = q[s, offsets[0]:offsets[0] + hkv * hd].double().cpu().view(hkv, hd)
+                values[-1] = q[s, offsets[1]:offsets[1] + hkv * hd].double().cpu().view(hkv, hd)
+            want = attend(q[s, :hq * hd].double().cpu().view(1, hq, hd), keys, values, 0.2, torch.tensor([lengths[s] - 1]))
+            assert rel(out[s].view(1, hq, hd), want) < TOL[dtype] * 2
+    assert int(kernels.kernel_status(q.device)) == 0

@@ -450,5 +450,46 @@ def test_toy_architecture_with_rotation_a_window_and_routed_experts(tmp_path):
             for sl in slots:
                 engine.release(sl)
             engine.cache.check()
+        # a step may bring several tokens to a sequence that already holds some: as many as the windowed layer's ring
+        # of pages allows (64 - 24 + 1 = 41 here); the run 50..79 wraps around the ring
+        assert engine.cache.max_continued_run == 41
+        slot = engine.new_sequence()
+        seq = seqs[0]
+        engine.step([StepEntry(slot, seq[:50], [])])
+        got = engine.step([StepEntry(slot, seq[50:80], list(range(30)))])
+        assert rel(got, want[0][50:80]) < 1e-4
+        with pytest.raises(bt.CacheError, match="at most 41 tokens"):
+            engine.step([StepEntry(slot, (seq * 2)[:42], [])])
+        assert engine.length(slot) == 80
+        got = engine.step([StepEntry(slot, seq[80:], [len(seq) - 81])])
+        assert rel(got[0], want[0][-1]) < 1e-4
+        engine.release(slot)
+        with pytest.raises(bt.GenerationError, match="prefill_chunk_size 42"):
+            bt.generate(engine, [seq[:50]], bt.GenerationConfig(max_new_tokens=2), prefill_chunk_size=42)
     finally:
         unregister_architecture("toy_routed")
+
+
+def test_a_checkpoint_with_separate_transposed_projections_runs_in_the_same_parts(tmp_path):
+    """Queries, keys and values stored as three [out, in] matrices (and the other projections transposed too) load
+    into the unchanged CausalSelfAttention and DenseFeedForward through the plan's sources, and the engine gives
+    bit for bit the logits of the fused [in, out] checkpoint."""
+    from burn_transformers_b200.weights import load_weights
+    from test_weights import split_qkv_plan, store_split
+    from tiny_configs import TINY_B, make_folder, random_prompts
+    fused = make_folder(tmp_path / "fused", TINY_B, seed=5, storage="float32", loud=True)
+    split = make_folder(tmp_path / "split", TINY_B, seed=5, storage="float32", loud=True)
+    store_split(split)
+    seqs = random_prompts(TINY_B, [19, 70], seed=2)
+    for dtype in ("float32", "bfloat16"):
+        want_engine = bt.Engine.from_folder(fused, dtype, max_tokens=64 * 4)
+        plan = split_qkv_plan(split)
+        tensors, _ = load_weights(split, plan.weights, dtype, torch.device(DEV))
+        got_engine = bt.Engine(plan, tensors, dtype, CacheConfig(64 * 4, 4, plan.max_context), DEV)
+        for seq in seqs:
+            logits = []
+            for engine in (want_engine, got_engine):
+                slot = engine.new_sequence()
+                logits.append(engine.step([StepEntry(slot, seq, list(range(len(seq))))]).clone())
+                engine.release(slot)
+            assert torch.equal(logits[0], logits[1])

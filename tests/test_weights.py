@@ -137,3 +137,79 @@ def test_loud_weights_move_every_tensor(tmp_path):
     assert float(t["h.0.attn.c_attn.bias"].abs().max()) > 0
     assert float((t["ln_f.weight"] - 1).abs().max()) > 0
     assert float(t["h.0.attn.c_attn.weight"].std()) > 0.1
+
+
+# ---- tensors that are made from stored tensors: Stored(transposed), Split, Concat ---------------------------------
+
+def split_qkv_plan(folder):
+    """GPT-2's plan for a checkpoint that stores queries, keys and values separately and every projection [out, in]
+    (the layout most other decoders' checkpoints have): only the sources differ, the parts are the same."""
+    from burn_transformers_b200.weights.spec import Concat, Stored
+    arch, config = config_from_folder(folder)
+    model = arch.build(config)
+    for i in range(config.n_layer):
+        p = f"h.{i}."
+        model.sources[p + "attn.c_attn.weight"] = Concat(tuple(Stored(p + f"attn.{x}.weight", transposed=True) for x in "qkv"), axis=1)
+        model.sources[p + "attn.c_attn.bias"] = Concat(tuple(Stored(p + f"attn.{x}.bias") for x in "qkv"), axis=0)
+        model.sources[p + "attn.c_proj.weight"] = Stored(p + "attn.o.weight", transposed=True)
+        model.sources[p + "mlp.c_fc.weight"] = Stored(p + "mlp.up.weight", transposed=True)
+    return model
+
+
+def store_split(folder):
+    """Rewrites a GPT-2 folder's file in the layout of `split_qkv_plan`."""
+    def edit(t):
+        for name in [n for n in t if n.endswith("attn.c_attn.weight")]:
+            p = name[:-len("attn.c_attn.weight")]
+            w, b = t.pop(name), t.pop(p + "attn.c_attn.bias")
+            d = w.shape[0]
+            for j, x in enumerate("qkv"):
+                t[p + f"attn.{x}.weight"] = w[:, j * d:(j + 1) * d].t().contiguous()
+                t[p + f"attn.{x}.bias"] = b[j * d:(j + 1) * d].contiguous()
+            t[p + "attn.o.weight"] = t.pop(p + "attn.c_proj.weight").t().contiguous()
+            t[p + "mlp.up.weight"] = t.pop(p + "mlp.c_fc.weight").t().contiguous()
+    rewrite(folder, edit)
+
+
+def test_separate_transposed_projections_load_into_the_same_parts(tmp_path):
+    fused = make_folder(tmp_path / "fused", TINY_B, seed=5, storage="float32", loud=True)
+    split = make_folder(tmp_path / "split", TINY_B, seed=5, storage="float32", loud=True)
+    store_split(split)
+    want, _ = load_weights(fused, plan_of(fused), "float32", "cpu")
+    plan = split_qkv_plan(split).weights
+    got, report = load_weights(split, plan, "float32", "cpu")
+    assert set(got) == set(want) and all(torch.equal(got[n], want[n]) for n in want)
+    assert all(t.is_contiguous() for t in got.values())
+    actions = {r["name"]: r["action"] for r in report}
+    assert actions["h.0.attn.c_attn.weight"] == "concat" and actions["h.0.attn.c_proj.weight"] == "transpose"
+    assert actions["wte.weight"] == "map"
+    # the strict accounting is kept, in the checkpoint's own names
+    with pytest.raises(CheckpointError) as info:
+        check(plan_of(fused), discover(split))
+    assert "h.0.attn.q.weight" in info.value.unexpected and "h.0.attn.c_attn.weight" in info.value.missing
+    rewrite(split, lambda t: (t.pop("h.1.attn.k.bias"), t.__setitem__("h.2.attn.v.weight", torch.zeros(96, 95))))
+    with pytest.raises(CheckpointError) as info:
+        check(plan, discover(split))
+    assert info.value.missing == ["h.1.attn.k.bias"]
+    assert any(m.startswith("h.2.attn.v.weight: expected shape [96, 96]") for m in info.value.mismatched)
+
+
+def test_split_reads_pieces_of_one_stored_tensor():
+    from burn_transformers_b200.weights.spec import MATRIX, Concat, Split, Stored, TensorSpec, WeightPlan, resolve
+    plan = WeightPlan({"q": TensorSpec((4, 6)), "k": TensorSpec((4, 2)), "v": TensorSpec((4, 2))},
+                      sources={"q": Split("qkv", 1, (6, 2, 2), 0), "k": Split("qkv", 1, (6, 2, 2), 1),
+                               "v": Split("qkv", 1, (6, 2, 2), 2)})
+    assert {n: s.shape for n, s in plan.stored().items()} == {"qkv": (4, 10)}
+    stored = {"qkv": torch.arange(40.0).reshape(4, 10)}
+    assert torch.equal(resolve(plan.source_of("k"), stored), stored["qkv"][:, 6:8])
+    # stored the other way round: [10, 4]
+    flipped = WeightPlan({"k": TensorSpec((4, 2))}, sources={"k": Split("qkv_t", 1, (6, 2, 2), 1, transposed=True)})
+    assert flipped.stored()["qkv_t"].shape == (10, 4)
+    assert torch.equal(resolve(flipped.source_of("k"), {"qkv_t": stored["qkv"].t().contiguous()}), stored["qkv"][:, 6:8])
+    # two readers that disagree about a stored tensor's shape are a fault of the plan
+    bad = WeightPlan({"a": TensorSpec((4, 6)), "b": TensorSpec((4, 3))},
+                     sources={"a": Split("x", 1, (6, 2), 0), "b": Split("x", 1, (3, 3), 0)})
+    with pytest.raises(ValueError, match="is asked for as"):
+        bad.stored()
+    with pytest.raises(ValueError, match="cannot make"):
+        WeightPlan({"a": TensorSpec((4, 7))}, sources={"a": Concat((Stored("p"), Stored("q")), 1)}).stored()
