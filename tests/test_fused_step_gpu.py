@@ -150,3 +150,27 @@ def test_a_refused_launch_of_the_fused_step_falls_back_to_separate_kernels(case,
     assert engine.use_fused_step is False and not fused_programs(engine)
     err, where = replay.worst_error(got, ref)
     assert err < TOL_BF16, f"after the refusal: {err:.3e} at {where}"
+
+
+@pytest.mark.parametrize("splits", [None, 1, 3])
+def test_fused_step_at_long_contexts_with_loud_weights(splits, monkeypatch, tmp_path):
+    """With weights of the usual scale attention is nearly uniform, and a lost or misplaced page of keys moves the
+    logits by less than a bfloat16 rounding.  Loud weights make the softmax pick out single keys anywhere in the
+    context: contexts of 333 and 700 tokens (6 and 11 pages, more than a block's ring of page slots holds when one
+    block takes a whole head), decoded through the fused step with the splits it chooses, with one and with three."""
+    cfg = FUSED_CONFIGS["h64"]
+    folder = make_folder(tmp_path, cfg, seed=21, storage="bfloat16", loud=True)
+    pcfg, pw = plain.load_model(folder)
+    seqs = random_prompts(cfg, [333, 700], seed=6)
+    rounded = {k: (plain.round_to_bf16(v) if v.ndim == 2 else v) for k, v in pw.items()}
+    ref = [plain.logits(pcfg, rounded, s, quant=plain.round_to_bf16) for s in seqs]
+    monkeypatch.setattr(step_program, "SPLITS_OVERRIDE", splits)
+    engine = Engine.from_folder(folder, "bfloat16", max_tokens=64 * 20)
+    got = replay.tail_one_by_one(engine, seqs, tail=12)
+    assert fused_programs(engine), "the decode steps did not run as a fused step"
+    err, where = replay.worst_error(got, ref)
+    assert err < TOL_BF16, f"fused, loud, splits {splits}: {err:.3e} at {where}"
+    # both sequences decoding together (two rows, unequal lengths)
+    both = replay.batches(engine, seqs, [[0, 1]], [len(s) - 6 for s in seqs])
+    err, where = replay.worst_error(both, ref)
+    assert err < TOL_BF16, f"fused batch, loud, splits {splits}: {err:.3e} at {where}"
