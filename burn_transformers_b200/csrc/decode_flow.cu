@@ -1,0 +1,1260 @@
+// A whole decode step (at most 16 sequences, one token each, bfloat16) as ONE persistent kernel in which data,
+// not barriers, tells a block when to go on.
+//
+// A decode step of a small model is a chain of some sixty short dependent operations (per layer: LayerNorm +
+// projection -> attention -> output projection + residual -> LayerNorm + feed-forward up + GELU -> feed-forward
+// down + residual).  Every link of the chain needs whole rows that all blocks produced, so every link is a
+// hand-over between all multiprocessors; what a link costs is the round trips to the L2 cache that the hand-over
+// takes.  A grid barrier costs three (a release fence that waits for the block's stores, the arrival at the
+// counter, the poll that sees it) and the load of the rows after it a fourth.  Here a hand-over costs one:
+//
+//   * Everything that passes from one phase to the next carries a tag that says which launch (and, for the residual
+//     stream, which phase) wrote it: a bfloat16 value travels as a 32-bit word (value | tag << 16), a 32-bit value
+//     as a 64-bit pair (value, tag).  A word or a pair is written and read by one instruction, so a reader sees
+//     either the old tag or the new value with its tag, never a mix.  A consumer simply loads the rows it needs and
+//     looks at the tags; what is not there yet is loaded again (with a limit: see "waits").  No fence, no counter,
+//     no second trip.  Buffers are zeroed before first use and tags are never zero.
+//   * Weights and cache pages never change during a step.  Two producer warps of every block walk the phase list
+//     on their own, ahead of the computing warps: one streams the block's weight tiles through a ring of slots in
+//     shared memory (bulk copies, one per 8 x 512 piece of W[N, K]), the other the block's pages of keys and values
+//     (tensor-map copies with the 128-byte swizzle).  The rings are the only coupling: a slot is handed back when
+//     its last reader is done.  The weight stream therefore runs through hand-overs and phases without a pause.
+//   * Matrix products: a phase's output columns are dealt out in tiles of 8 to the blocks; the 8 computing warps of
+//     a block split K (32 elements at a time, round-robin), take A from a shared-memory panel of the (at most 16)
+//     rows and B from the ring, both with ldmatrix, and add their partial sums through shared memory in a fixed
+//     order.  The panel is built once per block and phase from tagged rows: copied, or LayerNorm-ed (32-bit
+//     statistics, two passes over registers).
+//   * Attention is the tensor-core routine of decode_mma.cuh over the pages in the ring.  With several splits per
+//     (sequence, head) every split leaves a tagged partial result and the block of split 0 merges them, in split
+//     order, as soon as their tags show up: the projection after it reads plain rows.
+//   * Nothing is accumulated with atomics and every sum has a fixed order: results do not depend on timing.
+//
+// The one place where the step still meets at a grid barrier is before token selection, which reads the plain
+// 32-bit logits (they are also the step's result for the host) or the readout's per-block partials.
+//
+// Waits.  Every wait (a tag that does not show up, a ring slot that is not filled or not handed back, the grid
+// barrier) is bounded.  A block that gives up sets the status word, which every other waiting block looks at now and
+// then, so that all blocks leave soon after; a producer warp waits (bounded) for its own copies in flight before it
+// returns.  The launch is cooperative (one block per multiprocessor, all resident), which the waiting relies on.
+#include "common.cuh"
+#include "sampling.cuh"
+#include "tma.cuh"
+#include "decode_mma.cuh"
+
+namespace bt {
+
+constexpr int DF_CWARPS = 8, DF_CONSUMERS = DF_CWARPS * 32;     // warps that compute
+constexpr int DF_THREADS = DF_CONSUMERS + 64;                   // + the weight producer and the page producer
+constexpr int DF_KC = 512;                       // k extent of a weight slot
+constexpr int DF_WROW = DF_KC * 2 + 16;          // bytes between the 8 rows of a slot (16 apart modulo 128: no bank conflicts)
+constexpr int DF_WSLOT = 8 * DF_WROW;
+constexpr int DF_MAX_WSLOTS = 24, DF_MAX_PSLOTS = 16;
+constexpr int DF_MAX_ITEMS = 8;                  // (sequence, head, split) items of an attention phase a block takes, at most
+constexpr int DF_TABLE_CACHE = 64;               // page-table entries per sequence kept in shared memory
+constexpr int DF_SPIN_LIMIT = 1 << 21;           // tries of any wait before a block gives up
+constexpr int DF_TRACE_SLOTS = 8;
+
+enum { FP_EMBED = 0, FP_LINEAR = 1, FP_ATTENTION = 2, FP_SAMPLE = 3 };
+enum { FA_ROWS = 0, FA_LAYERNORM = 1 };
+enum { FO_WORDS = 0, FO_PAIRS = 1, FO_PLAIN = 2 };
+
+struct FlowPhase {
+  int type, M;
+  // ---- linear: out[M, N] = act(A @ w^T + bias) (+ residual) ----
+  int a_kind;                    // FA_ROWS: tagged bfloat16 words [M][K]; FA_LAYERNORM: LayerNorm of tagged 32-bit pairs [.][K]
+  int N, K, act;
+  int out_kind;                  // FO_WORDS: tagged bfloat16 words; FO_PAIRS: tagged 32-bit pairs (the residual stream, added to);
+                                 // FO_PLAIN: plain 32-bit (the logits)
+  int a_src;                     // FA_LAYERNORM: index of the phase that wrote the pairs this phase reads
+  int res_src;                   // FO_PAIRS: index of the phase that last wrote the pairs this phase adds to
+  int pad0_;
+  const void* a;
+  const int* rows;               // FA_LAYERNORM: row r of the panel is row rows[r] of `a` (null: r)
+  const float* gamma;
+  const float* beta;
+  float eps;
+  int pad1_;
+  const __nv_bfloat16* w;        // [N, K]
+  const float* bias;
+  void* out;                     // [M][N] in the layout of out_kind
+  float* track;                  // optional [M][blocks][4]: every block's (max, sum of exp(. - max), first argmax) of the rows of `out`
+  // ---- attention ----
+  const unsigned* q;             // tagged words of the step's projections [M][q_stride]: query head h at h * head_dim
+  long long q_stride;
+  int k_off, v_off;              // where the new token's key / value channels begin in a row; k_off < 0: the pages hold them already
+  __nv_bfloat16* k_pool;         // [page][kv_head][64][head_dim]
+  __nv_bfloat16* v_pool;
+  const int* table;
+  int table_stride, table_len;
+  const int* ctx_len;
+  int n_heads, n_kv_heads, head_dim, n_splits;
+  float scale_log2;
+  int window;
+  uint2* part;                   // n_splits > 1: tagged pairs [(sequence * heads + head) * splits + split][head_dim + 2]
+  unsigned* attn_out;            // tagged words [M][n_heads * head_dim]
+  // ---- embed ----
+  const int* tokens;
+  const int* positions;
+  const __nv_bfloat16* wte;
+  const __nv_bfloat16* wpe;
+  uint2* resid;                  // tagged pairs [M][width]
+  int width, vocab, n_positions;
+  // ---- sample (and advance) ----
+  int do_sample;
+  const float* logits;
+  float temperature;
+  int top_k;
+  float top_p, min_p;
+  const unsigned long long* seeds;
+  int* counters;
+  int* out_ids;
+  float* out_logp;
+  int* adv_tokens;
+  int* adv_positions;
+  int* adv_past;
+  int* adv_ctx;
+  const float* partials;         // greedy selection from the readout's `track` instead of from the logits
+  int n_partials;
+  int pad2_;
+  // ---- attention: tensor maps of the layer's key and value pools, seen as [pages * kv_heads * 64 rows][head_dim] ----
+  alignas(64) CUtensorMap k_map;
+  CUtensorMap v_map;
+};
+static_assert(sizeof(FlowPhase) % 64 == 0, "tensor maps in an array of phases stay on 64-byte boundaries");
+
+// ---- tagged data ------------------------------------------------------------------------------------------
+// Loads and stores of tagged data go to the L2 cache, where all blocks meet (relaxed, gpu scope).  A 32-bit word and a
+// 64-bit pair are each one access: never torn.
+__device__ __forceinline__ uint4 df_ld_words4(const unsigned* p) {         // four tagged words
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void df_ld_pairs2(const uint2* p, uint2& a, uint2& b) {      // two tagged pairs
+  unsigned long long x, y;
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];\n" : "=l"(x), "=l"(y) : "l"(p) : "memory");
+  a = make_uint2((unsigned)x, (unsigned)(x >> 32));
+  b = make_uint2((unsigned)y, (unsigned)(y >> 32));
+}
+__device__ __forceinline__ uint2 df_ld_pair(const uint2* p) {
+  unsigned long long x;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];\n" : "=l"(x) : "l"(p) : "memory");
+  return make_uint2((unsigned)x, (unsigned)(x >> 32));
+}
+__device__ __forceinline__ void df_st_pair(uint2* p, float v, unsigned tag) {
+  const unsigned long long x = (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;\n" ::"l"(p), "l"(x) : "memory");
+}
+__device__ __forceinline__ void df_st_pairs2(uint2* p, float v0, float v1, unsigned tag) {
+  const unsigned long long x = (unsigned long long)__float_as_uint(v0) | ((unsigned long long)tag << 32);
+  const unsigned long long y = (unsigned long long)__float_as_uint(v1) | ((unsigned long long)tag << 32);
+  asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1,%2};\n" ::"l"(p), "l"(x), "l"(y) : "memory");
+}
+__device__ __forceinline__ unsigned df_word(float v, unsigned tag16) {
+  return (unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(v)) | (tag16 << 16);
+}
+__device__ __forceinline__ void df_st_words2(unsigned* p, float v0, float v1, unsigned tag16) {
+  asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};\n" ::"l"(p), "r"(df_word(v0, tag16)), "r"(df_word(v1, tag16)) : "memory");
+}
+__device__ __forceinline__ void df_st_word(unsigned* p, float v, unsigned tag16) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;\n" ::"l"(p), "r"(df_word(v, tag16)) : "memory");
+}
+__device__ __forceinline__ int df_ld_status(const int* status) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(status) : "memory");
+  return v;
+}
+
+struct FlowItem {
+  int seq, head, split, L, lo, pg_first, pg_end;   // pages [pg_first, pg_end)
+};
+struct FlowWork {
+  FlowItem it[DF_MAX_ITEMS];
+  int start[DF_MAX_ITEMS + 2];     // where each item's pages begin in the block's stream of pages; [n]: their number
+  int n;
+};
+
+struct FlowShared {
+  volatile int failed;             // a wait of this block ran out (or another block said so): everybody winds down
+  int ok;
+  alignas(16) float red[2][DF_CWARPS][32][4];  // the warps' partial sums of a tile, two sets used in turn (read and written 16 bytes at a time)
+  float ml[2][DF_CWARPS][2];
+  float trk[DF_CWARPS][16][3];
+  SampleShared sample;
+  alignas(64) FlowPhase phase[2];
+  FlowWork work;                   // the computing warps' list of attention items
+  FlowWork pwork;                  // the page producer's own (it runs ahead)
+  const int* ctx_src;
+  const int* table_src;
+  int ctx_cache[16];
+  int table_cache[16][DF_TABLE_CACHE];
+  unsigned long long wfull[DF_MAX_WSLOTS], wempty[DF_MAX_WSLOTS];
+  unsigned long long pfull[DF_MAX_PSLOTS], pempty[DF_MAX_PSLOTS];
+  long long* trace;
+};
+
+__device__ __forceinline__ void df_stamp(FlowShared& sh, int slot) {
+  if (threadIdx.x == 0 && sh.trace) {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    sh.trace[slot] = t;
+  }
+}
+__device__ __forceinline__ void df_bar_consumers() { asm volatile("bar.sync 1, %0;\n" ::"n"(DF_CONSUMERS) : "memory"); }
+
+// A wait that ran out: remember it here and tell everybody.
+__device__ __forceinline__ void df_give_up(FlowShared& sh, int* status, int code) {
+  sh.failed = 1;
+  if (status) atomicCAS(status, 0, code);
+}
+// True when the mbarrier's phase with this parity has completed; gives up when the limit runs out or the block has failed.
+__device__ __forceinline__ bool df_mbar_wait(unsigned long long* bar, unsigned parity, FlowShared& sh, int* status) {
+  for (int i = 0; i < DF_SPIN_LIMIT; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(ds_smem(bar)), "r"(parity) : "memory");
+    if (done) return true;
+    if ((i & 1023) == 1023 && (sh.failed || (status && df_ld_status(status) != 0))) break;
+  }
+  df_give_up(sh, status, 3);
+  return false;
+}
+__device__ __forceinline__ void df_mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(ds_smem(bar)) : "memory");
+}
+
+// ---- layout of the dynamic shared memory (the host computes the same numbers) --------------------------------
+struct FlowLayout {
+  int w_slots, p_slots, p_slot_bytes;
+  int panel_rows, panel_stride;          // rows of the panel (8 or 16) and bytes between them
+  long long w_off, p_off, panel_off, norm_off, rows_off, acc_off, total;
+};
+__host__ __device__ inline int df_kpad(int K) { return (K + 31) / 32 * 32; }
+__host__ __device__ inline int df_col_blocks(int head_dim) { return (head_dim + 63) / 64; }
+__host__ __device__ inline int df_page_slot_bytes(int head_dim) { return 2 * df_col_blocks(head_dim) * DS_PAGE * 128; }
+
+// max_k: the longest K of a product; max_ln_k: the longest LayerNorm-ed K; head_dim: 0 without attention.
+__host__ __device__ inline FlowLayout df_layout(int rows, int max_k, int max_ln_k, int head_dim, int w_slots, int p_slots) {
+  FlowLayout L;
+  L.w_slots = w_slots;
+  L.p_slots = p_slots;
+  L.p_slot_bytes = head_dim > 0 ? df_page_slot_bytes(head_dim) : 0;
+  L.panel_rows = rows > 8 ? 16 : 8;
+  L.panel_stride = df_kpad(max_k) * 2 + 16;
+  long long at = 0;
+  L.p_off = at;                                  // page slots first: the swizzle pattern wants 1024-byte boundaries
+  at += (long long)p_slots * L.p_slot_bytes;
+  L.w_off = at;
+  at += (long long)w_slots * DF_WSLOT;
+  L.panel_off = at;
+  at += (long long)L.panel_rows * L.panel_stride;
+  L.norm_off = at;                               // gamma, beta of the phase's LayerNorm
+  at += 2ll * max_ln_k * 4;
+  L.rows_off = at;                               // attention: query, new key, new value of every item
+  at += (long long)DF_MAX_ITEMS * 3 * head_dim * 2;
+  at = (at + 15) / 16 * 16;
+  L.acc_off = at;                                // attention: the warps' results, two sets
+  at += 2ll * DF_CWARPS * head_dim * 4;
+  L.total = at + 1024;                           // room to move the base up to a 1024-byte boundary
+  return L;
+}
+
+struct FlowArgs {
+  const FlowPhase* phases;
+  int n_phases;
+  unsigned epoch;                  // of this launch, counted per program from 1
+  unsigned* counter;               // the grid barrier's (cleared before the launch)
+  int* status;
+  long long* trace;
+  int rows, max_k, max_ln_k, head_dim, w_slots, p_slots;
+};
+
+__device__ __forceinline__ unsigned df_tag32(unsigned epoch, int phase) { return (epoch << 10) | (unsigned)(phase + 1); }
+__device__ __forceinline__ unsigned df_tag16(unsigned epoch) { return epoch % 65535u + 1u; }
+
+// ---- the producers ---------------------------------------------------------------------------------------
+// The weight producer: one warp that walks the phases and, for every linear phase, sends the block's tiles through the
+// ring: tile after tile, 512 k at a time, 8 rows (output columns) per slot; lane r copies row r.
+// Returns how many slots it filled.
+__device__ unsigned df_weight_producer(const FlowArgs& args, const FlowLayout& lay, unsigned char* smem, FlowShared& sh) {
+  const int lane = threadIdx.x & 31;
+  unsigned use = 0;
+  for (int pi = 0; pi < args.n_phases && !sh.failed; ++pi) {
+    const FlowPhase* ph = args.phases + pi;
+    if (ph->type != FP_LINEAR) continue;
+    const int N = ph->N, K = ph->K;
+    const __nv_bfloat16* w = ph->w;
+    const int n_tiles = (N + 7) / 8, n_chunks = (K + DF_KC - 1) / DF_KC;
+    for (int tile = blockIdx.x; tile < n_tiles && !sh.failed; tile += gridDim.x) {
+      const int n = tile * 8 + lane;
+      const int rows_here = min(8, N - tile * 8);
+      for (int c = 0; c < n_chunks; ++c, ++use) {
+        const unsigned slot = use % (unsigned)lay.w_slots, turn = use / (unsigned)lay.w_slots;
+        if (turn > 0 && !df_mbar_wait(&sh.wempty[slot], (turn - 1) & 1u, sh, args.status)) return use;
+        const int kc = min(DF_KC, K - c * DF_KC);
+        const unsigned bytes = (unsigned)kc * 2u;
+        unsigned char* dst = smem + lay.w_off + (size_t)slot * DF_WSLOT;
+        const unsigned bar = ds_smem(&sh.wfull[slot]);
+        if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes * (unsigned)rows_here) : "memory");
+        __syncwarp();
+        if (lane < rows_here)
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                           ds_smem(dst + lane * DF_WROW)),
+                       "l"(w + (long long)n * K + (long long)c * DF_KC), "r"(bytes), "r"(bar)
+                       : "memory");
+      }
+    }
+  }
+  return use;
+}
+
+// Before a producer warp returns, the copies it asked for last (one ring's worth) have landed: a block must not end
+// with copies into its shared memory in flight.  Bounded; there is nothing more to do if they do not land.
+__device__ void df_drain(unsigned long long* full, unsigned uses, int slots) {
+  const unsigned first = uses > (unsigned)slots ? uses - (unsigned)slots : 0u;
+  for (unsigned u = first; u < uses; ++u) {
+    const unsigned slot = u % (unsigned)slots, parity = (u / (unsigned)slots) & 1u;
+    for (int t = 0; t < (1 << 18); ++t) {
+      unsigned done;
+      asm volatile(
+          "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+          : "=r"(done) : "r"(ds_smem(&full[slot])), "r"(parity) : "memory");
+      if (done) break;
+    }
+  }
+}
+
+// ---- attention: the block's items -----------------------------------------------------------------------------
+__device__ __forceinline__ int df_ctx_len(const FlowPhase* ph, const FlowShared& sh, int seq) {
+  return sh.ctx_src == ph->ctx_len ? sh.ctx_cache[seq] : ph->ctx_len[seq];
+}
+__device__ __forceinline__ int df_table_entry(const FlowPhase* ph, const FlowShared& sh, int seq, int index) {
+  return sh.table_src == ph->table ? sh.table_cache[seq][index] : ph->table[(long long)seq * ph->table_stride + index];
+}
+__device__ __forceinline__ FlowItem df_item(const FlowPhase* ph, const FlowShared& sh, int item) {
+  FlowItem it;
+  const int S = ph->n_splits;
+  it.split = item % S;
+  const int unit = item / S;
+  it.head = unit % ph->n_heads;
+  it.seq = unit / ph->n_heads;
+  it.L = df_ctx_len(ph, sh, it.seq);
+  it.lo = ph->window > 0 ? max(0, it.L - ph->window) : 0;
+  // (a sequence without keys, L <= 0, owns no page, files nothing and yields zeros)
+  const int first = it.lo / DS_PAGE, last = it.L > 0 ? (it.L - 1) / DS_PAGE : first - 1;
+  const int per = (last - first + 1 + S - 1) / S;
+  it.pg_first = first + it.split * per;
+  it.pg_end = min(last + 1, it.pg_first + per);
+  return it;
+}
+// One warp lists the block's items of an attention phase (blockIdx.x, blockIdx.x + grid, ...) into `work`.
+__device__ void df_plan(const FlowPhase* ph, const FlowShared& sh, FlowWork& work) {
+  const int lane = threadIdx.x & 31;
+  const int n_items = ph->M * ph->n_heads * ph->n_splits;
+  int pages = -1;
+  if (lane < DF_MAX_ITEMS) {
+    const int item = blockIdx.x + lane * gridDim.x;
+    if (item < n_items) {
+      const FlowItem it = df_item(ph, sh, item);
+      work.it[lane] = it;
+      pages = max(it.pg_end - it.pg_first, 0);
+    }
+  }
+  // an exclusive running sum over the first lanes (items are contiguous from lane 0)
+  int incl = max(pages, 0);
+#pragma unroll
+  for (int o = 1; o < DF_MAX_ITEMS; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  const unsigned have = __ballot_sync(0xffffffffu, pages >= 0);
+  const int n = __popc(have);
+  if (lane < DF_MAX_ITEMS && pages >= 0) work.start[lane] = incl - pages;
+  if (lane == max(n - 1, 0)) {
+    work.start[n] = n > 0 ? incl : 0;
+    work.n = n;
+  }
+  __syncwarp();
+}
+
+// The page producer: one warp that walks the phases and sends the pages of the block's attention items through the
+// ring of page slots, in the order the computing warps take them.
+__device__ unsigned df_page_producer(const FlowArgs& args, const FlowLayout& lay, unsigned char* smem, FlowShared& sh) {
+  const int lane = threadIdx.x & 31;
+  unsigned use = 0;
+  for (int pi = 0; pi < args.n_phases && !sh.failed; ++pi) {
+    const FlowPhase* ph = args.phases + pi;
+    if (ph->type != FP_ATTENTION) continue;
+    df_plan(ph, sh, sh.pwork);
+    const int total = sh.pwork.start[sh.pwork.n];
+    const int cbs = df_col_blocks(ph->head_dim);
+    const int group = ph->n_heads / ph->n_kv_heads;
+    for (int base = 0; base < total && !sh.failed; base += 32) {
+      // every lane looks up one page of the stream
+      const int k = base + lane;
+      int row = 0;
+      if (k < total) {
+        int j = 0;
+        while (j + 1 < sh.pwork.n && sh.pwork.start[j + 1] <= k) ++j;
+        const FlowItem it = sh.pwork.it[j];
+        const int pg = it.pg_first + (k - sh.pwork.start[j]);
+        const int page = df_table_entry(ph, sh, it.seq, pg % ph->table_len);
+        row = (page * ph->n_kv_heads + it.head / group) * DS_PAGE;
+      }
+      const int n = min(32, total - base);
+      for (int j = 0; j < n; ++j, ++use) {
+        const int my_row = __shfl_sync(0xffffffffu, row, j);
+        const unsigned slot = use % (unsigned)lay.p_slots, turn = use / (unsigned)lay.p_slots;
+        if (turn > 0 && !df_mbar_wait(&sh.pempty[slot], (turn - 1) & 1u, sh, args.status)) return use;
+        if (lane == 0) {
+          unsigned char* dst = smem + lay.p_off + (size_t)slot * lay.p_slot_bytes;
+          const unsigned bar = ds_smem(&sh.pfull[slot]);
+          // the slot may just have been written by ordinary stores (the newest key): order them before the copies
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"((unsigned)lay.p_slot_bytes) : "memory");
+          for (int cb = 0; cb < cbs; ++cb) {
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                             ds_smem(dst + cb * DS_PAGE * 128)),
+                         "l"(&ph->k_map), "r"(cb * 64), "r"(my_row), "r"(bar)
+                         : "memory");
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                             ds_smem(dst + (cbs + cb) * DS_PAGE * 128)),
+                         "l"(&ph->v_map), "r"(cb * 64), "r"(my_row), "r"(bar)
+                         : "memory");
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+  return use;
+}
+
+// ---- the rows' panel ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void df_cp16(const void* smem_dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(ds_smem(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void df_cp_wait() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
+// LayerNorm of one row per warp from tagged pairs.  The row is held in registers (J loads of two pairs per lane):
+// loaded until every tag is the expected one, then mean, then the variance about it, then the normalised row goes
+// into the panel as bfloat16.  Returns false if the tags did not show up in time.
+template <int J>
+__device__ __forceinline__ bool df_layernorm_row(const uint2* __restrict__ src, bool live, int K, unsigned tag, float eps,
+                                                 const float* gs, const float* bs, __nv_bfloat16* dst, FlowShared& sh, int* status,
+                                                 bool params_in_flight) {
+  const int lane = threadIdx.x & 31;
+  // value and tag of every element in place; a round loads what is still pending, all loads in flight together
+  uint2 a[J], b[J];
+  unsigned pending = 0;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    a[j] = b[j] = make_uint2(0u, tag);
+    if (live && lane * 2 + j * 64 < K) pending |= 1u << j;
+  }
+  for (int tries = 0; pending != 0; ++tries) {
+    if (tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (status && df_ld_status(status) != 0)))) {
+      df_give_up(sh, status, 3);
+      break;
+    }
+#pragma unroll
+    for (int j = 0; j < J; ++j)
+      if (pending & (1u << j)) df_ld_pairs2(src + lane * 2 + j * 64, a[j], b[j]);
+#pragma unroll
+    for (int j = 0; j < J; ++j)
+      if (a[j].y == tag && b[j].y == tag) pending &= ~(1u << j);
+  }
+  float v[J][2];
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    v[j][0] = __uint_as_float(a[j].x);
+    v[j][1] = __uint_as_float(b[j].x);
+  }
+  const bool ok = __all_sync(0xffffffffu, pending == 0);
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < J; ++j) s += v[j][0] + v[j][1];
+  const float mean = warp_sum(s) / (float)K;
+  float d2 = 0.f;
+#pragma unroll
+  for (int j = 0; j < J; ++j)
+    if (lane * 2 + j * 64 < K) {
+      const float x = v[j][0] - mean, y = v[j][1] - mean;
+      d2 += x * x + y * y;
+    }
+  const float rs = 1.f / sqrtf(warp_sum(d2) / (float)K + eps);
+  if (params_in_flight) {      // gamma and beta were asked for before the row: they have had the row's time to arrive
+    df_cp_wait();
+    df_bar_consumers();
+  }
+  if (!live) return ok;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = lane * 2 + j * 64;
+    if (c < K) {
+      const float2 g2 = *reinterpret_cast<const float2*>(gs + c);
+      float2 b2 = make_float2(0.f, 0.f);
+      if (bs) b2 = *reinterpret_cast<const float2*>(bs + c);
+      *reinterpret_cast<unsigned*>(dst + c) = ds_pack((v[j][0] - mean) * rs * g2.x + b2.x, (v[j][1] - mean) * rs * g2.y + b2.y);
+    }
+  }
+  return ok;
+}
+
+// Builds the panel of the phase's rows: row r at panel + r * stride, K bfloat16 and zeros up to the next multiple of 32.
+__device__ void df_build_panel(const FlowPhase& ph, const FlowArgs& args, const FlowLayout& lay, unsigned char* smem, FlowShared& sh) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int K = ph.K, M = ph.M, KP = df_kpad(K);
+  unsigned char* panel = smem + lay.panel_off;
+  const int stride = lay.panel_stride;
+  // the zeros behind every row's K elements (the products run over whole blocks of 32)
+  if (KP > K)
+    for (int i = tid; i < M * (KP - K); i += DF_CONSUMERS) {
+      const int r = i / (KP - K), c = K + i % (KP - K);
+      reinterpret_cast<__nv_bfloat16*>(panel + (size_t)r * stride)[c] = __float2bfloat16_rn(0.f);
+    }
+  if (ph.a_kind == FA_LAYERNORM) {
+    float* gs = reinterpret_cast<float*>(smem + lay.norm_off);
+    float* bs = ph.beta ? gs + K : nullptr;
+    for (int i = tid; i < K / 4; i += DF_CONSUMERS) {         // (K is a multiple of 8)
+      df_cp16(gs + i * 4, ph.gamma + i * 4);
+      if (bs) df_cp16(bs + i * 4, ph.beta + i * 4);
+    }
+    const unsigned tag = df_tag32(args.epoch, ph.a_src);
+    const uint2* x = reinterpret_cast<const uint2*>(ph.a);
+    for (int r0 = 0; r0 < M; r0 += DF_CWARPS) {
+      const int r = r0 + warp;
+      const bool live = r < M;
+      const uint2* src = x + (long long)(live ? (ph.rows ? ph.rows[r] : r) : 0) * K;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(panel + (size_t)(live ? r : 0) * stride);
+      if (K <= 16 * 64)
+        df_layernorm_row<16>(src, live, K, tag, ph.eps, gs, bs, dst, sh, args.status, r0 == 0);
+      else
+        df_layernorm_row<32>(src, live, K, tag, ph.eps, gs, bs, dst, sh, args.status, r0 == 0);
+    }
+  } else {
+    // tagged words [M][K]: four at a time, twelve loads of a thread in flight together
+    const unsigned tag16 = df_tag16(args.epoch);
+    const unsigned* a = reinterpret_cast<const unsigned*>(ph.a);
+    const int quads_per_row = K / 4, quads = M * quads_per_row;
+    constexpr int B = 12;
+    for (int q0 = 0; q0 < quads; q0 += B * DF_CONSUMERS) {
+      uint4 v[B];
+      unsigned pending = 0;
+#pragma unroll
+      for (int j = 0; j < B; ++j)
+        if (q0 + j * DF_CONSUMERS + tid < quads) pending |= 1u << j;
+      const unsigned mine = pending;
+      for (int tries = 0; pending != 0; ++tries) {
+        if (tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (args.status && df_ld_status(args.status) != 0)))) {
+          df_give_up(sh, args.status, 3);
+          break;
+        }
+#pragma unroll
+        for (int j = 0; j < B; ++j)
+          if (pending & (1u << j)) v[j] = df_ld_words4(a + (long long)(q0 + j * DF_CONSUMERS + tid) * 4);
+#pragma unroll
+        for (int j = 0; j < B; ++j)
+          if ((pending & (1u << j)) && (v[j].x >> 16) == tag16 && (v[j].y >> 16) == tag16 && (v[j].z >> 16) == tag16 &&
+              (v[j].w >> 16) == tag16)
+            pending &= ~(1u << j);
+      }
+#pragma unroll
+      for (int j = 0; j < B; ++j)
+        if (mine & (1u << j)) {
+          const int qi = q0 + j * DF_CONSUMERS + tid;
+          const int r = qi / quads_per_row, c = (qi - r * quads_per_row) * 4;
+          uint2 packed;
+          packed.x = (v[j].x & 0xffffu) | (v[j].y << 16);
+          packed.y = (v[j].z & 0xffffu) | (v[j].w << 16);
+          *reinterpret_cast<uint2*>(panel + (size_t)r * stride + c * 2) = packed;
+        }
+    }
+  }
+  df_bar_consumers();
+}
+
+// Running (max, sum of exp(value - max), first index of the max) of the values a thread has finished, for two rows.
+struct FlowTrack {
+  float m[2], l[2];
+  int idx[2];
+};
+__device__ __forceinline__ void df_track_merge(float& m, float& l, int& idx, float m2, float l2, int idx2) {
+  if (m2 > m || (m2 == m && idx2 < idx)) idx = idx2;
+  const float mm = fmaxf(m, m2);
+  l = mm == -INFINITY ? 0.f : l * expf(m - mm) + l2 * expf(m2 - mm);
+  m = mm;
+}
+
+__device__ __forceinline__ void df_ldmatrix_x2(unsigned (&r)[2], unsigned smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr));
+}
+
+// A linear phase for the computing warps.  `wuse`: how many weight slots the block has consumed so far in the launch.
+__device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& args, const FlowLayout& lay, unsigned char* smem,
+                                FlowShared& sh, unsigned& wuse) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, q = lane & 3;
+  const int N = ph.N, K = ph.K, M = ph.M;
+  const int n_tiles = (N + 7) / 8, n_chunks = (K + DF_KC - 1) / DF_KC;
+  if ((int)blockIdx.x >= n_tiles) {       // nothing to do in this phase (uniform for the block)
+    if (ph.track && tid < 16 && tid < M) {
+      float* dst = ph.track + ((long long)tid * gridDim.x + blockIdx.x) * 4;
+      dst[0] = -INFINITY;
+      dst[1] = 0.f;
+      dst[2] = __int_as_float(0x7fffffff);
+    }
+    return;
+  }
+  df_build_panel(ph, args, lay, smem, sh);
+  df_stamp(sh, 2);
+  const unsigned panel = ds_smem(smem + lay.panel_off);
+  const int stride = lay.panel_stride;
+  const bool two_rows = lay.panel_rows > 8;
+  const unsigned tag16 = df_tag16(args.epoch), tag_out = df_tag32(args.epoch, pi);
+  FlowTrack trk;
+  trk.m[0] = trk.m[1] = -INFINITY;
+  trk.l[0] = trk.l[1] = 0.f;
+  trk.idx[0] = trk.idx[1] = 0x7fffffff;
+  // lane's row and k offset inside a 16 x 16 block of A and an 8 x 32 block of W, as ldmatrix wants the addresses
+  const unsigned a_lane = two_rows ? (unsigned)((((lane >> 3) & 1) * 8 + (lane & 7)) * stride + (lane >> 4) * 16)
+                                   : (unsigned)((lane & 7) * stride + ((lane >> 3) & 1) * 16);
+  const unsigned b_lane = (unsigned)((lane & 7) * DF_WROW + (lane >> 3) * 16);
+  int tile_i = 0;
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_i) {
+    const bool finisher = warp == (tile_i & (DF_CWARPS - 1));
+    // the finishing warp's bias and residual travel while the products run
+    float bias[4] = {0.f, 0.f, 0.f, 0.f};
+    uint2 res[4];
+    if (finisher) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = g + (i >> 1) * 8, c = tile * 8 + 2 * q + (i & 1);
+        res[i] = make_uint2(0u, 0u);
+        if (r < M && c < N) {
+          if (ph.bias) bias[i] = __ldg(ph.bias + c);
+          if (ph.out_kind == FO_PAIRS) res[i] = df_ld_pair(reinterpret_cast<const uint2*>(ph.out) + (long long)r * N + c);
+        }
+      }
+    }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int c = 0; c < n_chunks; ++c, ++wuse) {
+      const unsigned slot = wuse % (unsigned)lay.w_slots, turn = wuse / (unsigned)lay.w_slots;
+      df_mbar_wait(&sh.wfull[slot], turn & 1u, sh, args.status);
+      const unsigned ws = ds_smem(smem + lay.w_off + (size_t)slot * DF_WSLOT) + b_lane;
+      const int kc = min(DF_KC, K - c * DF_KC), units = (kc + 31) / 32;
+      for (int u = warp; u < units; u += DF_CWARPS) {
+        unsigned b[4];
+        ds_ldmatrix_x4(b, ws + (unsigned)u * 64u);
+        const unsigned pa = panel + a_lane + (unsigned)(c * DF_KC + u * 32) * 2u;
+        if (two_rows) {
+          unsigned a0[4], a1[4];
+          ds_ldmatrix_x4(a0, pa);
+          ds_ldmatrix_x4(a1, pa + 32u);
+          ds_mma(acc, a0[0], a0[1], a0[2], a0[3], b[0], b[1]);
+          ds_mma(acc, a1[0], a1[1], a1[2], a1[3], b[2], b[3]);
+        } else {
+          unsigned a0[2], a1[2];
+          df_ldmatrix_x2(a0, pa);
+          df_ldmatrix_x2(a1, pa + 32u);
+          ds_mma(acc, a0[0], 0u, a0[1], 0u, b[0], b[1]);
+          ds_mma(acc, a1[0], 0u, a1[1], 0u, b[2], b[3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) df_mbar_arrive(&sh.wempty[slot]);
+    }
+    float (*red)[32][4] = sh.red[tile_i & 1];
+    *reinterpret_cast<float4*>(red[warp][lane]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    df_bar_consumers();
+    if (finisher) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = g + (i >> 1) * 8, c = tile * 8 + 2 * q + (i & 1);
+        float v = 0.f;
+#pragma unroll
+        for (int w2 = 0; w2 < DF_CWARPS; ++w2) v += red[w2][lane][i];
+        v = apply_activation(v + bias[i], ph.act);
+        acc[i] = v;
+        if (r < M && c < N && ph.track) {          // columns come to a thread in rising order: the first maximum stays
+          float& m = trk.m[i >> 1];
+          if (v > m) {
+            trk.l[i >> 1] = trk.l[i >> 1] * expf(m - v) + 1.f;
+            m = v;
+            trk.idx[i >> 1] = c;
+          } else if (m != -INFINITY) {
+            trk.l[i >> 1] += expf(v - m);
+          }
+        }
+      }
+      if (ph.out_kind == FO_PAIRS) {
+        // the residual stream: this element was last written by phase res_src (by this very thread, or by the
+        // embedding): wait for its tag, add, write with this phase's tag
+        const unsigned want = df_tag32(args.epoch, ph.res_src);
+        uint2* out = reinterpret_cast<uint2*>(ph.out);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = g + (i >> 1) * 8, c = tile * 8 + 2 * q + (i & 1);
+          if (r < M && c < N) {
+            for (int tries = 0; res[i].y != want; ++tries) {
+              if (tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (args.status && df_ld_status(args.status) != 0)))) {
+                df_give_up(sh, args.status, 3);
+                break;
+              }
+              res[i] = df_ld_pair(out + (long long)r * N + c);
+            }
+            acc[i] += __uint_as_float(res[i].x);
+          }
+        }
+      }
+    }
+    if (finisher) {
+      const int c0 = tile * 8 + 2 * q;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = g + h * 8;
+        if (r >= M || c0 >= N) continue;
+        const bool pair_ok = c0 + 1 < N;
+        const long long o = (long long)r * N + c0;
+        if (ph.out_kind == FO_WORDS) {
+          unsigned* out = reinterpret_cast<unsigned*>(ph.out) + o;
+          if (pair_ok && (o & 1) == 0) df_st_words2(out, acc[2 * h], acc[2 * h + 1], tag16);
+          else {
+            df_st_word(out, acc[2 * h], tag16);
+            if (pair_ok) df_st_word(out + 1, acc[2 * h + 1], tag16);
+          }
+        } else if (ph.out_kind == FO_PAIRS) {
+          uint2* out = reinterpret_cast<uint2*>(ph.out) + o;
+          if (pair_ok && (o & 1) == 0) df_st_pairs2(out, acc[2 * h], acc[2 * h + 1], tag_out);
+          else {
+            df_st_pair(out, acc[2 * h], tag_out);
+            if (pair_ok) df_st_pair(out + 1, acc[2 * h + 1], tag_out);
+          }
+        } else {
+          float* out = reinterpret_cast<float*>(ph.out) + o;
+          out[0] = acc[2 * h];
+          if (pair_ok) out[1] = acc[2 * h + 1];
+        }
+      }
+    }
+  }
+  if (ph.track) {
+    // the block's (max, sum, argmax) of every row: the four lanes that share a row, then the warps
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int o = 1; o <= 2; o <<= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, trk.m[h], o);
+        const float l2 = __shfl_xor_sync(0xffffffffu, trk.l[h], o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, trk.idx[h], o);
+        df_track_merge(trk.m[h], trk.l[h], trk.idx[h], m2, l2, i2);
+      }
+      if (q == 0) {
+        sh.trk[warp][g + 8 * h][0] = trk.m[h];
+        sh.trk[warp][g + 8 * h][1] = trk.l[h];
+        sh.trk[warp][g + 8 * h][2] = __int_as_float(trk.idx[h]);
+      }
+    }
+    df_bar_consumers();
+    if (tid < M && tid < 16) {
+      const int r = tid;
+      float m = sh.trk[0][r][0], l = sh.trk[0][r][1];
+      int idx = __float_as_int(sh.trk[0][r][2]);
+      for (int w2 = 1; w2 < DF_CWARPS; ++w2) df_track_merge(m, l, idx, sh.trk[w2][r][0], sh.trk[w2][r][1], __float_as_int(sh.trk[w2][r][2]));
+      float* dst = ph.track + ((long long)r * gridDim.x + blockIdx.x) * 4;
+      dst[0] = m;
+      dst[1] = l;
+      dst[2] = __int_as_float(idx);
+    }
+    df_bar_consumers();
+  }
+}
+
+
+// ---- attention ---------------------------------------------------------------------------------------------
+// One query per (sequence, head) is row 0 of a 16-row tile (decode_mma.cuh); the pages of the block's items arrive
+// through the ring of page slots in the order of the block's stream of pages.  A warp takes chunks of 8 T keys
+// (the c-th chunk of the stream belongs to warp c % 8) and hands every page back when it is done with it, whether
+// it had a chunk in it or not.  `puse`: how many page slots the block has consumed so far in the launch.
+template <int I, int T>
+__device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& args, const FlowLayout& lay, unsigned char* smem,
+                                   FlowShared& sh, unsigned& puse) {
+  constexpr int CK = 8 * T, CPP = DS_PAGE / CK;       // keys of a chunk, chunks of a page
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, q = lane & 3;
+  const int hd = ph.head_dim, page_elems = DS_PAGE * hd, cbs = df_col_blocks(hd);
+  const int S = ph.n_splits, H = ph.n_heads, group = ph.n_heads / ph.n_kv_heads;
+  const float scale_log2 = ph.scale_log2;
+  const unsigned tag16 = df_tag16(args.epoch), tag_part = df_tag32(args.epoch, pi);
+  __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(smem + lay.rows_off);      // [items][query, new key, new value][hd]
+  float* s_acc = reinterpret_cast<float*>(smem + lay.acc_off);                       // [2][warps][hd]
+  if (warp == 0) df_plan(&ph, sh, sh.work);
+  df_bar_consumers();
+  const int n_mine = sh.work.n, total = sh.work.start[n_mine];
+  {
+    // every item's query and new key and value: tagged words of the projections, four at a time
+    const int quads = hd / 4, kinds = ph.k_off >= 0 ? 3 : 1, n_loads = n_mine * kinds * quads;
+    for (int i0 = 0; i0 < n_loads; i0 += 2 * DF_CONSUMERS) {
+      uint4 v[2];
+      const unsigned* src[2];
+      unsigned pending = 0;
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        const int i = i0 + b * DF_CONSUMERS + tid;
+        src[b] = ph.q;
+        if (i < n_loads) {
+          const int j = i / (kinds * quads), r = (i / quads) % kinds, c = i % quads;
+          const FlowItem it = sh.work.it[j];
+          const int col = r == 0 ? it.head * hd : (r == 1 ? ph.k_off : ph.v_off) + (it.head / group) * hd;
+          src[b] = ph.q + (long long)it.seq * ph.q_stride + col + c * 4;
+          pending |= 1u << b;
+        }
+      }
+      const unsigned mine = pending;
+      for (int tries = 0; pending != 0; ++tries) {
+        if (tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (args.status && df_ld_status(args.status) != 0)))) {
+          df_give_up(sh, args.status, 3);
+          break;
+        }
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+          if (pending & (1u << b)) v[b] = df_ld_words4(src[b]);
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+          if ((pending & (1u << b)) && (v[b].x >> 16) == tag16 && (v[b].y >> 16) == tag16 && (v[b].z >> 16) == tag16 &&
+              (v[b].w >> 16) == tag16)
+            pending &= ~(1u << b);
+      }
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+        if (mine & (1u << b)) {
+          const int i = i0 + b * DF_CONSUMERS + tid;
+          const int j = i / (kinds * quads), r = (i / quads) % kinds, c = i % quads;
+          uint2 packed;
+          packed.x = (v[b].x & 0xffffu) | (v[b].y << 16);
+          packed.y = (v[b].z & 0xffffu) | (v[b].w << 16);
+          *reinterpret_cast<uint2*>(rows + (j * 3 + r) * hd + c * 4) = packed;
+        }
+    }
+  }
+  df_bar_consumers();
+  const unsigned base = puse;
+  puse += (unsigned)total;
+  for (int mine = 0; mine < n_mine; ++mine) {
+    const FlowItem it = sh.work.it[mine];
+    const __nv_bfloat16* my_rows = rows + mine * 3 * hd;
+    const int k0 = sh.work.start[mine], n_pages = sh.work.start[mine + 1] - k0;
+    const int kv_head = it.head / group;
+    const int lo = max(it.lo, it.pg_first * DS_PAGE), hi = min(it.L, it.pg_end * DS_PAGE);
+    // the query in the layout of the keys' loads; only row 0 of the tile (lanes with g = 0) is a query
+    unsigned qa[I * 4];          // per 16 dims: dims 2q, 2q + 1 and 8 + 2q, 9 + 2q
+#pragma unroll
+    for (int j = 0; j < I * 4; ++j) {
+      const int d = 16 * (j >> 1) + 8 * (j & 1) + 2 * q;
+      qa[j] = (g == 0 && d < hd) ? *reinterpret_cast<const unsigned*>(my_rows + d) : 0u;
+    }
+    if (ph.k_off >= 0 && it.L > 0 && it.split == 0 && it.head == kv_head * group) {
+      // this block also files the new token's key and value in the sequence's page (for the steps to come)
+      const int pos = it.L - 1;
+      const long long page = df_table_entry(&ph, sh, it.seq, (pos / DS_PAGE) % ph.table_len);
+      const long long off = (page * ph.n_kv_heads + kv_head) * (long long)page_elems + (long long)(pos % DS_PAGE) * hd;
+      for (int c = tid; c < hd / 8; c += DF_CONSUMERS) {
+        *reinterpret_cast<uint4*>(ph.k_pool + off + c * 8) = *reinterpret_cast<const uint4*>(my_rows + hd + c * 8);
+        *reinterpret_cast<uint4*>(ph.v_pool + off + c * 8) = *reinterpret_cast<const uint4*>(my_rows + 2 * hd + c * 8);
+      }
+    }
+    float m = -INFINITY, l = 0.f;
+    float acc[I * 4][4];
+#pragma unroll
+    for (int n = 0; n < I * 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+    for (int p = 0; p < n_pages; ++p) {
+      const int k = k0 + p;
+      const unsigned use = base + (unsigned)k, slot = use % (unsigned)lay.p_slots, turn = use / (unsigned)lay.p_slots;
+      unsigned char* Kt = smem + lay.p_off + (size_t)slot * lay.p_slot_bytes;      // the page's key tiles; its value tiles follow
+      const unsigned Ks = ds_smem(Kt), Vs = Ks + (unsigned)(cbs * DS_PAGE * 128);
+      bool landed = false;
+#pragma unroll 1
+      for (int h = 0; h < CPP; ++h) {
+        if (((k * CPP + h) & (DF_CWARPS - 1)) != warp) continue;
+        const int key0 = (it.pg_first + p) * DS_PAGE + h * CK;
+        if (key0 >= hi || key0 + CK <= lo) continue;
+        if (!landed) {
+          df_mbar_wait(&sh.pfull[slot], turn & 1u, sh, args.status);
+          landed = true;
+        }
+        if (ph.k_off >= 0 && it.L - 1 >= key0 && it.L - 1 < key0 + CK) {
+          // the newest key and value are not in their page yet (or only just): they come from the projections.
+          // (No other warp touches this chunk's rows; the rows beyond are masked and hold old, finite numbers.)
+          const int row = (it.L - 1) % DS_PAGE;
+          for (int ch = lane; ch < hd / 8; ch += 32) {
+            const unsigned off = (unsigned)((ch >> 3) * DS_PAGE * 128 + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
+            *reinterpret_cast<uint4*>(Kt + off) = *reinterpret_cast<const uint4*>(my_rows + hd + ch * 8);
+            *reinterpret_cast<uint4*>(Kt + cbs * DS_PAGE * 128 + off) = *reinterpret_cast<const uint4*>(my_rows + 2 * hd + ch * 8);
+          }
+          __syncwarp();
+        }
+        ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, scale_log2, m, l, acc);
+      }
+      __syncwarp();
+      if (lane == 0) df_mbar_arrive(&sh.pempty[slot]);      // (every warp, once per page, with or without a chunk in it)
+    }
+    df_stamp(sh, 2 + min(mine, 5));
+    // the four lanes of a row each summed their own keys' weights
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    // lane q of row 0 holds dims 8 n + 2 q + {0, 1} of value tile n.  (Two sets of the warps' results, used in
+    // turn: the block-wide hand-over of the next item orders this item's reads before the item after that writes.)
+    float* my_acc = s_acc + (mine & 1) * DF_CWARPS * hd;
+    float (*my_ml)[2] = sh.ml[mine & 1];
+    if (g == 0) {
+#pragma unroll
+      for (int n = 0; n < I * 4; ++n) {
+        const int d = 8 * n + 2 * q;
+        if (d < hd) *reinterpret_cast<float2*>(my_acc + warp * hd + d) = make_float2(acc[n][0], acc[n][1]);
+      }
+      if (q == 0) {
+        my_ml[warp][0] = m;
+        my_ml[warp][1] = l;
+      }
+    }
+    df_bar_consumers();
+    if (tid < hd) {
+      float Mb = -INFINITY;
+#pragma unroll
+      for (int w2 = 0; w2 < DF_CWARPS; ++w2) Mb = fmaxf(Mb, my_ml[w2][0]);
+      float Lb = 0.f, o = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < DF_CWARPS; ++w2) {
+        const float wg = Mb == -INFINITY ? 0.f : ds_exp2(my_ml[w2][0] - Mb);
+        Lb += my_ml[w2][1] * wg;
+        o += my_acc[w2 * hd + tid] * wg;
+      }
+      const long long unit = (long long)it.seq * H + it.head;
+      if (S == 1) {
+        df_st_word(ph.attn_out + unit * hd + tid, Lb > 0.f ? o / Lb : 0.f, tag16);
+      } else {
+        uint2* dst = ph.part + (unit * S + it.split) * (hd + 2);
+        df_st_pair(dst + tid, o, tag_part);
+        if (tid == 0) {
+          df_st_pair(dst + hd, Mb, tag_part);
+          df_st_pair(dst + hd + 1, Lb, tag_part);
+        }
+      }
+    }
+  }
+  if (S > 1) {
+    // The block of split 0 merges the splits of its (sequence, head), in split order, as their tags show up: thread d
+    // takes dim d.  Eight splits' worth of loads are in flight together.
+    for (int mine = 0; mine < n_mine; ++mine) {
+      const FlowItem it = sh.work.it[mine];
+      if (it.split != 0 || tid >= hd) continue;
+      const long long unit = (long long)it.seq * H + it.head;
+      const uint2* src = ph.part + unit * S * (hd + 2);
+      float Mx = -INFINITY, Lall = 0.f, o = 0.f;
+      for (int s0 = 0; s0 < S; s0 += 8) {
+        uint2 po[8], pm[8], pl[8];
+        unsigned pending = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (s0 + j < S) pending |= 1u << j;
+        const unsigned have = pending;
+        for (int tries = 0; pending != 0; ++tries) {
+          if (tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (args.status && df_ld_status(args.status) != 0)))) {
+            df_give_up(sh, args.status, 3);
+            break;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (pending & (1u << j)) {
+              const uint2* one = src + (long long)(s0 + j) * (hd + 2);
+              po[j] = df_ld_pair(one + tid);
+              pm[j] = df_ld_pair(one + hd);
+              pl[j] = df_ld_pair(one + hd + 1);
+            }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if ((pending & (1u << j)) && po[j].y == tag_part && pm[j].y == tag_part && pl[j].y == tag_part) pending &= ~(1u << j);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (have & (1u << j)) {
+            const float ms = __uint_as_float(pm[j].x);
+            if (ms == -INFINITY) continue;
+            const float mm = fmaxf(Mx, ms);
+            const float a = Mx == -INFINITY ? 0.f : ds_exp2(Mx - mm), b = ds_exp2(ms - mm);
+            Lall = Lall * a + __uint_as_float(pl[j].x) * b;
+            o = o * a + __uint_as_float(po[j].x) * b;
+            Mx = mm;
+          }
+      }
+      df_st_word(ph.attn_out + unit * hd + tid, Lall > 0.f ? o / Lall : 0.f, tag16);
+    }
+  }
+}
+
+// ---- the kernel --------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowArgs args) {
+  extern __shared__ __align__(128) unsigned char df_smem_raw[];
+  __shared__ FlowShared sh;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  unsigned char* smem = df_smem_raw + ((1024u - (ds_smem(df_smem_raw) & 1023u)) & 1023u);
+  const FlowLayout lay = df_layout(args.rows, args.max_k, args.max_ln_k, args.head_dim, args.w_slots, args.p_slots);
+  if (tid == 0) {
+    for (int i = 0; i < lay.w_slots; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ds_smem(&sh.wfull[i])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(ds_smem(&sh.wempty[i])), "r"(DF_CWARPS));
+    }
+    for (int i = 0; i < lay.p_slots; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ds_smem(&sh.pfull[i])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(ds_smem(&sh.pempty[i])), "r"(DF_CWARPS));
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    sh.failed = 0;
+    sh.ok = 1;
+    sh.ctx_src = nullptr;
+    sh.table_src = nullptr;
+    sh.trace = nullptr;
+  }
+  // The weight slots and the panel start as zeros: products run over whole blocks of 32 k, and what lies behind a row's
+  // K elements must be a number (zero times it is added), never the bits of a NaN.
+  for (long long i = tid; i < (lay.norm_off - lay.w_off) / 16; i += DF_THREADS)
+    reinterpret_cast<uint4*>(smem + lay.w_off)[i] = make_uint4(0u, 0u, 0u, 0u);
+  // the phase list's first attention phase: its lengths and page tables are read once (they do not change during the step)
+  int first_attention = -1;
+  for (int pi = 0; pi < args.n_phases && first_attention < 0; ++pi)
+    if (args.phases[pi].type == FP_ATTENTION) first_attention = pi;
+  __syncthreads();
+  if (first_attention >= 0) {
+    const FlowPhase* ph = args.phases + first_attention;
+    if (ph->M <= 16 && ph->table_len <= DF_TABLE_CACHE) {
+      for (int i = tid; i < ph->M * ph->table_len; i += DF_THREADS) {
+        const int seq = i / ph->table_len, index = i - seq * ph->table_len;
+        sh.table_cache[seq][index] = ph->table[(long long)seq * ph->table_stride + index];
+      }
+      if (tid < ph->M) sh.ctx_cache[tid] = ph->ctx_len[tid];
+      if (tid == 0) {
+        sh.ctx_src = ph->ctx_len;
+        sh.table_src = ph->table;
+      }
+    }
+  }
+  static_assert(sizeof(FlowPhase) % 16 == 0, "phases are copied 16 bytes at a time");
+  constexpr int PHASE_VECS = (int)(sizeof(FlowPhase) / 16);
+  if (tid < PHASE_VECS) reinterpret_cast<uint4*>(&sh.phase[0])[tid] = reinterpret_cast<const uint4*>(args.phases)[tid];
+  __syncthreads();
+  // token selection comes last (if at all) and is the work of the whole block after the grid barrier
+  const bool selects = args.phases[args.n_phases - 1].type == FP_SAMPLE;
+  const int n_main = args.n_phases - (selects ? 1 : 0);
+
+  if (warp == DF_CWARPS) {
+    // ---- the weight producer ----
+    FlowArgs mine = args;
+    mine.n_phases = n_main;
+    const unsigned uses = df_weight_producer(mine, lay, smem, sh);
+    if (lane == 0) df_drain(sh.wfull, uses, lay.w_slots);
+  } else if (warp == DF_CWARPS + 1) {
+    // ---- the page producer ----
+    FlowArgs mine = args;
+    mine.n_phases = n_main;
+    const unsigned uses = df_page_producer(mine, lay, smem, sh);
+    if (lane == 0) df_drain(sh.pfull, uses, lay.p_slots);
+  } else {
+    // ---- the computing warps ----
+    unsigned wuse = 0, puse = 0;
+    for (int pi = 0; pi < n_main; ++pi) {
+      df_bar_consumers();      // everyone is done with the previous phase: its description, the panel, the partial sums
+      if (sh.failed) break;    // (uniform: written before the barrier)
+      const FlowPhase& ph = sh.phase[pi & 1];
+      // the next phase's description travels meanwhile
+      if (pi + 1 < args.n_phases && tid < PHASE_VECS)
+        df_cp16(reinterpret_cast<uint4*>(&sh.phase[(pi + 1) & 1]) + tid, reinterpret_cast<const uint4*>(args.phases + pi + 1) + tid);
+      if (tid == 0) sh.trace = (args.trace && blockIdx.x == 0) ? args.trace + DF_TRACE_SLOTS * pi : nullptr;
+      df_stamp(sh, 0);
+      if (ph.type == FP_EMBED) {
+        const unsigned tag = df_tag32(args.epoch, pi);
+        for (int r = blockIdx.x; r < ph.M; r += gridDim.x) {
+          const int id = ph.tokens[r], pos = ph.wpe ? ph.positions[r] : 0;
+          const bool ok = id >= 0 && id < ph.vocab && pos >= 0 && (!ph.wpe || pos < ph.n_positions);
+          for (int c = tid * 2; c < ph.width; c += 2 * DF_CONSUMERS) {
+            float v0 = 0.f, v1 = 0.f;
+            if (ok) {
+              const __nv_bfloat162 e = *reinterpret_cast<const __nv_bfloat162*>(ph.wte + (long long)id * ph.width + c);
+              v0 = __low2float(e);
+              v1 = __high2float(e);
+              if (ph.wpe) {
+                const __nv_bfloat162 p = *reinterpret_cast<const __nv_bfloat162*>(ph.wpe + (long long)pos * ph.width + c);
+                v0 += __low2float(p);
+                v1 += __high2float(p);
+              }
+            }
+            df_st_pairs2(ph.resid + (long long)r * ph.width + c, v0, v1, tag);
+          }
+          if (!ok && tid == 0 && args.status) atomicCAS(args.status, 0, 4);
+        }
+      } else if (ph.type == FP_LINEAR) {
+        df_linear_phase(ph, pi, args, lay, smem, sh, wuse);
+      } else if (ph.type == FP_ATTENTION) {
+        if (ph.head_dim <= 64) df_attention_items<2, 4>(ph, pi, args, lay, smem, sh, puse);      // chunks of 32 keys
+        else df_attention_items<4, 2>(ph, pi, args, lay, smem, sh, puse);                         // chunks of 16 keys
+      }
+      df_stamp(sh, 1);
+      df_cp_wait();
+    }
+  }
+  __syncthreads();
+  if (selects && !sh.failed) {
+    // ---- the grid barrier before token selection: everything the blocks wrote is visible before the arrival is ----
+    if (tid == 0) {
+      asm volatile("red.release.gpu.global.add.u32 [%0], 1;\n" ::"l"(args.counter) : "memory");
+      int ok = 1, spins = 0;
+      for (;;) {
+        unsigned seen;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(args.counter) : "memory");
+        if (seen >= gridDim.x) break;
+        if (++spins > DF_SPIN_LIMIT || ((spins & 1023) == 1023 && args.status && df_ld_status(args.status) != 0)) {
+          ok = 0;
+          break;
+        }
+      }
+      if (!ok) df_give_up(sh, args.status, 3);
+      sh.ok = ok;
+    }
+    __syncthreads();
+    const FlowPhase* ph = args.phases + args.n_phases - 1;
+    if (sh.ok) {
+      for (int r = blockIdx.x; r < ph->M; r += gridDim.x) {
+        if (!ph->do_sample && ph->partials) {
+          // greedy: the readout left every block's (max, sum, argmax) of the row; a warp merges them
+          if (warp == 0) {
+            float m = -INFINITY, l = 0.f;
+            int idx = 0x7fffffff;
+            for (int b = lane; b < ph->n_partials; b += 32) {
+              const float4 p = __ldcg(reinterpret_cast<const float4*>(ph->partials + ((long long)r * ph->n_partials + b) * 4));
+              df_track_merge(m, l, idx, p.x, p.y, __float_as_int(p.z));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+              const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+              const float l2 = __shfl_xor_sync(0xffffffffu, l, o);
+              const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+              df_track_merge(m, l, idx, m2, l2, i2);
+            }
+            if (lane == 0) {
+              ph->out_ids[r] = idx;
+              ph->out_logp[r] = -logf(l);
+              ph->adv_tokens[r] = idx;
+              ph->adv_positions[r] += 1;
+              ph->adv_past[r] += 1;
+              ph->adv_ctx[r] += 1;
+              ph->counters[r] += 1;
+            }
+          }
+          continue;
+        }
+        float u = 0.f;
+        if (ph->do_sample) u = stream_uniform(ph->seeds[r], (unsigned long long)ph->counters[r]);
+        select_row<DF_THREADS>(ph->logits + (long long)r * ph->vocab, ph->vocab, ph->do_sample, ph->temperature, ph->top_k,
+                               ph->top_p, ph->min_p, u, ph->out_ids + r, ph->out_logp + r, sh.sample);
+        __syncthreads();
+        if (tid == 0) {      // the selected id becomes the next step's token; the sequence moves on by one
+          ph->adv_tokens[r] = ph->out_ids[r];
+          ph->adv_positions[r] += 1;
+          ph->adv_past[r] += 1;
+          ph->adv_ctx[r] += 1;
+          ph->counters[r] += 1;
+        }
+      }
+    }
+  }
+}
+
+}  // namespace bt
+
+extern "C" int bt_decode_flow_phase_bytes() { return (int)sizeof(bt::FlowPhase); }
+
+// Sizes the step's shared memory for these phases (host copy of the program) and `rows` sequences.
+// out[0..6] = max_k, max_ln_k, head_dim, w_slots, p_slots, bytes of dynamic shared memory, 0.  Returns 0, or non-zero with
+// the library's error text when the step does not fit.
+extern "C" int bt_decode_flow_plan(const void* phases_host, int n_phases, int rows, long long* out) {
+  using namespace bt;
+  const FlowPhase* ph = reinterpret_cast<const FlowPhase*>(phases_host);
+  BT_CHECK(n_phases >= 1 && n_phases < 1023, "decode_flow: %d phases are outside 1..1022", n_phases);
+  BT_CHECK(rows >= 1 && rows <= 16, "decode_flow: %d rows are outside 1..16", rows);
+  int max_k = 32, max_ln_k = 8, head_dim = 0;
+  for (int i = 0; i < n_phases; ++i) {
+    BT_CHECK(ph[i].type != FP_SAMPLE || i == n_phases - 1, "decode_flow: token selection must be the last phase");
+    if (ph[i].type == FP_LINEAR) {
+      BT_CHECK(ph[i].K % 8 == 0 && ph[i].K >= 8, "decode_flow: K=%d is no multiple of 8", ph[i].K);
+      if (ph[i].K > max_k) max_k = ph[i].K;
+      if (ph[i].a_kind == FA_LAYERNORM) {
+        BT_CHECK(ph[i].K <= 32 * 64, "decode_flow: a LayerNorm over %d channels exceeds the 2048 a warp holds", ph[i].K);
+        if (ph[i].K > max_ln_k) max_ln_k = ph[i].K;
+      }
+    } else if (ph[i].type == FP_ATTENTION) {
+      BT_CHECK(ph[i].head_dim % 16 == 0 && ph[i].head_dim >= 16 && ph[i].head_dim <= 128,
+               "decode_flow: head_dim %d is outside 16..128 in steps of 16", ph[i].head_dim);
+      BT_CHECK(head_dim == 0 || head_dim == ph[i].head_dim, "decode_flow: one head size in all attention phases");
+      head_dim = ph[i].head_dim;
+    }
+  }
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaFuncGetAttributes(&attr, decode_flow_kernel);
+  BT_CHECK(e == cudaSuccess, "decode_flow: cannot read the kernel's attributes: %s", cudaGetErrorString(e));
+  const long long budget = 227 * 1024 - (long long)attr.sharedSizeBytes - 64;
+  // page slots: about 64 KB of them (at least 2, at most 8); weight slots: what is left (at least 4)
+  int p_slots = 0;
+  if (head_dim > 0) {
+    p_slots = 64 * 1024 / df_page_slot_bytes(head_dim);
+    p_slots = p_slots < 2 ? 2 : (p_slots > 8 ? 8 : p_slots);
+  }
+  int w_slots = 0;
+  for (;;) {
+    const FlowLayout fixed = df_layout(rows, max_k, max_ln_k, head_dim, 0, p_slots);
+    w_slots = (int)((budget - fixed.total) / DF_WSLOT);
+    if (w_slots >= 4 || p_slots <= 2) break;
+    --p_slots;
+  }
+  BT_CHECK(w_slots >= 4, "decode_flow: %d rows of K=%d leave no room for the weights' ring in shared memory", rows, max_k);
+  if (w_slots > DF_MAX_WSLOTS) w_slots = DF_MAX_WSLOTS;
+  const FlowLayout lay = df_layout(rows, max_k, max_ln_k, head_dim, w_slots, p_slots);
+  out[0] = max_k;
+  out[1] = max_ln_k;
+  out[2] = head_dim;
+  out[3] = w_slots;
+  out[4] = p_slots;
+  out[5] = lay.total;
+  out[6] = 0;
+  return 0;
+}
+
+// phases_dev: the program in device memory; plan: what bt_decode_flow_plan gave for it.  epoch: a number that is new
+// for every launch of this program (1, 2, 3, ...): it is the tag of everything the launch writes.  counter: one
+// unsigned for the grid barrier before token selection (this call clears it).  The launch is cooperative: every block
+// is resident, which the waiting relies on.  trace: optional 8 * n_phases 64-bit slots for block 0's timeline.
+extern "C" int bt_decode_flow(const void* phases_dev, int n_phases, unsigned epoch, int rows, const long long* plan,
+                              unsigned* counter, int* status, long long* trace, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_phases >= 1 && epoch >= 1 && epoch < (1u << 22), "decode_flow: bad phase count %d or epoch %u", n_phases, epoch);
+  const int n_sms = sm_count();
+  BT_CHECK(n_sms > 0, "decode_flow: cannot read the number of multiprocessors of the current device");
+  const long long smem_bytes = plan[5];
+  static long long configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  BT_CHECK(dev >= 0 && dev < 64, "decode_flow: device %d is beyond the 64 this library tracks", dev);
+  if (configured[dev] < smem_bytes) {
+    cudaError_t e = cudaFuncSetAttribute(decode_flow_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+    BT_CHECK(e == cudaSuccess, "decode_flow: cannot reserve %lld bytes of shared memory: %s", smem_bytes, cudaGetErrorString(e));
+    configured[dev] = smem_bytes;
+  }
+  cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned), stream);
+  BT_CHECK(e == cudaSuccess, "decode_flow: cannot clear the barrier counter: %s", cudaGetErrorString(e));
+  FlowArgs args{reinterpret_cast<const FlowPhase*>(phases_dev), n_phases, epoch, counter, status, trace, rows, (int)plan[0],
+                (int)plan[1], (int)plan[2], (int)plan[3], (int)plan[4]};
+  void* kargs[] = {(void*)&args};
+  e = cudaLaunchCooperativeKernel((const void*)decode_flow_kernel, dim3(n_sms), dim3(DF_THREADS), kargs, (size_t)smem_bytes, stream);
+  BT_CHECK(e == cudaSuccess, "decode_flow: launch failed: %s", cudaGetErrorString(e));
+  count_launch();
+  return 0;
+}
