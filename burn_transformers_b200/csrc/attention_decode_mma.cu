@@ -202,7 +202,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         }
         __syncwarp();
       }
-      ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, p.scale_log2, m, l, acc);
+      ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, p.scale_log2, m, l, acc, lane);
     }
     if (i + p.slots < n_pages) {      // the slot's next page may come
       __syncwarp();

@@ -43,12 +43,12 @@
 
 namespace bt {
 
-constexpr int DF_CWARPS = 8, DF_CONSUMERS = DF_CWARPS * 32;     // warps that compute
+// Eight warps a block, so that a thread may hold 255 registers: with nearly all of a multiprocessor's memory taken as
+// shared memory there is no cache left for spilled registers, and every spilled access would be a trip to the L2 cache.
+constexpr int DF_CWARPS = 6, DF_CONSUMERS = DF_CWARPS * 32;     // warps that compute
 constexpr int DF_THREADS = DF_CONSUMERS + 64;                   // + the weight producer and the page producer
-constexpr int DF_KC = 512;                       // k extent of a weight slot
-constexpr int DF_WROW = DF_KC * 2 + 16;          // bytes between the 8 rows of a slot (16 apart modulo 128: no bank conflicts)
-constexpr int DF_WSLOT = 8 * DF_WROW;
-constexpr int DF_MAX_WSLOTS = 24, DF_MAX_PSLOTS = 16;
+constexpr int DF_MAX_SLOT_K = 1024;              // largest k extent of a weight slot
+constexpr int DF_MAX_WSLOTS = 32, DF_MAX_PSLOTS = 16;
 constexpr int DF_MAX_ITEMS = 8;                  // (sequence, head, split) items of an attention phase a block takes, at most
 constexpr int DF_TABLE_CACHE = 64;               // page-table entries per sequence kept in shared memory
 constexpr int DF_SPIN_LIMIT = 1 << 21;           // tries of any wait before a block gives up
@@ -165,6 +165,46 @@ __device__ __forceinline__ int df_ld_status(const int* status) {
   return v;
 }
 
+// ---- layout of the dynamic shared memory (the host computes the same numbers) --------------------------------
+struct FlowLayout {
+  int w_slots, p_slots, p_slot_bytes;
+  int slot_k, w_row, w_slot_bytes;       // k extent of a weight slot, bytes between its 8 rows (16 apart modulo 128: no bank conflicts), its size
+  int panel_rows, panel_stride;          // rows of the panel (8 or 16) and bytes between them
+  long long w_off, p_off, panel_off, norm_off, rows_off, acc_off, total;
+};
+__host__ __device__ inline int df_kpad(int K) { return (K + 31) / 32 * 32; }
+__host__ __device__ inline int df_col_blocks(int head_dim) { return (head_dim + 63) / 64; }
+__host__ __device__ inline int df_page_slot_bytes(int head_dim) { return 2 * df_col_blocks(head_dim) * DS_PAGE * 128; }
+
+// max_k: the longest K of a product; max_ln_k: the longest LayerNorm-ed K; head_dim: 0 without attention.
+__host__ __device__ inline FlowLayout df_layout(int rows, int max_k, int max_ln_k, int head_dim, int w_slots, int p_slots, int slot_k) {
+  FlowLayout L;
+  L.slot_k = slot_k;
+  L.w_row = (slot_k * 2 + 127) / 128 * 128 + 16;
+  L.w_slot_bytes = 8 * L.w_row;
+  L.w_slots = w_slots;
+  L.p_slots = p_slots;
+  L.p_slot_bytes = head_dim > 0 ? df_page_slot_bytes(head_dim) : 0;
+  L.panel_rows = rows > 8 ? 16 : 8;
+  L.panel_stride = df_kpad(max_k) * 2 + 16;
+  long long at = 0;
+  L.p_off = at;                                  // page slots first: the swizzle pattern wants 1024-byte boundaries
+  at += (long long)p_slots * L.p_slot_bytes;
+  L.w_off = at;
+  at += (long long)w_slots * L.w_slot_bytes;
+  L.panel_off = at;
+  at += (long long)L.panel_rows * L.panel_stride;
+  L.norm_off = at;                               // gamma, beta of the phase's LayerNorm
+  at += 2ll * max_ln_k * 4;
+  L.rows_off = at;                               // attention: query, new key, new value of every item
+  at += (long long)DF_MAX_ITEMS * 3 * head_dim * 2;
+  at = (at + 15) / 16 * 16;
+  L.acc_off = at;                                // attention: the warps' results, two sets
+  at += 2ll * DF_CWARPS * head_dim * 4;
+  L.total = at + 1024;                           // room to move the base up to a 1024-byte boundary
+  return L;
+}
+
 struct FlowItem {
   int seq, head, split, L, lo, pg_first, pg_end;   // pages [pg_first, pg_end)
 };
@@ -176,6 +216,7 @@ struct FlowWork {
 
 struct FlowShared {
   volatile int failed;             // a wait of this block ran out (or another block said so): everybody winds down
+  volatile unsigned w_issued;      // weight slots the producer has asked for so far
   int ok;
   alignas(16) float red[2][DF_CWARPS][32][4];  // the warps' partial sums of a tile, two sets used in turn (read and written 16 bytes at a time)
   float ml[2][DF_CWARPS][2];
@@ -191,6 +232,7 @@ struct FlowShared {
   unsigned long long wfull[DF_MAX_WSLOTS], wempty[DF_MAX_WSLOTS];
   unsigned long long pfull[DF_MAX_PSLOTS], pempty[DF_MAX_PSLOTS];
   long long* trace;
+  FlowLayout lay;                  // where things lie in the dynamic shared memory (kept here, not in registers)
 };
 
 __device__ __forceinline__ void df_stamp(FlowShared& sh, int slot) {
@@ -199,6 +241,12 @@ __device__ __forceinline__ void df_stamp(FlowShared& sh, int slot) {
     asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
     sh.trace[slot] = t;
   }
+}
+// The same number, but the compiler no longer knows it: what a phase derives from it is computed in that phase (and its
+// registers are free again afterwards) instead of once for the whole kernel.
+__device__ __forceinline__ int df_opaque(int x) {
+  asm volatile("mov.b32 %0, %0;\n" : "+r"(x));
+  return x;
 }
 __device__ __forceinline__ void df_bar_consumers() { asm volatile("bar.sync 1, %0;\n" ::"n"(DF_CONSUMERS) : "memory"); }
 
@@ -224,42 +272,6 @@ __device__ __forceinline__ void df_mbar_arrive(unsigned long long* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(ds_smem(bar)) : "memory");
 }
 
-// ---- layout of the dynamic shared memory (the host computes the same numbers) --------------------------------
-struct FlowLayout {
-  int w_slots, p_slots, p_slot_bytes;
-  int panel_rows, panel_stride;          // rows of the panel (8 or 16) and bytes between them
-  long long w_off, p_off, panel_off, norm_off, rows_off, acc_off, total;
-};
-__host__ __device__ inline int df_kpad(int K) { return (K + 31) / 32 * 32; }
-__host__ __device__ inline int df_col_blocks(int head_dim) { return (head_dim + 63) / 64; }
-__host__ __device__ inline int df_page_slot_bytes(int head_dim) { return 2 * df_col_blocks(head_dim) * DS_PAGE * 128; }
-
-// max_k: the longest K of a product; max_ln_k: the longest LayerNorm-ed K; head_dim: 0 without attention.
-__host__ __device__ inline FlowLayout df_layout(int rows, int max_k, int max_ln_k, int head_dim, int w_slots, int p_slots) {
-  FlowLayout L;
-  L.w_slots = w_slots;
-  L.p_slots = p_slots;
-  L.p_slot_bytes = head_dim > 0 ? df_page_slot_bytes(head_dim) : 0;
-  L.panel_rows = rows > 8 ? 16 : 8;
-  L.panel_stride = df_kpad(max_k) * 2 + 16;
-  long long at = 0;
-  L.p_off = at;                                  // page slots first: the swizzle pattern wants 1024-byte boundaries
-  at += (long long)p_slots * L.p_slot_bytes;
-  L.w_off = at;
-  at += (long long)w_slots * DF_WSLOT;
-  L.panel_off = at;
-  at += (long long)L.panel_rows * L.panel_stride;
-  L.norm_off = at;                               // gamma, beta of the phase's LayerNorm
-  at += 2ll * max_ln_k * 4;
-  L.rows_off = at;                               // attention: query, new key, new value of every item
-  at += (long long)DF_MAX_ITEMS * 3 * head_dim * 2;
-  at = (at + 15) / 16 * 16;
-  L.acc_off = at;                                // attention: the warps' results, two sets
-  at += 2ll * DF_CWARPS * head_dim * 4;
-  L.total = at + 1024;                           // room to move the base up to a 1024-byte boundary
-  return L;
-}
-
 struct FlowArgs {
   const FlowPhase* phases;
   int n_phases;
@@ -267,42 +279,56 @@ struct FlowArgs {
   unsigned* counter;               // the grid barrier's (cleared before the launch)
   int* status;
   long long* trace;
-  int rows, max_k, max_ln_k, head_dim, w_slots, p_slots;
+  int rows, max_k, max_ln_k, head_dim, w_slots, p_slots, slot_k;
 };
 
 __device__ __forceinline__ unsigned df_tag32(unsigned epoch, int phase) { return (epoch << 10) | (unsigned)(phase + 1); }
 __device__ __forceinline__ unsigned df_tag16(unsigned epoch) { return epoch % 65535u + 1u; }
 
+// ---- how a product's output columns are dealt out -----------------------------------------------------------
+// Block b of B takes the columns [b N / B, (b + 1) N / B): every block gets N / B columns or one more, so that all
+// multiprocessors pull the same share of the weights.  A block works through its columns in tiles of (at most) 8.
+__device__ __forceinline__ void df_columns(int N, int& c0, int& c1) {
+  c0 = (int)((long long)blockIdx.x * N / gridDim.x);
+  c1 = (int)((long long)(blockIdx.x + 1) * N / gridDim.x);
+}
+
 // ---- the producers ---------------------------------------------------------------------------------------
 // The weight producer: one warp that walks the phases and, for every linear phase, sends the block's tiles through the
-// ring: tile after tile, 512 k at a time, 8 rows (output columns) per slot; lane r copies row r.
+// ring: tile after tile, slot_k of k at a time, 8 rows (output columns) per slot; lane r copies row r.
 // Returns how many slots it filled.
-__device__ unsigned df_weight_producer(const FlowArgs& args, const FlowLayout& lay, unsigned char* smem, FlowShared& sh) {
+__device__ unsigned df_weight_producer(const FlowArgs& args, int n_phases, const FlowLayout& lay, unsigned char* smem, FlowShared& sh) {
   const int lane = threadIdx.x & 31;
   unsigned use = 0;
-  for (int pi = 0; pi < args.n_phases && !sh.failed; ++pi) {
+  unsigned slot = 0, turn = 0;
+  for (int pi = 0; pi < n_phases && !sh.failed; ++pi) {
     const FlowPhase* ph = args.phases + pi;
     if (ph->type != FP_LINEAR) continue;
     const int N = ph->N, K = ph->K;
-    const __nv_bfloat16* w = ph->w;
-    const int n_tiles = (N + 7) / 8, n_chunks = (K + DF_KC - 1) / DF_KC;
-    for (int tile = blockIdx.x; tile < n_tiles && !sh.failed; tile += gridDim.x) {
-      const int n = tile * 8 + lane;
-      const int rows_here = min(8, N - tile * 8);
+    int c0, c1;
+    df_columns(N, c0, c1);
+    const int n_chunks = (K + lay.slot_k - 1) / lay.slot_k;
+    for (int t0 = c0; t0 < c1 && !sh.failed; t0 += 8) {
+      const int rows_here = min(8, c1 - t0);
+      const __nv_bfloat16* src = ph->w + (long long)(t0 + lane) * K;
       for (int c = 0; c < n_chunks; ++c, ++use) {
-        const unsigned slot = use % (unsigned)lay.w_slots, turn = use / (unsigned)lay.w_slots;
         if (turn > 0 && !df_mbar_wait(&sh.wempty[slot], (turn - 1) & 1u, sh, args.status)) return use;
-        const int kc = min(DF_KC, K - c * DF_KC);
+        const int kc = min(lay.slot_k, K - c * lay.slot_k);
         const unsigned bytes = (unsigned)kc * 2u;
-        unsigned char* dst = smem + lay.w_off + (size_t)slot * DF_WSLOT;
+        const unsigned dst = ds_smem(smem + lay.w_off) + slot * (unsigned)lay.w_slot_bytes + (unsigned)(lane * lay.w_row);
         const unsigned bar = ds_smem(&sh.wfull[slot]);
         if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes * (unsigned)rows_here) : "memory");
         __syncwarp();
         if (lane < rows_here)
-          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
-                           ds_smem(dst + lane * DF_WROW)),
-                       "l"(w + (long long)n * K + (long long)c * DF_KC), "r"(bytes), "r"(bar)
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                       "l"(src + (long long)c * lay.slot_k), "r"(bytes), "r"(bar)
                        : "memory");
+        __syncwarp();
+        if (lane == 0) sh.w_issued = use + 1;
+        if (++slot == (unsigned)lay.w_slots) {
+          slot = 0;
+          ++turn;
+        }
       }
     }
   }
@@ -380,10 +406,10 @@ __device__ void df_plan(const FlowPhase* ph, const FlowShared& sh, FlowWork& wor
 
 // The page producer: one warp that walks the phases and sends the pages of the block's attention items through the
 // ring of page slots, in the order the computing warps take them.
-__device__ unsigned df_page_producer(const FlowArgs& args, const FlowLayout& lay, unsigned char* smem, FlowShared& sh) {
+__device__ unsigned df_page_producer(const FlowArgs& args, int n_phases, const FlowLayout& lay, unsigned char* smem, FlowShared& sh) {
   const int lane = threadIdx.x & 31;
   unsigned use = 0;
-  for (int pi = 0; pi < args.n_phases && !sh.failed; ++pi) {
+  for (int pi = 0; pi < n_phases && !sh.failed; ++pi) {
     const FlowPhase* ph = args.phases + pi;
     if (ph->type != FP_ATTENTION) continue;
     df_plan(ph, sh, sh.pwork);
@@ -437,51 +463,60 @@ __device__ __forceinline__ void df_cp16(const void* smem_dst, const void* src) {
 }
 __device__ __forceinline__ void df_cp_wait() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
-// LayerNorm of one row per warp from tagged pairs.  The row is held in registers (J loads of two pairs per lane):
-// loaded until every tag is the expected one, then mean, then the variance about it, then the normalised row goes
-// into the panel as bfloat16.  Returns false if the tags did not show up in time.
+// True when a tagged wait should stop: the limit ran out, this block has failed or another block said so.
+__device__ __forceinline__ bool df_tired(int tries, FlowShared& sh, int* status) {
+  return tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (status && df_ld_status(status) != 0)));
+}
+
+// LayerNorm of one row per warp from tagged pairs.  A lane holds four neighbouring channels of every 128 (J such
+// groups: K <= 128 J): loaded until every tag is the expected one, then the mean, then the variance about it (two
+// passes over registers), then the normalised row goes into the panel as bfloat16, 8 bytes a lane at a time.
+// Returns false if the tags did not show up in time.
 template <int J>
 __device__ __forceinline__ bool df_layernorm_row(const uint2* __restrict__ src, bool live, int K, unsigned tag, float eps,
                                                  const float* gs, const float* bs, __nv_bfloat16* dst, FlowShared& sh, int* status,
-                                                 bool params_in_flight) {
-  const int lane = threadIdx.x & 31;
-  // value and tag of every element in place; a round loads what is still pending, all loads in flight together
-  uint2 a[J], b[J];
+                                                 bool params_in_flight, int lane) {
+  // e[j][i]: value and tag of channel 128 j + 4 lane + i; the loads' own registers hold the row
+  uint2 e[J][4];
   unsigned pending = 0;
 #pragma unroll
   for (int j = 0; j < J; ++j) {
-    a[j] = b[j] = make_uint2(0u, tag);
-    if (live && lane * 2 + j * 64 < K) pending |= 1u << j;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[j][i] = make_uint2(0u, tag);
+    if (live && lane * 4 + j * 128 < K) pending |= 1u << j;
   }
+  const unsigned mine = pending;
+  const uint2* mine_src = src + lane * 4;
   for (int tries = 0; pending != 0; ++tries) {
-    if (tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (status && df_ld_status(status) != 0)))) {
+    if (df_tired(tries, sh, status)) {
       df_give_up(sh, status, 3);
       break;
     }
+    // all loads of a round in flight together; a round loads what is still pending
 #pragma unroll
     for (int j = 0; j < J; ++j)
-      if (pending & (1u << j)) df_ld_pairs2(src + lane * 2 + j * 64, a[j], b[j]);
+      if (pending & (1u << j)) {
+        df_ld_pairs2(mine_src + j * 128, e[j][0], e[j][1]);
+        df_ld_pairs2(mine_src + j * 128 + 2, e[j][2], e[j][3]);
+      }
 #pragma unroll
     for (int j = 0; j < J; ++j)
-      if (a[j].y == tag && b[j].y == tag) pending &= ~(1u << j);
-  }
-  float v[J][2];
-#pragma unroll
-  for (int j = 0; j < J; ++j) {
-    v[j][0] = __uint_as_float(a[j].x);
-    v[j][1] = __uint_as_float(b[j].x);
+      if (((e[j][0].y ^ tag) | (e[j][1].y ^ tag) | (e[j][2].y ^ tag) | (e[j][3].y ^ tag)) == 0u) pending &= ~(1u << j);
   }
   const bool ok = __all_sync(0xffffffffu, pending == 0);
   float s = 0.f;
 #pragma unroll
-  for (int j = 0; j < J; ++j) s += v[j][0] + v[j][1];
+  for (int j = 0; j < J; ++j)
+    if (mine & (1u << j))
+      s += (__uint_as_float(e[j][0].x) + __uint_as_float(e[j][1].x)) + (__uint_as_float(e[j][2].x) + __uint_as_float(e[j][3].x));
   const float mean = warp_sum(s) / (float)K;
   float d2 = 0.f;
 #pragma unroll
   for (int j = 0; j < J; ++j)
-    if (lane * 2 + j * 64 < K) {
-      const float x = v[j][0] - mean, y = v[j][1] - mean;
-      d2 += x * x + y * y;
+    if (mine & (1u << j)) {
+      const float x0 = __uint_as_float(e[j][0].x) - mean, x1 = __uint_as_float(e[j][1].x) - mean;
+      const float x2 = __uint_as_float(e[j][2].x) - mean, x3 = __uint_as_float(e[j][3].x) - mean;
+      d2 += (x0 * x0 + x1 * x1) + (x2 * x2 + x3 * x3);
     }
   const float rs = 1.f / sqrtf(warp_sum(d2) / (float)K + eps);
   if (params_in_flight) {      // gamma and beta were asked for before the row: they have had the row's time to arrive
@@ -490,21 +525,25 @@ __device__ __forceinline__ bool df_layernorm_row(const uint2* __restrict__ src, 
   }
   if (!live) return ok;
 #pragma unroll
-  for (int j = 0; j < J; ++j) {
-    const int c = lane * 2 + j * 64;
-    if (c < K) {
-      const float2 g2 = *reinterpret_cast<const float2*>(gs + c);
-      float2 b2 = make_float2(0.f, 0.f);
-      if (bs) b2 = *reinterpret_cast<const float2*>(bs + c);
-      *reinterpret_cast<unsigned*>(dst + c) = ds_pack((v[j][0] - mean) * rs * g2.x + b2.x, (v[j][1] - mean) * rs * g2.y + b2.y);
+  for (int j = 0; j < J; ++j)
+    if (mine & (1u << j)) {
+      const int c = lane * 4 + j * 128;
+      const float4 g4 = *reinterpret_cast<const float4*>(gs + c);
+      float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (bs) b4 = *reinterpret_cast<const float4*>(bs + c);
+      uint2 packed;
+      packed.x = ds_pack((__uint_as_float(e[j][0].x) - mean) * rs * g4.x + b4.x, (__uint_as_float(e[j][1].x) - mean) * rs * g4.y + b4.y);
+      packed.y = ds_pack((__uint_as_float(e[j][2].x) - mean) * rs * g4.z + b4.z, (__uint_as_float(e[j][3].x) - mean) * rs * g4.w + b4.w);
+      *reinterpret_cast<uint2*>(dst + c) = packed;
     }
-  }
   return ok;
 }
 
 // Builds the panel of the phase's rows: row r at panel + r * stride, K bfloat16 and zeros up to the next multiple of 32.
+// LNJ: the LayerNorm path holds rows of up to 128 LNJ channels.
+template <int LNJ>
 __device__ void df_build_panel(const FlowPhase& ph, const FlowArgs& args, const FlowLayout& lay, unsigned char* smem, FlowShared& sh) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = df_opaque(threadIdx.x), warp = tid >> 5;
   const int K = ph.K, M = ph.M, KP = df_kpad(K);
   unsigned char* panel = smem + lay.panel_off;
   const int stride = lay.panel_stride;
@@ -528,48 +567,64 @@ __device__ void df_build_panel(const FlowPhase& ph, const FlowArgs& args, const 
       const bool live = r < M;
       const uint2* src = x + (long long)(live ? (ph.rows ? ph.rows[r] : r) : 0) * K;
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(panel + (size_t)(live ? r : 0) * stride);
-      if (K <= 16 * 64)
-        df_layernorm_row<16>(src, live, K, tag, ph.eps, gs, bs, dst, sh, args.status, r0 == 0);
-      else
-        df_layernorm_row<32>(src, live, K, tag, ph.eps, gs, bs, dst, sh, args.status, r0 == 0);
+      df_layernorm_row<LNJ>(src, live, K, tag, ph.eps, gs, bs, dst, sh, args.status, r0 == 0, tid & 31);
     }
   } else {
-    // tagged words [M][K]: four at a time, twelve loads of a thread in flight together
-    const unsigned tag16 = df_tag16(args.epoch);
+    // tagged words [M][K]: four at a time.  A thread takes the quads tid, tid + threads, ... of every row; a batch is
+    // B (row, quad) pairs whose loads are in flight together.
+    const unsigned tags = df_tag16(args.epoch) << 16;
     const unsigned* a = reinterpret_cast<const unsigned*>(ph.a);
-    const int quads_per_row = K / 4, quads = M * quads_per_row;
+    const int qpr = K / 4, per_row = (qpr + DF_CONSUMERS - 1) / DF_CONSUMERS, items = M * per_row;
     constexpr int B = 12;
-    for (int q0 = 0; q0 < quads; q0 += B * DF_CONSUMERS) {
+    for (int i0 = 0; i0 < items; i0 += B) {
+      const int r0 = i0 / per_row, j0 = i0 - r0 * per_row;
       uint4 v[B];
       unsigned pending = 0;
+      {
+        int r = r0, jq = j0;
 #pragma unroll
-      for (int j = 0; j < B; ++j)
-        if (q0 + j * DF_CONSUMERS + tid < quads) pending |= 1u << j;
+        for (int j = 0; j < B; ++j) {
+          if (r < M && tid + jq * DF_CONSUMERS < qpr) pending |= 1u << j;
+          if (++jq == per_row) {
+            jq = 0;
+            ++r;
+          }
+        }
+      }
       const unsigned mine = pending;
       for (int tries = 0; pending != 0; ++tries) {
-        if (tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (args.status && df_ld_status(args.status) != 0)))) {
+        if (df_tired(tries, sh, args.status)) {
           df_give_up(sh, args.status, 3);
           break;
         }
+        int r = r0, jq = j0;
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+          if (pending & (1u << j)) v[j] = df_ld_words4(a + (unsigned)(r * K + (tid + jq * DF_CONSUMERS) * 4));
+          if (++jq == per_row) {
+            jq = 0;
+            ++r;
+          }
+        }
 #pragma unroll
         for (int j = 0; j < B; ++j)
-          if (pending & (1u << j)) v[j] = df_ld_words4(a + (long long)(q0 + j * DF_CONSUMERS + tid) * 4);
-#pragma unroll
-        for (int j = 0; j < B; ++j)
-          if ((pending & (1u << j)) && (v[j].x >> 16) == tag16 && (v[j].y >> 16) == tag16 && (v[j].z >> 16) == tag16 &&
-              (v[j].w >> 16) == tag16)
+          if ((pending & (1u << j)) && ((((v[j].x ^ tags) | (v[j].y ^ tags) | (v[j].z ^ tags) | (v[j].w ^ tags)) >> 16) == 0u))
             pending &= ~(1u << j);
       }
+      int r = r0, jq = j0;
 #pragma unroll
-      for (int j = 0; j < B; ++j)
+      for (int j = 0; j < B; ++j) {
         if (mine & (1u << j)) {
-          const int qi = q0 + j * DF_CONSUMERS + tid;
-          const int r = qi / quads_per_row, c = (qi - r * quads_per_row) * 4;
           uint2 packed;
-          packed.x = (v[j].x & 0xffffu) | (v[j].y << 16);
-          packed.y = (v[j].z & 0xffffu) | (v[j].w << 16);
-          *reinterpret_cast<uint2*>(panel + (size_t)r * stride + c * 2) = packed;
+          packed.x = __byte_perm(v[j].x, v[j].y, 0x5410);
+          packed.y = __byte_perm(v[j].z, v[j].w, 0x5410);
+          *reinterpret_cast<uint2*>(panel + (unsigned)(r * stride + (tid + jq * DF_CONSUMERS) * 8)) = packed;
         }
+        if (++jq == per_row) {
+          jq = 0;
+          ++r;
+        }
+      }
     }
   }
   df_bar_consumers();
@@ -590,14 +645,25 @@ __device__ __forceinline__ void df_track_merge(float& m, float& l, int& idx, flo
 __device__ __forceinline__ void df_ldmatrix_x2(unsigned (&r)[2], unsigned smem_addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr));
 }
+__device__ __forceinline__ void df_bar_group(int id, int threads) {
+  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
+}
 
 // A linear phase for the computing warps.  `wuse`: how many weight slots the block has consumed so far in the launch.
+//
+// The block's columns come as T tiles of at most 8.  G warps share a tile (G = 6, 3, 2 or 1: the most that leaves every
+// tile a group), splitting its k between them 32 elements at a time; 6 / G tiles are in work together.  Warp 0 of a tile's
+// group adds the group's partial sums in warp order and finishes the tile (bias, activation, residual, tags).  A slot of
+// the ring belongs to one tile: every warp of the tile's group hands it back with 6 / G of the 6 arrivals that free it.
+template <int LNJ>
 __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& args, const FlowLayout& lay, unsigned char* smem,
                                 FlowShared& sh, unsigned& wuse) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, q = lane & 3;
+  const int tid = df_opaque(threadIdx.x), lane = tid & 31, warp = tid >> 5, g = lane >> 2, q = lane & 3;
   const int N = ph.N, K = ph.K, M = ph.M;
-  const int n_tiles = (N + 7) / 8, n_chunks = (K + DF_KC - 1) / DF_KC;
-  if ((int)blockIdx.x >= n_tiles) {       // nothing to do in this phase (uniform for the block)
+  int c0, c1;
+  df_columns(N, c0, c1);
+  const int T = (c1 - c0 + 7) / 8, n_chunks = (K + lay.slot_k - 1) / lay.slot_k;
+  if (T == 0) {       // nothing to do in this phase (uniform for the block)
     if (ph.track && tid < 16 && tid < M) {
       float* dst = ph.track + ((long long)tid * gridDim.x + blockIdx.x) * 4;
       dst[0] = -INFINITY;
@@ -606,8 +672,11 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
     }
     return;
   }
-  df_build_panel(ph, args, lay, smem, sh);
+  df_build_panel<LNJ>(ph, args, lay, smem, sh);
   df_stamp(sh, 2);
+  const int G = T == 1 ? 6 : (T == 2 ? 3 : (T == 3 ? 2 : 1)), n_groups = DF_CWARPS / G;
+  const int grp = warp / G, wg = warp - grp * G;
+  const bool finisher = wg == 0;
   const unsigned panel = ds_smem(smem + lay.panel_off);
   const int stride = lay.panel_stride;
   const bool two_rows = lay.panel_rows > 8;
@@ -619,125 +688,149 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
   // lane's row and k offset inside a 16 x 16 block of A and an 8 x 32 block of W, as ldmatrix wants the addresses
   const unsigned a_lane = two_rows ? (unsigned)((((lane >> 3) & 1) * 8 + (lane & 7)) * stride + (lane >> 4) * 16)
                                    : (unsigned)((lane & 7) * stride + ((lane >> 3) & 1) * 16);
-  const unsigned b_lane = (unsigned)((lane & 7) * DF_WROW + (lane >> 3) * 16);
-  int tile_i = 0;
-  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_i) {
-    const bool finisher = warp == (tile_i & (DF_CWARPS - 1));
+  const unsigned b_lane = (unsigned)((lane & 7) * lay.w_row + (lane >> 3) * 16);
+  const unsigned w_base = ds_smem(smem + lay.w_off);
+  int round = 0;
+  for (int t = grp; t < T; t += n_groups, ++round) {
+    const int tc0 = c0 + t * 8, nc = min(8, c1 - tc0);
     // the finishing warp's bias and residual travel while the products run
     float bias[4] = {0.f, 0.f, 0.f, 0.f};
     uint2 res[4];
     if (finisher) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int r = g + (i >> 1) * 8, c = tile * 8 + 2 * q + (i & 1);
+        const int r = g + (i >> 1) * 8, cc = 2 * q + (i & 1);
         res[i] = make_uint2(0u, 0u);
-        if (r < M && c < N) {
-          if (ph.bias) bias[i] = __ldg(ph.bias + c);
-          if (ph.out_kind == FO_PAIRS) res[i] = df_ld_pair(reinterpret_cast<const uint2*>(ph.out) + (long long)r * N + c);
+        if (r < M && cc < nc) {
+          if (ph.bias) bias[i] = __ldg(ph.bias + tc0 + cc);
+          if (ph.out_kind == FO_PAIRS) res[i] = df_ld_pair(reinterpret_cast<const uint2*>(ph.out) + (long long)r * N + tc0 + cc);
         }
       }
     }
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int c = 0; c < n_chunks; ++c, ++wuse) {
-      const unsigned slot = wuse % (unsigned)lay.w_slots, turn = wuse / (unsigned)lay.w_slots;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+    unsigned use = wuse + (unsigned)(t * n_chunks);
+    for (int c = 0; c < n_chunks; ++c, ++use) {
+      const unsigned slot = use % (unsigned)lay.w_slots, turn = use / (unsigned)lay.w_slots;
+      // Warps run through the ring at their own pace: a warp may come for a slot a whole turn early, when the slot's
+      // barrier still counts the turn before (whose parity it would mistake for its own).  So first the producer must
+      // have asked for this very use; then the barrier is in this turn, or past it.
+      for (int tries = 0; sh.w_issued <= use; ++tries)
+        if (df_tired(tries, sh, args.status)) {
+          df_give_up(sh, args.status, 3);
+          break;
+        }
       df_mbar_wait(&sh.wfull[slot], turn & 1u, sh, args.status);
-      const unsigned ws = ds_smem(smem + lay.w_off + (size_t)slot * DF_WSLOT) + b_lane;
-      const int kc = min(DF_KC, K - c * DF_KC), units = (kc + 31) / 32;
-      for (int u = warp; u < units; u += DF_CWARPS) {
+      const unsigned ws = w_base + slot * (unsigned)lay.w_slot_bytes + b_lane;
+      const int kc = min(lay.slot_k, K - c * lay.slot_k), units = (kc + 31) / 32;
+      const unsigned pa0 = panel + a_lane + (unsigned)(c * lay.slot_k) * 2u;
+      for (int u = wg; u < units; u += G) {
         unsigned b[4];
         ds_ldmatrix_x4(b, ws + (unsigned)u * 64u);
-        const unsigned pa = panel + a_lane + (unsigned)(c * DF_KC + u * 32) * 2u;
+        const unsigned pa = pa0 + (unsigned)u * 64u;
         if (two_rows) {
           unsigned a0[4], a1[4];
           ds_ldmatrix_x4(a0, pa);
           ds_ldmatrix_x4(a1, pa + 32u);
           ds_mma(acc, a0[0], a0[1], a0[2], a0[3], b[0], b[1]);
-          ds_mma(acc, a1[0], a1[1], a1[2], a1[3], b[2], b[3]);
+          ds_mma(acc2, a1[0], a1[1], a1[2], a1[3], b[2], b[3]);
         } else {
           unsigned a0[2], a1[2];
           df_ldmatrix_x2(a0, pa);
           df_ldmatrix_x2(a1, pa + 32u);
           ds_mma(acc, a0[0], 0u, a0[1], 0u, b[0], b[1]);
-          ds_mma(acc, a1[0], 0u, a1[1], 0u, b[2], b[3]);
+          ds_mma(acc2, a1[0], 0u, a1[1], 0u, b[2], b[3]);
         }
       }
       __syncwarp();
-      if (lane == 0) df_mbar_arrive(&sh.wempty[slot]);
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;\n" ::"r"(ds_smem(&sh.wempty[slot])), "r"(DF_CWARPS / G) : "memory");
     }
-    float (*red)[32][4] = sh.red[tile_i & 1];
-    *reinterpret_cast<float4*>(red[warp][lane]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    df_bar_consumers();
-    if (finisher) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
+    if (G > 1) {
+      float (*red)[32][4] = sh.red[round & 1];
+      *reinterpret_cast<float4*>(red[warp][lane]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      df_bar_group(2 + grp, G * 32);
+      if (finisher) {
+        float4 part[DF_CWARPS - 1];
+#pragma unroll
+        for (int w2 = 1; w2 < DF_CWARPS; ++w2)
+          if (w2 < G) part[w2 - 1] = *reinterpret_cast<const float4*>(red[warp + w2][lane]);
+#pragma unroll
+        for (int w2 = 1; w2 < DF_CWARPS; ++w2)
+          if (w2 < G) {
+            acc[0] += part[w2 - 1].x;
+            acc[1] += part[w2 - 1].y;
+            acc[2] += part[w2 - 1].z;
+            acc[3] += part[w2 - 1].w;
+          }
+      }
+    }
+    if (!finisher) continue;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = g + (i >> 1) * 8, cc = 2 * q + (i & 1);
+      const float v = apply_activation(acc[i] + bias[i], ph.act);
+      acc[i] = v;
+      if (r < M && cc < nc && ph.track) {          // columns come to a thread in rising order: the first maximum stays
+        float& m = trk.m[i >> 1];
+        if (v > m) {
+          trk.l[i >> 1] = trk.l[i >> 1] * expf(m - v) + 1.f;
+          m = v;
+          trk.idx[i >> 1] = tc0 + cc;
+        } else if (m != -INFINITY) {
+          trk.l[i >> 1] += expf(v - m);
+        }
+      }
+    }
+    if (ph.out_kind == FO_PAIRS) {
+      // the residual stream: this element was last written by phase res_src (by the thread that holds it in that
+      // phase, or by the embedding): wait for its tag, add, write with this phase's tag
+      const unsigned want = df_tag32(args.epoch, ph.res_src);
+      uint2* out = reinterpret_cast<uint2*>(ph.out);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int r = g + (i >> 1) * 8, c = tile * 8 + 2 * q + (i & 1);
-        float v = 0.f;
-#pragma unroll
-        for (int w2 = 0; w2 < DF_CWARPS; ++w2) v += red[w2][lane][i];
-        v = apply_activation(v + bias[i], ph.act);
-        acc[i] = v;
-        if (r < M && c < N && ph.track) {          // columns come to a thread in rising order: the first maximum stays
-          float& m = trk.m[i >> 1];
-          if (v > m) {
-            trk.l[i >> 1] = trk.l[i >> 1] * expf(m - v) + 1.f;
-            m = v;
-            trk.idx[i >> 1] = c;
-          } else if (m != -INFINITY) {
-            trk.l[i >> 1] += expf(v - m);
-          }
-        }
-      }
-      if (ph.out_kind == FO_PAIRS) {
-        // the residual stream: this element was last written by phase res_src (by this very thread, or by the
-        // embedding): wait for its tag, add, write with this phase's tag
-        const unsigned want = df_tag32(args.epoch, ph.res_src);
-        uint2* out = reinterpret_cast<uint2*>(ph.out);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = g + (i >> 1) * 8, c = tile * 8 + 2 * q + (i & 1);
-          if (r < M && c < N) {
-            for (int tries = 0; res[i].y != want; ++tries) {
-              if (tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (args.status && df_ld_status(args.status) != 0)))) {
-                df_give_up(sh, args.status, 3);
-                break;
-              }
-              res[i] = df_ld_pair(out + (long long)r * N + c);
+        const int r = g + (i >> 1) * 8, cc = 2 * q + (i & 1);
+        if (r < M && cc < nc) {
+          for (int tries = 0; res[i].y != want; ++tries) {
+            if (df_tired(tries, sh, args.status)) {
+              df_give_up(sh, args.status, 3);
+              break;
             }
-            acc[i] += __uint_as_float(res[i].x);
+            res[i] = df_ld_pair(out + (long long)r * N + tc0 + cc);
           }
+          acc[i] += __uint_as_float(res[i].x);
         }
       }
     }
-    if (finisher) {
-      const int c0 = tile * 8 + 2 * q;
+    const int cc0 = 2 * q;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int r = g + h * 8;
-        if (r >= M || c0 >= N) continue;
-        const bool pair_ok = c0 + 1 < N;
-        const long long o = (long long)r * N + c0;
-        if (ph.out_kind == FO_WORDS) {
-          unsigned* out = reinterpret_cast<unsigned*>(ph.out) + o;
-          if (pair_ok && (o & 1) == 0) df_st_words2(out, acc[2 * h], acc[2 * h + 1], tag16);
-          else {
-            df_st_word(out, acc[2 * h], tag16);
-            if (pair_ok) df_st_word(out + 1, acc[2 * h + 1], tag16);
-          }
-        } else if (ph.out_kind == FO_PAIRS) {
-          uint2* out = reinterpret_cast<uint2*>(ph.out) + o;
-          if (pair_ok && (o & 1) == 0) df_st_pairs2(out, acc[2 * h], acc[2 * h + 1], tag_out);
-          else {
-            df_st_pair(out, acc[2 * h], tag_out);
-            if (pair_ok) df_st_pair(out + 1, acc[2 * h + 1], tag_out);
-          }
-        } else {
-          float* out = reinterpret_cast<float*>(ph.out) + o;
-          out[0] = acc[2 * h];
-          if (pair_ok) out[1] = acc[2 * h + 1];
+    for (int h = 0; h < 2; ++h) {
+      const int r = g + h * 8;
+      if (r >= M || cc0 >= nc) continue;
+      const bool pair_ok = cc0 + 1 < nc;
+      const long long o = (long long)r * N + tc0 + cc0;
+      if (ph.out_kind == FO_WORDS) {
+        unsigned* out = reinterpret_cast<unsigned*>(ph.out) + o;
+        if (pair_ok && (o & 1) == 0) df_st_words2(out, acc[2 * h], acc[2 * h + 1], tag16);
+        else {
+          df_st_word(out, acc[2 * h], tag16);
+          if (pair_ok) df_st_word(out + 1, acc[2 * h + 1], tag16);
         }
+      } else if (ph.out_kind == FO_PAIRS) {
+        uint2* out = reinterpret_cast<uint2*>(ph.out) + o;
+        if (pair_ok && (o & 1) == 0) df_st_pairs2(out, acc[2 * h], acc[2 * h + 1], tag_out);
+        else {
+          df_st_pair(out, acc[2 * h], tag_out);
+          if (pair_ok) df_st_pair(out + 1, acc[2 * h + 1], tag_out);
+        }
+      } else {
+        float* out = reinterpret_cast<float*>(ph.out) + o;
+        out[0] = acc[2 * h];
+        if (pair_ok) out[1] = acc[2 * h + 1];
       }
     }
   }
+  wuse += (unsigned)(T * n_chunks);
   if (ph.track) {
     // the block's (max, sum, argmax) of every row: the four lanes that share a row, then the warps
 #pragma unroll
@@ -780,7 +873,7 @@ template <int I, int T>
 __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& args, const FlowLayout& lay, unsigned char* smem,
                                    FlowShared& sh, unsigned& puse) {
   constexpr int CK = 8 * T, CPP = DS_PAGE / CK;       // keys of a chunk, chunks of a page
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, q = lane & 3;
+  const int tid = df_opaque(threadIdx.x), lane = tid & 31, warp = tid >> 5, g = lane >> 2, q = lane & 3;
   const int hd = ph.head_dim, page_elems = DS_PAGE * hd, cbs = df_col_blocks(hd);
   const int S = ph.n_splits, H = ph.n_heads, group = ph.n_heads / ph.n_kv_heads;
   const float scale_log2 = ph.scale_log2;
@@ -876,7 +969,7 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
       bool landed = false;
 #pragma unroll 1
       for (int h = 0; h < CPP; ++h) {
-        if (((k * CPP + h) & (DF_CWARPS - 1)) != warp) continue;
+        if ((k * CPP + h) % DF_CWARPS != warp) continue;
         const int key0 = (it.pg_first + p) * DS_PAGE + h * CK;
         if (key0 >= hi || key0 + CK <= lo) continue;
         if (!landed) {
@@ -894,7 +987,7 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
           }
           __syncwarp();
         }
-        ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, scale_log2, m, l, acc);
+        ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, scale_log2, m, l, acc, lane);
       }
       __syncwarp();
       if (lane == 0) df_mbar_arrive(&sh.pempty[slot]);      // (every warp, once per page, with or without a chunk in it)
@@ -945,18 +1038,18 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
   }
   if (S > 1) {
     // The block of split 0 merges the splits of its (sequence, head), in split order, as their tags show up: thread d
-    // takes dim d.  Eight splits' worth of loads are in flight together.
+    // takes dim d.  Four splits' worth of loads are in flight together.
     for (int mine = 0; mine < n_mine; ++mine) {
       const FlowItem it = sh.work.it[mine];
       if (it.split != 0 || tid >= hd) continue;
       const long long unit = (long long)it.seq * H + it.head;
       const uint2* src = ph.part + unit * S * (hd + 2);
       float Mx = -INFINITY, Lall = 0.f, o = 0.f;
-      for (int s0 = 0; s0 < S; s0 += 8) {
-        uint2 po[8], pm[8], pl[8];
+      for (int s0 = 0; s0 < S; s0 += 4) {
+        uint2 po[4], pm[4], pl[4];
         unsigned pending = 0;
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 4; ++j)
           if (s0 + j < S) pending |= 1u << j;
         const unsigned have = pending;
         for (int tries = 0; pending != 0; ++tries) {
@@ -965,7 +1058,7 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
             break;
           }
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
+          for (int j = 0; j < 4; ++j)
             if (pending & (1u << j)) {
               const uint2* one = src + (long long)(s0 + j) * (hd + 2);
               po[j] = df_ld_pair(one + tid);
@@ -973,11 +1066,11 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
               pl[j] = df_ld_pair(one + hd + 1);
             }
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
+          for (int j = 0; j < 4; ++j)
             if ((pending & (1u << j)) && po[j].y == tag_part && pm[j].y == tag_part && pl[j].y == tag_part) pending &= ~(1u << j);
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 4; ++j)
           if (have & (1u << j)) {
             const float ms = __uint_as_float(pm[j].x);
             if (ms == -INFINITY) continue;
@@ -994,28 +1087,33 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
 }
 
 // ---- the kernel --------------------------------------------------------------------------------------------
+// LNJ: rows of up to 128 LNJ channels can be normalised; AI, AT: head sizes up to 32 AI, chunks of 8 AT keys.
+template <int LNJ, int AI, int AT>
 __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowArgs args) {
   extern __shared__ __align__(128) unsigned char df_smem_raw[];
   __shared__ FlowShared sh;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   unsigned char* smem = df_smem_raw + ((1024u - (ds_smem(df_smem_raw) & 1023u)) & 1023u);
-  const FlowLayout lay = df_layout(args.rows, args.max_k, args.max_ln_k, args.head_dim, args.w_slots, args.p_slots);
   if (tid == 0) {
-    for (int i = 0; i < lay.w_slots; ++i) {
+    sh.lay = df_layout(args.rows, args.max_k, args.max_ln_k, args.head_dim, args.w_slots, args.p_slots, args.slot_k);
+    for (int i = 0; i < args.w_slots; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ds_smem(&sh.wfull[i])));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(ds_smem(&sh.wempty[i])), "r"(DF_CWARPS));
     }
-    for (int i = 0; i < lay.p_slots; ++i) {
+    for (int i = 0; i < args.p_slots; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ds_smem(&sh.pfull[i])));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(ds_smem(&sh.pempty[i])), "r"(DF_CWARPS));
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     sh.failed = 0;
+    sh.w_issued = 0;
     sh.ok = 1;
     sh.ctx_src = nullptr;
     sh.table_src = nullptr;
     sh.trace = nullptr;
   }
+  __syncthreads();
+  const FlowLayout& lay = sh.lay;
   // The weight slots and the panel start as zeros: products run over whole blocks of 32 k, and what lies behind a row's
   // K elements must be a number (zero times it is added), never the bits of a NaN.
   for (long long i = tid; i < (lay.norm_off - lay.w_off) / 16; i += DF_THREADS)
@@ -1047,18 +1145,16 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowAr
   const bool selects = args.phases[args.n_phases - 1].type == FP_SAMPLE;
   const int n_main = args.n_phases - (selects ? 1 : 0);
 
-  if (warp == DF_CWARPS) {
-    // ---- the weight producer ----
-    FlowArgs mine = args;
-    mine.n_phases = n_main;
-    const unsigned uses = df_weight_producer(mine, lay, smem, sh);
-    if (lane == 0) df_drain(sh.wfull, uses, lay.w_slots);
-  } else if (warp == DF_CWARPS + 1) {
-    // ---- the page producer ----
-    FlowArgs mine = args;
-    mine.n_phases = n_main;
-    const unsigned uses = df_page_producer(mine, lay, smem, sh);
-    if (lane == 0) df_drain(sh.pfull, uses, lay.p_slots);
+  if (warp >= DF_CWARPS) {
+    if (warp == DF_CWARPS) {
+      // ---- the weight producer ----
+      const unsigned uses = df_weight_producer(args, n_main, lay, smem, sh);
+      if (lane == 0) df_drain(sh.wfull, uses, lay.w_slots);
+    } else if (warp == DF_CWARPS + 1) {
+      // ---- the page producer ----
+      const unsigned uses = df_page_producer(args, n_main, lay, smem, sh);
+      if (lane == 0) df_drain(sh.pfull, uses, lay.p_slots);
+    }
   } else {
     // ---- the computing warps ----
     unsigned wuse = 0, puse = 0;
@@ -1093,10 +1189,9 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowAr
           if (!ok && tid == 0 && args.status) atomicCAS(args.status, 0, 4);
         }
       } else if (ph.type == FP_LINEAR) {
-        df_linear_phase(ph, pi, args, lay, smem, sh, wuse);
+        df_linear_phase<LNJ>(ph, pi, args, lay, smem, sh, wuse);
       } else if (ph.type == FP_ATTENTION) {
-        if (ph.head_dim <= 64) df_attention_items<2, 4>(ph, pi, args, lay, smem, sh, puse);      // chunks of 32 keys
-        else df_attention_items<4, 2>(ph, pi, args, lay, smem, sh, puse);                         // chunks of 16 keys
+        df_attention_items<AI, AT>(ph, pi, args, lay, smem, sh, puse);
       }
       df_stamp(sh, 1);
       df_cp_wait();
@@ -1171,11 +1266,24 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowAr
 
 }  // namespace bt
 
+namespace bt {
+
+typedef void (*FlowKernel)(const FlowArgs);
+// The kernel's variants: rows of up to 1024 or 2048 channels to normalise, head sizes up to 64 or 128.
+static FlowKernel df_variant(int max_ln_k, int head_dim, int* index) {
+  const int wide = max_ln_k > 1024 ? 1 : 0, big = head_dim > 64 ? 1 : 0;
+  *index = wide * 2 + big;
+  if (!wide) return big ? decode_flow_kernel<8, 4, 2> : decode_flow_kernel<8, 2, 4>;
+  return big ? decode_flow_kernel<16, 4, 2> : decode_flow_kernel<16, 2, 4>;
+}
+
+}  // namespace bt
+
 extern "C" int bt_decode_flow_phase_bytes() { return (int)sizeof(bt::FlowPhase); }
 
 // Sizes the step's shared memory for these phases (host copy of the program) and `rows` sequences.
-// out[0..6] = max_k, max_ln_k, head_dim, w_slots, p_slots, bytes of dynamic shared memory, 0.  Returns 0, or non-zero with
-// the library's error text when the step does not fit.
+// out[0..7] = max_k, max_ln_k, head_dim, w_slots, p_slots, bytes of dynamic shared memory, slot_k, 0.  Returns 0, or
+// non-zero with the library's error text when the step does not fit.
 extern "C" int bt_decode_flow_plan(const void* phases_host, int n_phases, int rows, long long* out) {
   using namespace bt;
   const FlowPhase* ph = reinterpret_cast<const FlowPhase*>(phases_host);
@@ -1188,7 +1296,7 @@ extern "C" int bt_decode_flow_plan(const void* phases_host, int n_phases, int ro
       BT_CHECK(ph[i].K % 8 == 0 && ph[i].K >= 8, "decode_flow: K=%d is no multiple of 8", ph[i].K);
       if (ph[i].K > max_k) max_k = ph[i].K;
       if (ph[i].a_kind == FA_LAYERNORM) {
-        BT_CHECK(ph[i].K <= 32 * 64, "decode_flow: a LayerNorm over %d channels exceeds the 2048 a warp holds", ph[i].K);
+        BT_CHECK(ph[i].K <= 16 * 128, "decode_flow: a LayerNorm over %d channels exceeds the 2048 a warp holds", ph[i].K);
         if (ph[i].K > max_ln_k) max_ln_k = ph[i].K;
       }
     } else if (ph[i].type == FP_ATTENTION) {
@@ -1198,8 +1306,23 @@ extern "C" int bt_decode_flow_plan(const void* phases_host, int n_phases, int ro
       head_dim = ph[i].head_dim;
     }
   }
+  // The k extent of a weight slot (a multiple of 32, at most 1024; a slot holds one piece of one tile's k): the one
+  // that leaves the least of the ring unused; of equals the largest.
+  int slot_k = 32;
+  long long best = -1;
+  for (int c = 32; c <= DF_MAX_SLOT_K; c += 32) {
+    long long cost = 0;
+    for (int i = 0; i < n_phases; ++i)
+      if (ph[i].type == FP_LINEAR) cost += (long long)ph[i].N * ((ph[i].K + c - 1) / c) * c;
+    if (best < 0 || cost <= best) {
+      best = cost;
+      slot_k = c;
+    }
+  }
+  int variant = 0;
+  FlowKernel kernel = df_variant(max_ln_k, head_dim, &variant);
   cudaFuncAttributes attr;
-  cudaError_t e = cudaFuncGetAttributes(&attr, decode_flow_kernel);
+  cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
   BT_CHECK(e == cudaSuccess, "decode_flow: cannot read the kernel's attributes: %s", cudaGetErrorString(e));
   const long long budget = 227 * 1024 - (long long)attr.sharedSizeBytes - 64;
   // page slots: about 64 KB of them (at least 2, at most 8); weight slots: what is left (at least 4)
@@ -1210,21 +1333,22 @@ extern "C" int bt_decode_flow_plan(const void* phases_host, int n_phases, int ro
   }
   int w_slots = 0;
   for (;;) {
-    const FlowLayout fixed = df_layout(rows, max_k, max_ln_k, head_dim, 0, p_slots);
-    w_slots = (int)((budget - fixed.total) / DF_WSLOT);
+    const FlowLayout fixed = df_layout(rows, max_k, max_ln_k, head_dim, 0, p_slots, slot_k);
+    w_slots = (int)((budget - fixed.total) / fixed.w_slot_bytes);
     if (w_slots >= 4 || p_slots <= 2) break;
     --p_slots;
   }
   BT_CHECK(w_slots >= 4, "decode_flow: %d rows of K=%d leave no room for the weights' ring in shared memory", rows, max_k);
   if (w_slots > DF_MAX_WSLOTS) w_slots = DF_MAX_WSLOTS;
-  const FlowLayout lay = df_layout(rows, max_k, max_ln_k, head_dim, w_slots, p_slots);
+  const FlowLayout lay = df_layout(rows, max_k, max_ln_k, head_dim, w_slots, p_slots, slot_k);
   out[0] = max_k;
   out[1] = max_ln_k;
   out[2] = head_dim;
   out[3] = w_slots;
   out[4] = p_slots;
   out[5] = lay.total;
-  out[6] = 0;
+  out[6] = slot_k;
+  out[7] = 0;
   return 0;
 }
 
@@ -1239,21 +1363,23 @@ extern "C" int bt_decode_flow(const void* phases_dev, int n_phases, unsigned epo
   const int n_sms = sm_count();
   BT_CHECK(n_sms > 0, "decode_flow: cannot read the number of multiprocessors of the current device");
   const long long smem_bytes = plan[5];
-  static long long configured[64];
+  int variant = 0;
+  FlowKernel kernel = df_variant((int)plan[1], (int)plan[2], &variant);
+  static long long configured[64][4];
   int dev = 0;
   cudaGetDevice(&dev);
   BT_CHECK(dev >= 0 && dev < 64, "decode_flow: device %d is beyond the 64 this library tracks", dev);
-  if (configured[dev] < smem_bytes) {
-    cudaError_t e = cudaFuncSetAttribute(decode_flow_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+  if (configured[dev][variant] < smem_bytes) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
     BT_CHECK(e == cudaSuccess, "decode_flow: cannot reserve %lld bytes of shared memory: %s", smem_bytes, cudaGetErrorString(e));
-    configured[dev] = smem_bytes;
+    configured[dev][variant] = smem_bytes;
   }
   cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned), stream);
   BT_CHECK(e == cudaSuccess, "decode_flow: cannot clear the barrier counter: %s", cudaGetErrorString(e));
   FlowArgs args{reinterpret_cast<const FlowPhase*>(phases_dev), n_phases, epoch, counter, status, trace, rows, (int)plan[0],
-                (int)plan[1], (int)plan[2], (int)plan[3], (int)plan[4]};
+                (int)plan[1], (int)plan[2], (int)plan[3], (int)plan[4], (int)plan[6]};
   void* kargs[] = {(void*)&args};
-  e = cudaLaunchCooperativeKernel((const void*)decode_flow_kernel, dim3(n_sms), dim3(DF_THREADS), kargs, (size_t)smem_bytes, stream);
+  e = cudaLaunchCooperativeKernel((const void*)kernel, dim3(n_sms), dim3(DF_THREADS), kargs, (size_t)smem_bytes, stream);
   BT_CHECK(e == cudaSuccess, "decode_flow: launch failed: %s", cudaGetErrorString(e));
   count_launch();
   return 0;

@@ -38,11 +38,12 @@ __device__ __forceinline__ unsigned ds_swizzled(unsigned tiles, int row, int chu
 
 // One chunk of 8 T keys (rows row0.. of the page whose keys lie at Ks and values at Vs, shared-memory addresses):
 // scores, the running softmax (32-bit), the weighted values.  `qa`: the query's fragments (row 0 of the tile),
-// two registers per 16 dims.
+// two registers per 16 dims.  `lane`: the caller's lane (a caller may pass a number the compiler cannot see through, so
+// that the addresses derived from it are not kept in registers from one call to the next).
 template <int I, int T>
 __device__ __forceinline__ void ds_attn_chunk(const unsigned (&qa)[I * 4], unsigned Ks, unsigned Vs, int hd, int row0, int key0, int lo,
-                                              int hi, float scale_log2, float& m, float& l, float (&acc)[I * 4][4]) {
-  const int lane = threadIdx.x & 31, q = lane & 3;
+                                              int hi, float scale_log2, float& m, float& l, float (&acc)[I * 4][4], int lane) {
+  const int q = lane & 3;
   const int blk = lane >> 3, r = lane & 7;       // this lane gives the address of row r of block blk of a load of four
   float s[T][4];
 #pragma unroll

@@ -960,7 +960,7 @@ __device__ bool ds_attention_items(const Phase& ph, const Phase* maps, unsigned 
         }
         __syncwarp();
       }
-      ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, scale_log2, m, l, acc);
+      ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, scale_log2, m, l, acc, lane);
     };
     // chunks go round the warps, counted through the block's stream so that every warp gets some
     if (total <= slots) {          // (uniform in the block) all pages are on their way: a warp goes straight to its chunks
