@@ -67,13 +67,13 @@ struct FlowPhase {
                                  // FO_PLAIN: plain 32-bit (the logits)
   int a_src;                     // FA_LAYERNORM: index of the phase that wrote the pairs this phase reads
   int res_src;                   // FO_PAIRS: index of the phase that last wrote the pairs this phase adds to
-  int pad0_;
+  int col_q;                     // set by bt_decode_flow_plan: N / blocks ...
   const void* a;
   const int* rows;               // FA_LAYERNORM: row r of the panel is row rows[r] of `a` (null: r)
   const float* gamma;
   const float* beta;
   float eps;
-  int pad1_;
+  int col_r;                     // ... and N % blocks: block b takes col_q columns, one more if b < col_r
   const __nv_bfloat16* w;        // [N, K]
   const float* bias;
   void* out;                     // [M][N] in the layout of out_kind
@@ -115,7 +115,7 @@ struct FlowPhase {
   int* adv_ctx;
   const float* partials;         // greedy selection from the readout's `track` instead of from the logits
   int n_partials;
-  int pad2_;
+  int n_chunks;                  // set by bt_decode_flow_plan: slots a tile's k takes
   // ---- attention: tensor maps of the layer's key and value pools, seen as [pages * kv_heads * 64 rows][head_dim] ----
   alignas(64) CUtensorMap k_map;
   CUtensorMap v_map;
@@ -170,7 +170,7 @@ struct FlowLayout {
   int w_slots, p_slots, p_slot_bytes;
   int slot_k, w_row, w_slot_bytes;       // k extent of a weight slot, bytes between its 8 rows (16 apart modulo 128: no bank conflicts), its size
   int panel_rows, panel_stride;          // rows of the panel (8 or 16) and bytes between them
-  long long w_off, p_off, panel_off, norm_off, rows_off, acc_off, total;
+  long long w_off, p_off, panel_off, rows_off, acc_off, total;
 };
 __host__ __device__ inline int df_kpad(int K) { return (K + 31) / 32 * 32; }
 __host__ __device__ inline int df_col_blocks(int head_dim) { return (head_dim + 63) / 64; }
@@ -194,8 +194,6 @@ __host__ __device__ inline FlowLayout df_layout(int rows, int max_k, int max_ln_
   at += (long long)w_slots * L.w_slot_bytes;
   L.panel_off = at;
   at += (long long)L.panel_rows * L.panel_stride;
-  L.norm_off = at;                               // gamma, beta of the phase's LayerNorm
-  at += 2ll * max_ln_k * 4;
   L.rows_off = at;                               // attention: query, new key, new value of every item
   at += (long long)DF_MAX_ITEMS * 3 * head_dim * 2;
   at = (at + 15) / 16 * 16;
@@ -221,6 +219,7 @@ struct FlowShared {
   alignas(16) float red[2][DF_CWARPS][32][4];  // the warps' partial sums of a tile, two sets used in turn (read and written 16 bytes at a time)
   float ml[2][DF_CWARPS][2];
   float trk[DF_CWARPS][16][3];
+  alignas(16) float ln[2][DF_CWARPS][8];       // LayerNorm: the warps' sums and squared deviations of (at most 8) rows
   SampleShared sample;
   alignas(64) FlowPhase phase[2];
   FlowWork work;                   // the computing warps' list of attention items
@@ -280,18 +279,20 @@ struct FlowArgs {
   int* status;
   long long* trace;
   int rows, max_k, max_ln_k, head_dim, w_slots, p_slots, slot_k;
+  unsigned tag16;                  // epoch % 65535 + 1: the tag of this launch's bfloat16 words (never zero)
 };
 
 __device__ __forceinline__ unsigned df_tag32(unsigned epoch, int phase) { return (epoch << 10) | (unsigned)(phase + 1); }
-__device__ __forceinline__ unsigned df_tag16(unsigned epoch) { return epoch % 65535u + 1u; }
 
 // ---- how a product's output columns are dealt out -----------------------------------------------------------
 // Block b of B takes the columns [b N / B, (b + 1) N / B): every block gets N / B columns or one more, so that all
 // multiprocessors pull the same share of the weights.  A block works through its columns in tiles of (at most) 8.
-__device__ __forceinline__ void df_columns(int N, int& c0, int& c1) {
-  c0 = (int)((long long)blockIdx.x * N / gridDim.x);
-  c1 = (int)((long long)(blockIdx.x + 1) * N / gridDim.x);
+__device__ __forceinline__ void df_columns(const FlowPhase* ph, int& c0, int& c1) {
+  const int b = blockIdx.x, q = ph->col_q, r = ph->col_r;
+  c0 = b * q + min(b, r);
+  c1 = c0 + q + (b < r ? 1 : 0);
 }
+__device__ __forceinline__ void df_prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p)); }
 
 // ---- the producers ---------------------------------------------------------------------------------------
 // The weight producer: one warp that walks the phases and, for every linear phase, sends the block's tiles through the
@@ -306,8 +307,16 @@ __device__ unsigned df_weight_producer(const FlowArgs& args, int n_phases, const
     if (ph->type != FP_LINEAR) continue;
     const int N = ph->N, K = ph->K;
     int c0, c1;
-    df_columns(N, c0, c1);
-    const int n_chunks = (K + lay.slot_k - 1) / lay.slot_k;
+    df_columns(ph, c0, c1);
+    const int n_chunks = ph->n_chunks;
+    // What the phase's computing warps will read from plain memory, on its way into the L2 cache: the block's bias
+    // values, and (one block for all) the norm's parameters.
+    if (ph->bias && c0 + lane * 32 < c1) df_prefetch_l2(ph->bias + c0 + lane * 32);
+    if (ph->a_kind == FA_LAYERNORM && pi % (int)gridDim.x == (int)blockIdx.x)
+      for (int k = lane * 32; k < K; k += 32 * 32) {
+        df_prefetch_l2(ph->gamma + k);
+        if (ph->beta) df_prefetch_l2(ph->beta + k);
+      }
     for (int t0 = c0; t0 < c1 && !sh.failed; t0 += 8) {
       const int rows_here = min(8, c1 - t0);
       const __nv_bfloat16* src = ph->w + (long long)(t0 + lane) * K;
@@ -468,82 +477,234 @@ __device__ __forceinline__ bool df_tired(int tries, FlowShared& sh, int* status)
   return tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (status && df_ld_status(status) != 0)));
 }
 
-// LayerNorm of one row per warp from tagged pairs.  A lane holds four neighbouring channels of every 128 (J such
-// groups: K <= 128 J): loaded until every tag is the expected one, then the mean, then the variance about it (two
-// passes over registers), then the normalised row goes into the panel as bfloat16, 8 bytes a lane at a time.
-// Returns false if the tags did not show up in time.
-template <int J>
-__device__ __forceinline__ bool df_layernorm_row(const uint2* __restrict__ src, bool live, int K, unsigned tag, float eps,
-                                                 const float* gs, const float* bs, __nv_bfloat16* dst, FlowShared& sh, int* status,
-                                                 bool params_in_flight, int lane) {
-  // e[j][i]: value and tag of channel 128 j + 4 lane + i; the loads' own registers hold the row
-  uint2 e[J][4];
-  unsigned pending = 0;
+// out[r] = the sum over the warps, in warp order, of what each left for row r (read four rows at a time).
+template <int RP>
+__device__ __forceinline__ void df_sum_warps(const float (*part)[8], float (&out)[RP]) {
 #pragma unroll
-  for (int j = 0; j < J; ++j) {
+  for (int r = 0; r < RP; ++r) out[r] = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) e[j][i] = make_uint2(0u, tag);
-    if (live && lane * 4 + j * 128 < K) pending |= 1u << j;
-  }
-  const unsigned mine = pending;
-  const uint2* mine_src = src + lane * 4;
-  for (int tries = 0; pending != 0; ++tries) {
-    if (df_tired(tries, sh, status)) {
-      df_give_up(sh, status, 3);
-      break;
+  for (int w2 = 0; w2 < DF_CWARPS; ++w2) {
+    if (RP >= 4) {
+#pragma unroll
+      for (int r4 = 0; r4 < RP / 4; ++r4) {
+        const float4 v = *reinterpret_cast<const float4*>(&part[w2][4 * r4]);
+        out[4 * r4] += v.x;
+        out[4 * r4 + 1] += v.y;
+        out[4 * r4 + 2] += v.z;
+        out[4 * r4 + 3] += v.w;
+      }
+    } else {
+      const float2 v = *reinterpret_cast<const float2*>(&part[w2][0]);
+      out[0] += v.x;
+      if (RP > 1) out[RP > 1 ? 1 : 0] += v.y;
     }
-    // all loads of a round in flight together; a round loads what is still pending
+  }
+}
+
+// LayerNorm of the phase's rows from tagged pairs, all warps on every row: warp w takes the quads (four neighbouring
+// channels) [w qpw, (w + 1) qpw) of each row, a lane Q of them (K <= 768 Q).  Rows go in passes of RP (as many as keep
+// the loads of a pass in 64 registers): loaded until every tag is the expected one, then each warp's sum per row, the
+// mean from the warps' sums in warp order, each warp's squared deviations, the variance, and the normalised rows go
+// into the panel as bfloat16, 8 bytes a lane at a time.
+template <int Q>
+__device__ __forceinline__ void df_layernorm_rows(const FlowPhase& ph, const FlowArgs& args, unsigned char* panel, int stride,
+                                                  FlowShared& sh, int tid) {
+  constexpr int RP = Q == 1 ? 8 : (Q == 2 ? 4 : 2);
+  const int lane = tid & 31, warp = tid >> 5;
+  const int K = ph.K, M = ph.M, quads = K >> 2, qpw = (quads + DF_CWARPS - 1) / DF_CWARPS;
+  const unsigned tag = df_tag32(args.epoch, ph.a_src);
+  const float inv_k = 1.f / (float)K;
+  int qd[Q];
+  unsigned has = 0;
+  float4 g4[Q], b4[Q];
 #pragma unroll
-    for (int j = 0; j < J; ++j)
-      if (pending & (1u << j)) {
-        df_ld_pairs2(mine_src + j * 128, e[j][0], e[j][1]);
-        df_ld_pairs2(mine_src + j * 128 + 2, e[j][2], e[j][3]);
+  for (int i = 0; i < Q; ++i) {
+    const int k = lane + 32 * i;
+    qd[i] = warp * qpw + k;
+    g4[i] = b4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (k < qpw && qd[i] < quads) {
+      has |= 1u << i;
+      g4[i] = __ldg(reinterpret_cast<const float4*>(ph.gamma) + qd[i]);
+      if (ph.beta) b4[i] = __ldg(reinterpret_cast<const float4*>(ph.beta) + qd[i]);
+    }
+  }
+  const uint2* x = reinterpret_cast<const uint2*>(ph.a);
+  for (int r0 = 0; r0 < M; r0 += RP) {
+    // e[r][i][c]: value and tag of channel 4 qd[i] + c of row r0 + r; the loads' own registers hold the rows
+    uint2 e[RP][Q][4];
+    unsigned src[RP];          // where each row begins, in pairs
+    unsigned pending = 0;
+#pragma unroll
+    for (int r = 0; r < RP; ++r) {
+      const int row = r0 + r;
+      src[r] = (unsigned)((row < M ? (ph.rows ? ph.rows[row] : row) : 0) * K);
+#pragma unroll
+      for (int i = 0; i < Q; ++i) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) e[r][i][c] = make_uint2(0u, tag);
+        if (row < M && (has & (1u << i))) pending |= 1u << (r * Q + i);
+      }
+    }
+    const unsigned mine = pending;
+    for (int tries = 0; pending != 0; ++tries) {
+      if (df_tired(tries, sh, args.status)) {
+        df_give_up(sh, args.status, 3);
+        break;
+      }
+      // all loads of a round in flight together; a round loads what is still pending
+#pragma unroll
+      for (int r = 0; r < RP; ++r)
+#pragma unroll
+        for (int i = 0; i < Q; ++i)
+          if (pending & (1u << (r * Q + i))) {
+            df_ld_pairs2(x + (src[r] + (unsigned)(qd[i] * 4)), e[r][i][0], e[r][i][1]);
+            df_ld_pairs2(x + (src[r] + (unsigned)(qd[i] * 4 + 2)), e[r][i][2], e[r][i][3]);
+          }
+#pragma unroll
+      for (int r = 0; r < RP; ++r)
+#pragma unroll
+        for (int i = 0; i < Q; ++i)
+          if (((e[r][i][0].y ^ tag) | (e[r][i][1].y ^ tag) | (e[r][i][2].y ^ tag) | (e[r][i][3].y ^ tag)) == 0u)
+            pending &= ~(1u << (r * Q + i));
+    }
+    // the warp's sum of every row (what a lane does not hold is zero)
+    float part[RP];
+#pragma unroll
+    for (int r = 0; r < RP; ++r) {
+      float t = 0.f;
+#pragma unroll
+      for (int i = 0; i < Q; ++i)
+        t += (__uint_as_float(e[r][i][0].x) + __uint_as_float(e[r][i][1].x)) + (__uint_as_float(e[r][i][2].x) + __uint_as_float(e[r][i][3].x));
+      part[r] = t;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int r = 0; r < RP; ++r) part[r] += __shfl_xor_sync(0xffffffffu, part[r], o);
+    if (lane < RP) {
+      float mine_sum = part[0];
+#pragma unroll
+      for (int r = 1; r < RP; ++r)
+        if (lane == r) mine_sum = part[r];
+      sh.ln[0][warp][lane] = mine_sum;
+    }
+    df_bar_consumers();
+    float mean[RP];
+    df_sum_warps<RP>(sh.ln[0], mean);
+#pragma unroll
+    for (int r = 0; r < RP; ++r) mean[r] *= inv_k;
+#pragma unroll
+    for (int r = 0; r < RP; ++r) {
+      float t = 0.f;
+#pragma unroll
+      for (int i = 0; i < Q; ++i)
+        if (mine & (1u << (r * Q + i))) {
+          const float x0 = __uint_as_float(e[r][i][0].x) - mean[r], x1 = __uint_as_float(e[r][i][1].x) - mean[r];
+          const float x2 = __uint_as_float(e[r][i][2].x) - mean[r], x3 = __uint_as_float(e[r][i][3].x) - mean[r];
+          t += (x0 * x0 + x1 * x1) + (x2 * x2 + x3 * x3);
+        }
+      part[r] = t;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int r = 0; r < RP; ++r) part[r] += __shfl_xor_sync(0xffffffffu, part[r], o);
+    if (lane < RP) {
+      float mine_sum = part[0];
+#pragma unroll
+      for (int r = 1; r < RP; ++r)
+        if (lane == r) mine_sum = part[r];
+      sh.ln[1][warp][lane] = mine_sum;
+    }
+    df_bar_consumers();
+    float var[RP];
+    df_sum_warps<RP>(sh.ln[1], var);
+#pragma unroll
+    for (int r = 0; r < RP; ++r) {
+      // (the result is rounded to bfloat16: the hardware's reciprocal square root, 2 ulp, is far below that)
+      const float rs = rsqrtf(var[r] * inv_k + ph.eps), shift = -mean[r] * rs;
+#pragma unroll
+      for (int i = 0; i < Q; ++i)
+        if (mine & (1u << (r * Q + i))) {
+          uint2 packed;
+          packed.x = ds_pack(fmaf(fmaf(__uint_as_float(e[r][i][0].x), rs, shift), g4[i].x, b4[i].x),
+                             fmaf(fmaf(__uint_as_float(e[r][i][1].x), rs, shift), g4[i].y, b4[i].y));
+          packed.y = ds_pack(fmaf(fmaf(__uint_as_float(e[r][i][2].x), rs, shift), g4[i].z, b4[i].z),
+                             fmaf(fmaf(__uint_as_float(e[r][i][3].x), rs, shift), g4[i].w, b4[i].w));
+          *reinterpret_cast<uint2*>(panel + (unsigned)((r0 + r) * stride + qd[i] * 8)) = packed;
+        }
+    }
+  }
+}
+
+// The panel from tagged bfloat16 words [M][K] (what a product or the attention left): loaded until every tag is this
+// launch's, packed two to a word.  
+__device__ __forceinline__ void df_panel_from_words(const FlowPhase& ph, const FlowArgs& args, unsigned char* panel, int stride,
+                                                 FlowShared& sh, int tid) {
+  const int K = ph.K, M = ph.M;
+  // tagged words [M][K]: four at a time.  A thread takes the quads tid, tid + threads, ... of every row; a batch is
+  // B (row, quad) pairs whose loads are in flight together.
+  const unsigned tags = args.tag16 << 16;
+  const unsigned* a = reinterpret_cast<const unsigned*>(ph.a);
+  const int qpr = K / 4, per_row = (qpr + DF_CONSUMERS - 1) / DF_CONSUMERS, items = M * per_row;
+  constexpr int B = 16;
+  for (int i0 = 0; i0 < items; i0 += B) {
+    const int r0 = i0 / per_row, j0 = i0 - r0 * per_row;
+    uint4 v[B];
+    unsigned pending = 0;
+    {
+      int r = r0, jq = j0;
+#pragma unroll
+      for (int j = 0; j < B; ++j) {
+        if (r < M && tid + jq * DF_CONSUMERS < qpr) pending |= 1u << j;
+        if (++jq == per_row) {
+          jq = 0;
+          ++r;
+        }
+      }
+    }
+    const unsigned mine = pending;
+    for (int tries = 0; pending != 0; ++tries) {
+      if (df_tired(tries, sh, args.status)) {
+        df_give_up(sh, args.status, 3);
+        break;
+      }
+      int r = r0, jq = j0;
+#pragma unroll
+      for (int j = 0; j < B; ++j) {
+        if (pending & (1u << j)) v[j] = df_ld_words4(a + (unsigned)(r * K + (tid + jq * DF_CONSUMERS) * 4));
+        if (++jq == per_row) {
+          jq = 0;
+          ++r;
+        }
       }
 #pragma unroll
-    for (int j = 0; j < J; ++j)
-      if (((e[j][0].y ^ tag) | (e[j][1].y ^ tag) | (e[j][2].y ^ tag) | (e[j][3].y ^ tag)) == 0u) pending &= ~(1u << j);
-  }
-  const bool ok = __all_sync(0xffffffffu, pending == 0);
-  float s = 0.f;
-#pragma unroll
-  for (int j = 0; j < J; ++j)
-    if (mine & (1u << j))
-      s += (__uint_as_float(e[j][0].x) + __uint_as_float(e[j][1].x)) + (__uint_as_float(e[j][2].x) + __uint_as_float(e[j][3].x));
-  const float mean = warp_sum(s) / (float)K;
-  float d2 = 0.f;
-#pragma unroll
-  for (int j = 0; j < J; ++j)
-    if (mine & (1u << j)) {
-      const float x0 = __uint_as_float(e[j][0].x) - mean, x1 = __uint_as_float(e[j][1].x) - mean;
-      const float x2 = __uint_as_float(e[j][2].x) - mean, x3 = __uint_as_float(e[j][3].x) - mean;
-      d2 += (x0 * x0 + x1 * x1) + (x2 * x2 + x3 * x3);
+      for (int j = 0; j < B; ++j)
+        if ((pending & (1u << j)) && ((((v[j].x ^ tags) | (v[j].y ^ tags) | (v[j].z ^ tags) | (v[j].w ^ tags)) >> 16) == 0u))
+          pending &= ~(1u << j);
     }
-  const float rs = 1.f / sqrtf(warp_sum(d2) / (float)K + eps);
-  if (params_in_flight) {      // gamma and beta were asked for before the row: they have had the row's time to arrive
-    df_cp_wait();
-    df_bar_consumers();
-  }
-  if (!live) return ok;
+    int r = r0, jq = j0;
 #pragma unroll
-  for (int j = 0; j < J; ++j)
-    if (mine & (1u << j)) {
-      const int c = lane * 4 + j * 128;
-      const float4 g4 = *reinterpret_cast<const float4*>(gs + c);
-      float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (bs) b4 = *reinterpret_cast<const float4*>(bs + c);
-      uint2 packed;
-      packed.x = ds_pack((__uint_as_float(e[j][0].x) - mean) * rs * g4.x + b4.x, (__uint_as_float(e[j][1].x) - mean) * rs * g4.y + b4.y);
-      packed.y = ds_pack((__uint_as_float(e[j][2].x) - mean) * rs * g4.z + b4.z, (__uint_as_float(e[j][3].x) - mean) * rs * g4.w + b4.w);
-      *reinterpret_cast<uint2*>(dst + c) = packed;
+    for (int j = 0; j < B; ++j) {
+      if (mine & (1u << j)) {
+        uint2 packed;
+        packed.x = __byte_perm(v[j].x, v[j].y, 0x5410);
+        packed.y = __byte_perm(v[j].z, v[j].w, 0x5410);
+        *reinterpret_cast<uint2*>(panel + (unsigned)(r * stride + (tid + jq * DF_CONSUMERS) * 8)) = packed;
+      }
+      if (++jq == per_row) {
+        jq = 0;
+        ++r;
+      }
     }
-  return ok;
+  }
 }
 
 // Builds the panel of the phase's rows: row r at panel + r * stride, K bfloat16 and zeros up to the next multiple of 32.
-// LNJ: the LayerNorm path holds rows of up to 128 LNJ channels.
-template <int LNJ>
+// LNQ: the LayerNorm path takes rows of up to 768 LNQ channels.
+template <int LNQ>
 __device__ void df_build_panel(const FlowPhase& ph, const FlowArgs& args, const FlowLayout& lay, unsigned char* smem, FlowShared& sh) {
-  const int tid = df_opaque(threadIdx.x), warp = tid >> 5;
+  const int tid = df_opaque(threadIdx.x);
   const int K = ph.K, M = ph.M, KP = df_kpad(K);
   unsigned char* panel = smem + lay.panel_off;
   const int stride = lay.panel_stride;
@@ -554,80 +715,25 @@ __device__ void df_build_panel(const FlowPhase& ph, const FlowArgs& args, const 
       reinterpret_cast<__nv_bfloat16*>(panel + (size_t)r * stride)[c] = __float2bfloat16_rn(0.f);
     }
   if (ph.a_kind == FA_LAYERNORM) {
-    float* gs = reinterpret_cast<float*>(smem + lay.norm_off);
-    float* bs = ph.beta ? gs + K : nullptr;
-    for (int i = tid; i < K / 4; i += DF_CONSUMERS) {         // (K is a multiple of 8)
-      df_cp16(gs + i * 4, ph.gamma + i * 4);
-      if (bs) df_cp16(bs + i * 4, ph.beta + i * 4);
-    }
-    const unsigned tag = df_tag32(args.epoch, ph.a_src);
-    const uint2* x = reinterpret_cast<const uint2*>(ph.a);
-    for (int r0 = 0; r0 < M; r0 += DF_CWARPS) {
-      const int r = r0 + warp;
-      const bool live = r < M;
-      const uint2* src = x + (long long)(live ? (ph.rows ? ph.rows[r] : r) : 0) * K;
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(panel + (size_t)(live ? r : 0) * stride);
-      df_layernorm_row<LNJ>(src, live, K, tag, ph.eps, gs, bs, dst, sh, args.status, r0 == 0, tid & 31);
-    }
+    df_layernorm_rows<LNQ>(ph, args, panel, stride, sh, tid);
   } else {
-    // tagged words [M][K]: four at a time.  A thread takes the quads tid, tid + threads, ... of every row; a batch is
-    // B (row, quad) pairs whose loads are in flight together.
-    const unsigned tags = df_tag16(args.epoch) << 16;
-    const unsigned* a = reinterpret_cast<const unsigned*>(ph.a);
-    const int qpr = K / 4, per_row = (qpr + DF_CONSUMERS - 1) / DF_CONSUMERS, items = M * per_row;
-    constexpr int B = 12;
-    for (int i0 = 0; i0 < items; i0 += B) {
-      const int r0 = i0 / per_row, j0 = i0 - r0 * per_row;
-      uint4 v[B];
-      unsigned pending = 0;
-      {
-        int r = r0, jq = j0;
-#pragma unroll
-        for (int j = 0; j < B; ++j) {
-          if (r < M && tid + jq * DF_CONSUMERS < qpr) pending |= 1u << j;
-          if (++jq == per_row) {
-            jq = 0;
-            ++r;
-          }
-        }
-      }
-      const unsigned mine = pending;
-      for (int tries = 0; pending != 0; ++tries) {
-        if (df_tired(tries, sh, args.status)) {
-          df_give_up(sh, args.status, 3);
-          break;
-        }
-        int r = r0, jq = j0;
-#pragma unroll
-        for (int j = 0; j < B; ++j) {
-          if (pending & (1u << j)) v[j] = df_ld_words4(a + (unsigned)(r * K + (tid + jq * DF_CONSUMERS) * 4));
-          if (++jq == per_row) {
-            jq = 0;
-            ++r;
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < B; ++j)
-          if ((pending & (1u << j)) && ((((v[j].x ^ tags) | (v[j].y ^ tags) | (v[j].z ^ tags) | (v[j].w ^ tags)) >> 16) == 0u))
-            pending &= ~(1u << j);
-      }
-      int r = r0, jq = j0;
-#pragma unroll
-      for (int j = 0; j < B; ++j) {
-        if (mine & (1u << j)) {
-          uint2 packed;
-          packed.x = __byte_perm(v[j].x, v[j].y, 0x5410);
-          packed.y = __byte_perm(v[j].z, v[j].w, 0x5410);
-          *reinterpret_cast<uint2*>(panel + (unsigned)(r * stride + (tid + jq * DF_CONSUMERS) * 8)) = packed;
-        }
-        if (++jq == per_row) {
-          jq = 0;
-          ++r;
-        }
-      }
-    }
+    df_panel_from_words(ph, args, panel, stride, sh, tid);
   }
   df_bar_consumers();
+}
+
+// The activation of a product's epilogue.  A result that is rounded to bfloat16 anyway takes the tanh form of GELU with
+// the hardware's tanh (relative error about 2^-11, below that rounding), as the prefill's product does; 32-bit results
+// get the full-precision functions.
+__device__ __noinline__ float df_activation_exact(float x, int act) { return apply_activation(x, act); }
+__device__ __forceinline__ float df_activation(float x, int act, bool exact) {
+  if (act == kActNone) return x;
+  if (act == kActGeluTanh && !exact) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;\n" : "=f"(t) : "f"(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    return 0.5f * x * (1.f + t);
+  }
+  return df_activation_exact(x, act);
 }
 
 // Running (max, sum of exp(value - max), first index of the max) of the values a thread has finished, for two rows.
@@ -649,38 +755,56 @@ __device__ __forceinline__ void df_bar_group(int id, int threads) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
 }
 
-// A linear phase for the computing warps.  `wuse`: how many weight slots the block has consumed so far in the launch.
+// How far the computing warps have come in the ring of weight slots: slots consumed so far in the launch, and where the
+// next one lies (slot = use % slots, turn = use / slots, carried along instead of divided out).
+struct FlowRing {
+  unsigned use, slot, turn;
+};
+
+// A linear phase for the computing warps.
 //
 // The block's columns come as T tiles of at most 8.  G warps share a tile (G = 6, 3, 2 or 1: the most that leaves every
 // tile a group), splitting its k between them 32 elements at a time; 6 / G tiles are in work together.  Warp 0 of a tile's
 // group adds the group's partial sums in warp order and finishes the tile (bias, activation, residual, tags).  A slot of
 // the ring belongs to one tile: every warp of the tile's group hands it back with 6 / G of the 6 arrivals that free it.
-template <int LNJ>
+template <int LNQ>
 __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& args, const FlowLayout& lay, unsigned char* smem,
-                                FlowShared& sh, unsigned& wuse) {
+                                FlowShared& sh, FlowRing& ring) {
   const int tid = df_opaque(threadIdx.x), lane = tid & 31, warp = tid >> 5, g = lane >> 2, q = lane & 3;
-  const int N = ph.N, K = ph.K, M = ph.M;
+  // (What the phase needs of its description and of the layout is read once, into registers: both lie in shared
+  // memory, and every wait in between would have the compiler read them again.)
+  const int N = ph.N, K = ph.K, M = ph.M, out_kind = ph.out_kind, act = ph.act, res_src = ph.res_src;
+  const float* const bias_p = ph.bias;
+  void* const out_p = ph.out;
+  float* const track_p = ph.track;
+  int* const status = args.status;
+  const unsigned w_slots = (unsigned)lay.w_slots, w_slot_bytes = (unsigned)lay.w_slot_bytes;
+  const int slot_k = lay.slot_k, w_row = lay.w_row;
   int c0, c1;
-  df_columns(N, c0, c1);
-  const int T = (c1 - c0 + 7) / 8, n_chunks = (K + lay.slot_k - 1) / lay.slot_k;
+  df_columns(&ph, c0, c1);
+  const int T = (c1 - c0 + 7) >> 3, n_chunks = ph.n_chunks;
   if (T == 0) {       // nothing to do in this phase (uniform for the block)
-    if (ph.track && tid < 16 && tid < M) {
-      float* dst = ph.track + ((long long)tid * gridDim.x + blockIdx.x) * 4;
+    if (track_p && tid < 16 && tid < M) {
+      float* dst = track_p + ((long long)tid * gridDim.x + blockIdx.x) * 4;
       dst[0] = -INFINITY;
       dst[1] = 0.f;
       dst[2] = __int_as_float(0x7fffffff);
     }
     return;
   }
-  df_build_panel<LNJ>(ph, args, lay, smem, sh);
+  df_build_panel<LNQ>(ph, args, lay, smem, sh);
   df_stamp(sh, 2);
-  const int G = T == 1 ? 6 : (T == 2 ? 3 : (T == 3 ? 2 : 1)), n_groups = DF_CWARPS / G;
-  const int grp = warp / G, wg = warp - grp * G;
+  // (tiles in work together: as many as there are, and no more than the ring feeds with two slots to spare)
+  const int feed = max(1, ((int)w_slots - 2) / n_chunks), want = min(T, feed);
+  int G = 1, n_groups = DF_CWARPS, grp = warp, wg = 0;
+  if (want == 1) G = 6, n_groups = 1, grp = 0, wg = warp;
+  else if (want == 2) G = 3, n_groups = 2, grp = warp / 3, wg = warp - grp * 3;
+  else if (want <= 5) G = 2, n_groups = 3, grp = warp >> 1, wg = warp & 1;
   const bool finisher = wg == 0;
   const unsigned panel = ds_smem(smem + lay.panel_off);
   const int stride = lay.panel_stride;
   const bool two_rows = lay.panel_rows > 8;
-  const unsigned tag16 = df_tag16(args.epoch), tag_out = df_tag32(args.epoch, pi);
+  const unsigned tag16 = args.tag16, tag_out = df_tag32(args.epoch, pi);
   FlowTrack trk;
   trk.m[0] = trk.m[1] = -INFINITY;
   trk.l[0] = trk.l[1] = 0.f;
@@ -688,7 +812,7 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
   // lane's row and k offset inside a 16 x 16 block of A and an 8 x 32 block of W, as ldmatrix wants the addresses
   const unsigned a_lane = two_rows ? (unsigned)((((lane >> 3) & 1) * 8 + (lane & 7)) * stride + (lane >> 4) * 16)
                                    : (unsigned)((lane & 7) * stride + ((lane >> 3) & 1) * 16);
-  const unsigned b_lane = (unsigned)((lane & 7) * lay.w_row + (lane >> 3) * 16);
+  const unsigned b_lane = (unsigned)((lane & 7) * w_row + (lane >> 3) * 16);
   const unsigned w_base = ds_smem(smem + lay.w_off);
   int round = 0;
   for (int t = grp; t < T; t += n_groups, ++round) {
@@ -702,47 +826,70 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
         const int r = g + (i >> 1) * 8, cc = 2 * q + (i & 1);
         res[i] = make_uint2(0u, 0u);
         if (r < M && cc < nc) {
-          if (ph.bias) bias[i] = __ldg(ph.bias + tc0 + cc);
-          if (ph.out_kind == FO_PAIRS) res[i] = df_ld_pair(reinterpret_cast<const uint2*>(ph.out) + (long long)r * N + tc0 + cc);
+          if (bias_p) bias[i] = __ldg(bias_p + tc0 + cc);
+          if (out_kind == FO_PAIRS) res[i] = df_ld_pair(reinterpret_cast<const uint2*>(out_p) + (unsigned)(r * N + tc0 + cc));
         }
       }
     }
     float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
-    unsigned use = wuse + (unsigned)(t * n_chunks);
+    // where the tile's first slot lies in the ring
+    unsigned use = ring.use + (unsigned)(t * n_chunks), slot = ring.slot + (unsigned)(t * n_chunks), turn = ring.turn;
+    while (slot >= w_slots) {
+      slot -= w_slots;
+      ++turn;
+    }
     for (int c = 0; c < n_chunks; ++c, ++use) {
-      const unsigned slot = use % (unsigned)lay.w_slots, turn = use / (unsigned)lay.w_slots;
       // Warps run through the ring at their own pace: a warp may come for a slot a whole turn early, when the slot's
       // barrier still counts the turn before (whose parity it would mistake for its own).  So first the producer must
       // have asked for this very use; then the barrier is in this turn, or past it.
       for (int tries = 0; sh.w_issued <= use; ++tries)
-        if (df_tired(tries, sh, args.status)) {
-          df_give_up(sh, args.status, 3);
+        if (df_tired(tries, sh, status)) {
+          df_give_up(sh, status, 3);
           break;
         }
-      df_mbar_wait(&sh.wfull[slot], turn & 1u, sh, args.status);
-      const unsigned ws = w_base + slot * (unsigned)lay.w_slot_bytes + b_lane;
-      const int kc = min(lay.slot_k, K - c * lay.slot_k), units = (kc + 31) / 32;
-      const unsigned pa0 = panel + a_lane + (unsigned)(c * lay.slot_k) * 2u;
-      for (int u = wg; u < units; u += G) {
-        unsigned b[4];
-        ds_ldmatrix_x4(b, ws + (unsigned)u * 64u);
-        const unsigned pa = pa0 + (unsigned)u * 64u;
+      df_mbar_wait(&sh.wfull[slot], turn & 1u, sh, status);
+      const unsigned ws = w_base + slot * w_slot_bytes + b_lane;
+      const int kc = min(slot_k, K - c * slot_k), units = (kc + 31) >> 5;
+      const unsigned pa0 = panel + a_lane + (unsigned)(c * slot_k) * 2u;
+      // two units of 32 k at a time: their six loads are under way before the first product needs one
+      for (int u = wg; u < units; u += 2 * G) {
+        const bool second = u + G < units;
+        const unsigned o0 = (unsigned)u * 64u, o1 = (unsigned)(second ? u + G : u) * 64u;
+        unsigned b0[4], b1[4];
+        ds_ldmatrix_x4(b0, ws + o0);
+        ds_ldmatrix_x4(b1, ws + o1);
         if (two_rows) {
-          unsigned a0[4], a1[4];
-          ds_ldmatrix_x4(a0, pa);
-          ds_ldmatrix_x4(a1, pa + 32u);
-          ds_mma(acc, a0[0], a0[1], a0[2], a0[3], b[0], b[1]);
-          ds_mma(acc2, a1[0], a1[1], a1[2], a1[3], b[2], b[3]);
+          unsigned a00[4], a01[4], a10[4], a11[4];
+          ds_ldmatrix_x4(a00, pa0 + o0);
+          ds_ldmatrix_x4(a01, pa0 + o0 + 32u);
+          ds_ldmatrix_x4(a10, pa0 + o1);
+          ds_ldmatrix_x4(a11, pa0 + o1 + 32u);
+          ds_mma(acc, a00[0], a00[1], a00[2], a00[3], b0[0], b0[1]);
+          ds_mma(acc2, a01[0], a01[1], a01[2], a01[3], b0[2], b0[3]);
+          if (second) {
+            ds_mma(acc, a10[0], a10[1], a10[2], a10[3], b1[0], b1[1]);
+            ds_mma(acc2, a11[0], a11[1], a11[2], a11[3], b1[2], b1[3]);
+          }
         } else {
-          unsigned a0[2], a1[2];
-          df_ldmatrix_x2(a0, pa);
-          df_ldmatrix_x2(a1, pa + 32u);
-          ds_mma(acc, a0[0], 0u, a0[1], 0u, b[0], b[1]);
-          ds_mma(acc2, a1[0], 0u, a1[1], 0u, b[2], b[3]);
+          unsigned a00[2], a01[2], a10[2], a11[2];
+          df_ldmatrix_x2(a00, pa0 + o0);
+          df_ldmatrix_x2(a01, pa0 + o0 + 32u);
+          df_ldmatrix_x2(a10, pa0 + o1);
+          df_ldmatrix_x2(a11, pa0 + o1 + 32u);
+          ds_mma(acc, a00[0], 0u, a00[1], 0u, b0[0], b0[1]);
+          ds_mma(acc2, a01[0], 0u, a01[1], 0u, b0[2], b0[3]);
+          if (second) {
+            ds_mma(acc, a10[0], 0u, a10[1], 0u, b1[0], b1[1]);
+            ds_mma(acc2, a11[0], 0u, a11[1], 0u, b1[2], b1[3]);
+          }
         }
       }
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;\n" ::"r"(ds_smem(&sh.wempty[slot])), "r"(DF_CWARPS / G) : "memory");
+      if (++slot == w_slots) {
+        slot = 0;
+        ++turn;
+      }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
@@ -769,9 +916,9 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = g + (i >> 1) * 8, cc = 2 * q + (i & 1);
-      const float v = apply_activation(acc[i] + bias[i], ph.act);
+      const float v = df_activation(acc[i] + bias[i], act, out_kind != FO_WORDS);
       acc[i] = v;
-      if (r < M && cc < nc && ph.track) {          // columns come to a thread in rising order: the first maximum stays
+      if (r < M && cc < nc && track_p) {          // columns come to a thread in rising order: the first maximum stays
         float& m = trk.m[i >> 1];
         if (v > m) {
           trk.l[i >> 1] = trk.l[i >> 1] * expf(m - v) + 1.f;
@@ -782,21 +929,21 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
         }
       }
     }
-    if (ph.out_kind == FO_PAIRS) {
+    if (out_kind == FO_PAIRS) {
       // the residual stream: this element was last written by phase res_src (by the thread that holds it in that
       // phase, or by the embedding): wait for its tag, add, write with this phase's tag
-      const unsigned want = df_tag32(args.epoch, ph.res_src);
-      uint2* out = reinterpret_cast<uint2*>(ph.out);
+      const unsigned want = df_tag32(args.epoch, res_src);
+      uint2* out = reinterpret_cast<uint2*>(out_p);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int r = g + (i >> 1) * 8, cc = 2 * q + (i & 1);
         if (r < M && cc < nc) {
           for (int tries = 0; res[i].y != want; ++tries) {
-            if (df_tired(tries, sh, args.status)) {
-              df_give_up(sh, args.status, 3);
+            if (df_tired(tries, sh, status)) {
+              df_give_up(sh, status, 3);
               break;
             }
-            res[i] = df_ld_pair(out + (long long)r * N + tc0 + cc);
+            res[i] = df_ld_pair(out + (unsigned)(r * N + tc0 + cc));
           }
           acc[i] += __uint_as_float(res[i].x);
         }
@@ -808,30 +955,35 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
       const int r = g + h * 8;
       if (r >= M || cc0 >= nc) continue;
       const bool pair_ok = cc0 + 1 < nc;
-      const long long o = (long long)r * N + tc0 + cc0;
-      if (ph.out_kind == FO_WORDS) {
-        unsigned* out = reinterpret_cast<unsigned*>(ph.out) + o;
+      const unsigned o = (unsigned)(r * N + tc0 + cc0);
+      if (out_kind == FO_WORDS) {
+        unsigned* out = reinterpret_cast<unsigned*>(out_p) + o;
         if (pair_ok && (o & 1) == 0) df_st_words2(out, acc[2 * h], acc[2 * h + 1], tag16);
         else {
           df_st_word(out, acc[2 * h], tag16);
           if (pair_ok) df_st_word(out + 1, acc[2 * h + 1], tag16);
         }
-      } else if (ph.out_kind == FO_PAIRS) {
-        uint2* out = reinterpret_cast<uint2*>(ph.out) + o;
+      } else if (out_kind == FO_PAIRS) {
+        uint2* out = reinterpret_cast<uint2*>(out_p) + o;
         if (pair_ok && (o & 1) == 0) df_st_pairs2(out, acc[2 * h], acc[2 * h + 1], tag_out);
         else {
           df_st_pair(out, acc[2 * h], tag_out);
           if (pair_ok) df_st_pair(out + 1, acc[2 * h + 1], tag_out);
         }
       } else {
-        float* out = reinterpret_cast<float*>(ph.out) + o;
+        float* out = reinterpret_cast<float*>(out_p) + o;
         out[0] = acc[2 * h];
         if (pair_ok) out[1] = acc[2 * h + 1];
       }
     }
   }
-  wuse += (unsigned)(T * n_chunks);
-  if (ph.track) {
+  ring.use += (unsigned)(T * n_chunks);
+  ring.slot += (unsigned)(T * n_chunks);
+  while (ring.slot >= w_slots) {
+    ring.slot -= w_slots;
+    ++ring.turn;
+  }
+  if (track_p) {
     // the block's (max, sum, argmax) of every row: the four lanes that share a row, then the warps
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -854,7 +1006,7 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
       float m = sh.trk[0][r][0], l = sh.trk[0][r][1];
       int idx = __float_as_int(sh.trk[0][r][2]);
       for (int w2 = 1; w2 < DF_CWARPS; ++w2) df_track_merge(m, l, idx, sh.trk[w2][r][0], sh.trk[w2][r][1], __float_as_int(sh.trk[w2][r][2]));
-      float* dst = ph.track + ((long long)r * gridDim.x + blockIdx.x) * 4;
+      float* dst = track_p + ((long long)r * gridDim.x + blockIdx.x) * 4;
       dst[0] = m;
       dst[1] = l;
       dst[2] = __int_as_float(idx);
@@ -863,6 +1015,59 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
   }
 }
 
+
+// ---- attention: merging the splits ----
+// The block of split 0 merges the splits of its (sequence, head), in split order, as their tags show up: thread d takes
+// dim d.  Two splits' worth of loads are in flight together.  (A function of its own, not inlined: what it holds in
+// registers is then no burden on the loop over the keys.)
+__device__ __noinline__ void df_attention_merge(const FlowPhase& ph, int pi, const FlowArgs& args, FlowShared& sh) {
+  const int tid = threadIdx.x, hd = ph.head_dim, S = ph.n_splits, H = ph.n_heads, n_mine = sh.work.n;
+  const unsigned tag16 = args.tag16, tag_part = df_tag32(args.epoch, pi);
+  for (int mine = 0; mine < n_mine; ++mine) {
+    const FlowItem it = sh.work.it[mine];
+    if (it.split != 0 || tid >= hd) continue;
+    const long long unit = (long long)it.seq * H + it.head;
+    const uint2* src = ph.part + unit * S * (hd + 2);
+    float Mx = -INFINITY, Lall = 0.f, o = 0.f;
+    for (int s0 = 0; s0 < S; s0 += 2) {
+      uint2 po[2], pm[2], pl[2];
+      unsigned pending = 0;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        if (s0 + j < S) pending |= 1u << j;
+      const unsigned have = pending;
+      for (int tries = 0; pending != 0; ++tries) {
+        if (tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (args.status && df_ld_status(args.status) != 0)))) {
+          df_give_up(sh, args.status, 3);
+          break;
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          if (pending & (1u << j)) {
+            const uint2* one = src + (long long)(s0 + j) * (hd + 2);
+            po[j] = df_ld_pair(one + tid);
+            pm[j] = df_ld_pair(one + hd);
+            pl[j] = df_ld_pair(one + hd + 1);
+          }
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          if ((pending & (1u << j)) && po[j].y == tag_part && pm[j].y == tag_part && pl[j].y == tag_part) pending &= ~(1u << j);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        if (have & (1u << j)) {
+          const float ms = __uint_as_float(pm[j].x);
+          if (ms == -INFINITY) continue;
+          const float mm = fmaxf(Mx, ms);
+          const float a = Mx == -INFINITY ? 0.f : ds_exp2(Mx - mm), b = ds_exp2(ms - mm);
+          Lall = Lall * a + __uint_as_float(pl[j].x) * b;
+          o = o * a + __uint_as_float(po[j].x) * b;
+          Mx = mm;
+        }
+    }
+    df_st_word(ph.attn_out + unit * hd + tid, Lall > 0.f ? o / Lall : 0.f, tag16);
+  }
+}
 
 // ---- attention ---------------------------------------------------------------------------------------------
 // One query per (sequence, head) is row 0 of a 16-row tile (decode_mma.cuh); the pages of the block's items arrive
@@ -877,7 +1082,7 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
   const int hd = ph.head_dim, page_elems = DS_PAGE * hd, cbs = df_col_blocks(hd);
   const int S = ph.n_splits, H = ph.n_heads, group = ph.n_heads / ph.n_kv_heads;
   const float scale_log2 = ph.scale_log2;
-  const unsigned tag16 = df_tag16(args.epoch), tag_part = df_tag32(args.epoch, pi);
+  const unsigned tag16 = args.tag16, tag_part = df_tag32(args.epoch, pi);
   __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(smem + lay.rows_off);      // [items][query, new key, new value][hd]
   float* s_acc = reinterpret_cast<float*>(smem + lay.acc_off);                       // [2][warps][hd]
   if (warp == 0) df_plan(&ph, sh, sh.work);
@@ -930,7 +1135,12 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
     }
   }
   df_bar_consumers();
-  const unsigned base = puse;
+  // where the block's stream of pages stands in the ring (slot = use % slots, turn = use / slots, carried along)
+  const unsigned p_slots = (unsigned)lay.p_slots, p_slot_bytes = (unsigned)lay.p_slot_bytes;
+  unsigned char* const pages = smem + lay.p_off;
+  int* const status = args.status;
+  const bool files = ph.k_off >= 0;
+  unsigned slot = puse % p_slots, turn = puse / p_slots;
   puse += (unsigned)total;
   for (int mine = 0; mine < n_mine; ++mine) {
     const FlowItem it = sh.work.it[mine];
@@ -963,20 +1173,17 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
       for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
     for (int p = 0; p < n_pages; ++p) {
       const int k = k0 + p;
-      const unsigned use = base + (unsigned)k, slot = use % (unsigned)lay.p_slots, turn = use / (unsigned)lay.p_slots;
-      unsigned char* Kt = smem + lay.p_off + (size_t)slot * lay.p_slot_bytes;      // the page's key tiles; its value tiles follow
+      unsigned char* Kt = pages + (size_t)slot * p_slot_bytes;      // the page's key tiles; its value tiles follow
       const unsigned Ks = ds_smem(Kt), Vs = Ks + (unsigned)(cbs * DS_PAGE * 128);
-      bool landed = false;
+      // Every warp waits for every page, with or without a chunk in it: a warp hands a slot back only in the turn it
+      // has seen filled, so that no warp's arrival is counted for the turn before.
+      df_mbar_wait(&sh.pfull[slot], turn & 1u, sh, status);
 #pragma unroll 1
       for (int h = 0; h < CPP; ++h) {
         if ((k * CPP + h) % DF_CWARPS != warp) continue;
         const int key0 = (it.pg_first + p) * DS_PAGE + h * CK;
         if (key0 >= hi || key0 + CK <= lo) continue;
-        if (!landed) {
-          df_mbar_wait(&sh.pfull[slot], turn & 1u, sh, args.status);
-          landed = true;
-        }
-        if (ph.k_off >= 0 && it.L - 1 >= key0 && it.L - 1 < key0 + CK) {
+        if (files && it.L - 1 >= key0 && it.L - 1 < key0 + CK) {
           // the newest key and value are not in their page yet (or only just): they come from the projections.
           // (No other warp touches this chunk's rows; the rows beyond are masked and hold old, finite numbers.)
           const int row = (it.L - 1) % DS_PAGE;
@@ -990,7 +1197,11 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
         ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, scale_log2, m, l, acc, lane);
       }
       __syncwarp();
-      if (lane == 0) df_mbar_arrive(&sh.pempty[slot]);      // (every warp, once per page, with or without a chunk in it)
+      if (lane == 0) df_mbar_arrive(&sh.pempty[slot]);      // (every warp, once per page)
+      if (++slot == p_slots) {
+        slot = 0;
+        ++turn;
+      }
     }
     df_stamp(sh, 2 + min(mine, 5));
     // the four lanes of a row each summed their own keys' weights
@@ -1036,59 +1247,12 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
       }
     }
   }
-  if (S > 1) {
-    // The block of split 0 merges the splits of its (sequence, head), in split order, as their tags show up: thread d
-    // takes dim d.  Four splits' worth of loads are in flight together.
-    for (int mine = 0; mine < n_mine; ++mine) {
-      const FlowItem it = sh.work.it[mine];
-      if (it.split != 0 || tid >= hd) continue;
-      const long long unit = (long long)it.seq * H + it.head;
-      const uint2* src = ph.part + unit * S * (hd + 2);
-      float Mx = -INFINITY, Lall = 0.f, o = 0.f;
-      for (int s0 = 0; s0 < S; s0 += 4) {
-        uint2 po[4], pm[4], pl[4];
-        unsigned pending = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (s0 + j < S) pending |= 1u << j;
-        const unsigned have = pending;
-        for (int tries = 0; pending != 0; ++tries) {
-          if (tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (args.status && df_ld_status(args.status) != 0)))) {
-            df_give_up(sh, args.status, 3);
-            break;
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (pending & (1u << j)) {
-              const uint2* one = src + (long long)(s0 + j) * (hd + 2);
-              po[j] = df_ld_pair(one + tid);
-              pm[j] = df_ld_pair(one + hd);
-              pl[j] = df_ld_pair(one + hd + 1);
-            }
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if ((pending & (1u << j)) && po[j].y == tag_part && pm[j].y == tag_part && pl[j].y == tag_part) pending &= ~(1u << j);
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (have & (1u << j)) {
-            const float ms = __uint_as_float(pm[j].x);
-            if (ms == -INFINITY) continue;
-            const float mm = fmaxf(Mx, ms);
-            const float a = Mx == -INFINITY ? 0.f : ds_exp2(Mx - mm), b = ds_exp2(ms - mm);
-            Lall = Lall * a + __uint_as_float(pl[j].x) * b;
-            o = o * a + __uint_as_float(po[j].x) * b;
-            Mx = mm;
-          }
-      }
-      df_st_word(ph.attn_out + unit * hd + tid, Lall > 0.f ? o / Lall : 0.f, tag16);
-    }
-  }
+  if (S > 1) df_attention_merge(ph, pi, args, sh);
 }
 
 // ---- the kernel --------------------------------------------------------------------------------------------
-// LNJ: rows of up to 128 LNJ channels can be normalised; AI, AT: head sizes up to 32 AI, chunks of 8 AT keys.
-template <int LNJ, int AI, int AT>
+// LNQ: rows of up to 768 LNQ channels can be normalised; AI, AT: head sizes up to 32 AI, chunks of 8 AT keys.
+template <int LNQ, int AI, int AT>
 __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowArgs args) {
   extern __shared__ __align__(128) unsigned char df_smem_raw[];
   __shared__ FlowShared sh;
@@ -1116,7 +1280,7 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowAr
   const FlowLayout& lay = sh.lay;
   // The weight slots and the panel start as zeros: products run over whole blocks of 32 k, and what lies behind a row's
   // K elements must be a number (zero times it is added), never the bits of a NaN.
-  for (long long i = tid; i < (lay.norm_off - lay.w_off) / 16; i += DF_THREADS)
+  for (long long i = tid; i < (lay.rows_off - lay.w_off) / 16; i += DF_THREADS)
     reinterpret_cast<uint4*>(smem + lay.w_off)[i] = make_uint4(0u, 0u, 0u, 0u);
   // the phase list's first attention phase: its lengths and page tables are read once (they do not change during the step)
   int first_attention = -1;
@@ -1157,7 +1321,8 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowAr
     }
   } else {
     // ---- the computing warps ----
-    unsigned wuse = 0, puse = 0;
+    FlowRing ring{0u, 0u, 0u};
+    unsigned puse = 0;
     for (int pi = 0; pi < n_main; ++pi) {
       df_bar_consumers();      // everyone is done with the previous phase: its description, the panel, the partial sums
       if (sh.failed) break;    // (uniform: written before the barrier)
@@ -1189,7 +1354,7 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowAr
           if (!ok && tid == 0 && args.status) atomicCAS(args.status, 0, 4);
         }
       } else if (ph.type == FP_LINEAR) {
-        df_linear_phase<LNJ>(ph, pi, args, lay, smem, sh, wuse);
+        df_linear_phase<LNQ>(ph, pi, args, lay, smem, sh, ring);
       } else if (ph.type == FP_ATTENTION) {
         df_attention_items<AI, AT>(ph, pi, args, lay, smem, sh, puse);
       }
@@ -1269,24 +1434,31 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowAr
 namespace bt {
 
 typedef void (*FlowKernel)(const FlowArgs);
-// The kernel's variants: rows of up to 1024 or 2048 channels to normalise, head sizes up to 64 or 128.
+// The kernel's variants: rows of up to 768, 1536 or 2304 channels to normalise, head sizes up to 64 or 128.
 static FlowKernel df_variant(int max_ln_k, int head_dim, int* index) {
-  const int wide = max_ln_k > 1024 ? 1 : 0, big = head_dim > 64 ? 1 : 0;
-  *index = wide * 2 + big;
-  if (!wide) return big ? decode_flow_kernel<8, 4, 2> : decode_flow_kernel<8, 2, 4>;
-  return big ? decode_flow_kernel<16, 4, 2> : decode_flow_kernel<16, 2, 4>;
+  const int q = max_ln_k <= 768 ? 1 : (max_ln_k <= 1536 ? 2 : 3), big = head_dim > 64 ? 1 : 0;
+  *index = (q - 1) * 2 + big;
+  switch (*index) {
+    case 0: return decode_flow_kernel<1, 2, 4>;
+    case 1: return decode_flow_kernel<1, 4, 2>;
+    case 2: return decode_flow_kernel<2, 2, 4>;
+    case 3: return decode_flow_kernel<2, 4, 2>;
+    case 4: return decode_flow_kernel<3, 2, 4>;
+    default: return decode_flow_kernel<3, 4, 2>;
+  }
 }
 
 }  // namespace bt
 
 extern "C" int bt_decode_flow_phase_bytes() { return (int)sizeof(bt::FlowPhase); }
 
-// Sizes the step's shared memory for these phases (host copy of the program) and `rows` sequences.
+// Sizes the step's shared memory for these phases (host copy of the program, in which it fills col_q, col_r and
+// n_chunks of the linear phases: upload the program after this call) and `rows` sequences.
 // out[0..7] = max_k, max_ln_k, head_dim, w_slots, p_slots, bytes of dynamic shared memory, slot_k, 0.  Returns 0, or
 // non-zero with the library's error text when the step does not fit.
-extern "C" int bt_decode_flow_plan(const void* phases_host, int n_phases, int rows, long long* out) {
+extern "C" int bt_decode_flow_plan(void* phases_host, int n_phases, int rows, long long* out) {
   using namespace bt;
-  const FlowPhase* ph = reinterpret_cast<const FlowPhase*>(phases_host);
+  FlowPhase* ph = reinterpret_cast<FlowPhase*>(phases_host);
   BT_CHECK(n_phases >= 1 && n_phases < 1023, "decode_flow: %d phases are outside 1..1022", n_phases);
   BT_CHECK(rows >= 1 && rows <= 16, "decode_flow: %d rows are outside 1..16", rows);
   int max_k = 32, max_ln_k = 8, head_dim = 0;
@@ -1296,7 +1468,7 @@ extern "C" int bt_decode_flow_plan(const void* phases_host, int n_phases, int ro
       BT_CHECK(ph[i].K % 8 == 0 && ph[i].K >= 8, "decode_flow: K=%d is no multiple of 8", ph[i].K);
       if (ph[i].K > max_k) max_k = ph[i].K;
       if (ph[i].a_kind == FA_LAYERNORM) {
-        BT_CHECK(ph[i].K <= 16 * 128, "decode_flow: a LayerNorm over %d channels exceeds the 2048 a warp holds", ph[i].K);
+        BT_CHECK(ph[i].K <= 3 * 768, "decode_flow: a LayerNorm over %d channels exceeds the 2304 the step holds", ph[i].K);
         if (ph[i].K > max_ln_k) max_ln_k = ph[i].K;
       }
     } else if (ph[i].type == FP_ATTENTION) {
@@ -1319,24 +1491,39 @@ extern "C" int bt_decode_flow_plan(const void* phases_host, int n_phases, int ro
       slot_k = c;
     }
   }
+  // what the kernel would otherwise divide out in every phase
+  const int n_blocks = sm_count();
+  BT_CHECK(n_blocks > 0, "decode_flow: cannot read the number of multiprocessors of the current device");
+  for (int i = 0; i < n_phases; ++i)
+    if (ph[i].type == FP_LINEAR) {
+      ph[i].col_q = ph[i].N / n_blocks;
+      ph[i].col_r = ph[i].N % n_blocks;
+      ph[i].n_chunks = (ph[i].K + slot_k - 1) / slot_k;
+    }
   int variant = 0;
   FlowKernel kernel = df_variant(max_ln_k, head_dim, &variant);
   cudaFuncAttributes attr;
   cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
   BT_CHECK(e == cudaSuccess, "decode_flow: cannot read the kernel's attributes: %s", cudaGetErrorString(e));
-  const long long budget = 227 * 1024 - (long long)attr.sharedSizeBytes - 64;
-  // page slots: about 64 KB of them (at least 2, at most 8); weight slots: what is left (at least 4)
-  int p_slots = 0;
-  if (head_dim > 0) {
-    p_slots = 64 * 1024 / df_page_slot_bytes(head_dim);
-    p_slots = p_slots < 2 ? 2 : (p_slots > 8 ? 8 : p_slots);
-  }
-  int w_slots = 0;
-  for (;;) {
-    const FlowLayout fixed = df_layout(rows, max_k, max_ln_k, head_dim, 0, p_slots, slot_k);
-    w_slots = (int)((budget - fixed.total) / fixed.w_slot_bytes);
-    if (w_slots >= 4 || p_slots <= 2) break;
-    --p_slots;
+  // Two sizes of shared memory are tried.  195 KB leaves the multiprocessor some 60 KB of first-level cache, where the
+  // few registers the compiler spills stay close; if that leaves the weights' ring fewer than 5 slots, everything the
+  // block may have (227 KB) is taken, and spilled registers live in the second-level cache.
+  // page slots: about 48 KB of them (at least 2, at most 8); weight slots: what is left (at least 4)
+  int p_slots = 0, w_slots = 0;
+  for (int kb = 195; kb <= 227; kb += 32) {
+    const long long budget = (long long)kb * 1024 - (long long)attr.sharedSizeBytes - 1024 - 64;
+    p_slots = 0;
+    if (head_dim > 0) {
+      p_slots = 48 * 1024 / df_page_slot_bytes(head_dim);
+      p_slots = p_slots < 2 ? 2 : (p_slots > 8 ? 8 : p_slots);
+    }
+    for (;;) {
+      const FlowLayout fixed = df_layout(rows, max_k, max_ln_k, head_dim, 0, p_slots, slot_k);
+      w_slots = (int)((budget - fixed.total) / fixed.w_slot_bytes);
+      if (w_slots >= 4 || p_slots <= 2) break;
+      --p_slots;
+    }
+    if (w_slots >= 5) break;
   }
   BT_CHECK(w_slots >= 4, "decode_flow: %d rows of K=%d leave no room for the weights' ring in shared memory", rows, max_k);
   if (w_slots > DF_MAX_WSLOTS) w_slots = DF_MAX_WSLOTS;
@@ -1365,7 +1552,7 @@ extern "C" int bt_decode_flow(const void* phases_dev, int n_phases, unsigned epo
   const long long smem_bytes = plan[5];
   int variant = 0;
   FlowKernel kernel = df_variant((int)plan[1], (int)plan[2], &variant);
-  static long long configured[64][4];
+  static long long configured[64][6];
   int dev = 0;
   cudaGetDevice(&dev);
   BT_CHECK(dev >= 0 && dev < 64, "decode_flow: device %d is beyond the 64 this library tracks", dev);
@@ -1377,7 +1564,7 @@ extern "C" int bt_decode_flow(const void* phases_dev, int n_phases, unsigned epo
   cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned), stream);
   BT_CHECK(e == cudaSuccess, "decode_flow: cannot clear the barrier counter: %s", cudaGetErrorString(e));
   FlowArgs args{reinterpret_cast<const FlowPhase*>(phases_dev), n_phases, epoch, counter, status, trace, rows, (int)plan[0],
-                (int)plan[1], (int)plan[2], (int)plan[3], (int)plan[4], (int)plan[6]};
+                (int)plan[1], (int)plan[2], (int)plan[3], (int)plan[4], (int)plan[6], epoch % 65535u + 1u};
   void* kargs[] = {(void*)&args};
   e = cudaLaunchCooperativeKernel((const void*)kernel, dim3(n_sms), dim3(DF_THREADS), kargs, (size_t)smem_bytes, stream);
   BT_CHECK(e == cudaSuccess, "decode_flow: launch failed: %s", cudaGetErrorString(e));

@@ -44,9 +44,9 @@ class Phase(ctypes.Structure):
     _fields_ = [
         ("type", c_int), ("M", c_int),
         ("a_kind", c_int), ("N", c_int), ("K", c_int), ("act", c_int), ("out_kind", c_int), ("a_src", c_int),
-        ("res_src", c_int), ("pad0_", c_int),
+        ("res_src", c_int), ("col_q", c_int),
         ("a", c_void_p), ("rows", c_void_p), ("gamma", c_void_p), ("beta", c_void_p),
-        ("eps", c_float), ("pad1_", c_int),
+        ("eps", c_float), ("col_r", c_int),
         ("w", c_void_p), ("bias", c_void_p), ("out", c_void_p), ("track", c_void_p),
         ("q", c_void_p), ("q_stride", c_longlong), ("k_off", c_int), ("v_off", c_int),
         ("k_pool", c_void_p), ("v_pool", c_void_p), ("table", c_void_p),
@@ -62,7 +62,7 @@ class Phase(ctypes.Structure):
         ("temperature", c_float), ("top_k", c_int), ("top_p", c_float), ("min_p", c_float),
         ("seeds", c_void_p), ("counters", c_void_p), ("out_ids", c_void_p), ("out_logp", c_void_p),
         ("adv_tokens", c_void_p), ("adv_positions", c_void_p), ("adv_past", c_void_p), ("adv_ctx", c_void_p),
-        ("partials", c_void_p), ("n_partials", c_int), ("pad2_", c_int),
+        ("partials", c_void_p), ("n_partials", c_int), ("n_chunks", c_int),
         ("pad3_", ctypes.c_ubyte * 8),                                    # the tensor maps lie on a 64-byte boundary
         ("k_map", ctypes.c_ubyte * 128), ("v_map", ctypes.c_ubyte * 128),
     ]
@@ -230,12 +230,13 @@ class DecodeProgram:
     # ---- running ---------------------------------------------------------------------------------------
     def finalize(self):
         array = (Phase * len(self.phases))(*self.phases)
-        host = torch.frombuffer(bytearray(bytes(array)), dtype=torch.uint8)
-        self.dev = host.to(self.device)
         plan = (c_longlong * 8)()
+        # (the plan also writes into the phases what the kernel would otherwise divide out: upload after it)
         if kernels.library().bt_decode_flow_plan(ctypes.cast(array, c_void_p), c_int(len(self.phases)),
                                                  c_int(self.n_rows), plan) != 0:
             raise ProgramUnsupported(kernels.library().bt_last_error().decode(errors="replace"))
+        host = torch.frombuffer(bytearray(bytes(array)), dtype=torch.uint8)
+        self.dev = host.to(self.device)
         self.plan = plan
         self.smem = int(plan[5])
 
