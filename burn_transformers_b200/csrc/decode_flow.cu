@@ -533,7 +533,7 @@ __device__ __forceinline__ void df_layernorm_rows(const FlowPhase& ph, const Flo
     // e[r][i][c]: value and tag of channel 4 qd[i] + c of row r0 + r; the loads' own registers hold the rows
     uint2 e[RP][Q][4];
     unsigned src[RP];          // where each row begins, in pairs
-    unsigned pending = 0;
+    unsigned mine = 0;
 #pragma unroll
     for (int r = 0; r < RP; ++r) {
       const int row = r0 + r;
@@ -542,30 +542,30 @@ __device__ __forceinline__ void df_layernorm_rows(const FlowPhase& ph, const Flo
       for (int i = 0; i < Q; ++i) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) e[r][i][c] = make_uint2(0u, tag);
-        if (row < M && (has & (1u << i))) pending |= 1u << (r * Q + i);
+        if (row < M && (has & (1u << i))) mine |= 1u << (r * Q + i);
       }
     }
-    const unsigned mine = pending;
-    for (int tries = 0; pending != 0; ++tries) {
+    // All loads of a round in flight together; a round whose tags are not all there is loaded again as a whole
+    // (the rows arrive within a fraction of a microsecond of one another: there is little to gain from finer books).
+    for (int tries = 0;; ++tries) {
+#pragma unroll
+      for (int r = 0; r < RP; ++r)
+#pragma unroll
+        for (int i = 0; i < Q; ++i)
+          if (mine & (1u << (r * Q + i))) {
+            df_ld_pairs2(x + (src[r] + (unsigned)(qd[i] * 4)), e[r][i][0], e[r][i][1]);
+            df_ld_pairs2(x + (src[r] + (unsigned)(qd[i] * 4 + 2)), e[r][i][2], e[r][i][3]);
+          }
+      unsigned stale = 0;
+#pragma unroll
+      for (int r = 0; r < RP; ++r)
+#pragma unroll
+        for (int i = 0; i < Q; ++i) stale |= (e[r][i][0].y ^ tag) | (e[r][i][1].y ^ tag) | (e[r][i][2].y ^ tag) | (e[r][i][3].y ^ tag);
+      if (stale == 0u) break;
       if (df_tired(tries, sh, args.status)) {
         df_give_up(sh, args.status, 3);
         break;
       }
-      // all loads of a round in flight together; a round loads what is still pending
-#pragma unroll
-      for (int r = 0; r < RP; ++r)
-#pragma unroll
-        for (int i = 0; i < Q; ++i)
-          if (pending & (1u << (r * Q + i))) {
-            df_ld_pairs2(x + (src[r] + (unsigned)(qd[i] * 4)), e[r][i][0], e[r][i][1]);
-            df_ld_pairs2(x + (src[r] + (unsigned)(qd[i] * 4 + 2)), e[r][i][2], e[r][i][3]);
-          }
-#pragma unroll
-      for (int r = 0; r < RP; ++r)
-#pragma unroll
-        for (int i = 0; i < Q; ++i)
-          if (((e[r][i][0].y ^ tag) | (e[r][i][1].y ^ tag) | (e[r][i][2].y ^ tag) | (e[r][i][3].y ^ tag)) == 0u)
-            pending &= ~(1u << (r * Q + i));
     }
     // the warp's sum of every row (what a lane does not hold is zero)
     float part[RP];
@@ -651,37 +651,38 @@ __device__ __forceinline__ void df_panel_from_words(const FlowPhase& ph, const F
   for (int i0 = 0; i0 < items; i0 += B) {
     const int r0 = i0 / per_row, j0 = i0 - r0 * per_row;
     uint4 v[B];
-    unsigned pending = 0;
+    unsigned mine = 0;
     {
       int r = r0, jq = j0;
 #pragma unroll
       for (int j = 0; j < B; ++j) {
-        if (r < M && tid + jq * DF_CONSUMERS < qpr) pending |= 1u << j;
+        v[j] = make_uint4(tags, tags, tags, tags);
+        if (r < M && tid + jq * DF_CONSUMERS < qpr) mine |= 1u << j;
         if (++jq == per_row) {
           jq = 0;
           ++r;
         }
       }
     }
-    const unsigned mine = pending;
-    for (int tries = 0; pending != 0; ++tries) {
-      if (df_tired(tries, sh, args.status)) {
-        df_give_up(sh, args.status, 3);
-        break;
-      }
+    // (a round whose tags are not all there is loaded again as a whole)
+    for (int tries = 0;; ++tries) {
       int r = r0, jq = j0;
 #pragma unroll
       for (int j = 0; j < B; ++j) {
-        if (pending & (1u << j)) v[j] = df_ld_words4(a + (unsigned)(r * K + (tid + jq * DF_CONSUMERS) * 4));
+        if (mine & (1u << j)) v[j] = df_ld_words4(a + (unsigned)(r * K + (tid + jq * DF_CONSUMERS) * 4));
         if (++jq == per_row) {
           jq = 0;
           ++r;
         }
       }
+      unsigned stale = 0;
 #pragma unroll
-      for (int j = 0; j < B; ++j)
-        if ((pending & (1u << j)) && ((((v[j].x ^ tags) | (v[j].y ^ tags) | (v[j].z ^ tags) | (v[j].w ^ tags)) >> 16) == 0u))
-          pending &= ~(1u << j);
+      for (int j = 0; j < B; ++j) stale |= (v[j].x ^ tags) | (v[j].y ^ tags) | (v[j].z ^ tags) | (v[j].w ^ tags);
+      if ((stale >> 16) == 0u) break;
+      if (df_tired(tries, sh, args.status)) {
+        df_give_up(sh, args.status, 3);
+        break;
+      }
     }
     int r = r0, jq = j0;
 #pragma unroll
@@ -1250,6 +1251,58 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
   if (S > 1) df_attention_merge(ph, pi, args, sh);
 }
 
+// Token selection for the rows this block takes (after the grid barrier): greedy from the readout's per-block
+// partials, or the full selection from the logits; the selected id becomes the next step's token.  A function of its
+// own: it runs once a step, and its code need not lie among the phases'.
+__device__ __noinline__ void df_select(const FlowArgs& args, FlowShared& sh) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const FlowPhase* ph = args.phases + args.n_phases - 1;
+  if (sh.ok) {
+    for (int r = blockIdx.x; r < ph->M; r += gridDim.x) {
+      if (!ph->do_sample && ph->partials) {
+        // greedy: the readout left every block's (max, sum, argmax) of the row; a warp merges them
+        if (warp == 0) {
+          float m = -INFINITY, l = 0.f;
+          int idx = 0x7fffffff;
+          for (int b = lane; b < ph->n_partials; b += 32) {
+            const float4 p = __ldcg(reinterpret_cast<const float4*>(ph->partials + ((long long)r * ph->n_partials + b) * 4));
+            df_track_merge(m, l, idx, p.x, p.y, __float_as_int(p.z));
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+            const float l2 = __shfl_xor_sync(0xffffffffu, l, o);
+            const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+            df_track_merge(m, l, idx, m2, l2, i2);
+          }
+          if (lane == 0) {
+            ph->out_ids[r] = idx;
+            ph->out_logp[r] = -logf(l);
+            ph->adv_tokens[r] = idx;
+            ph->adv_positions[r] += 1;
+            ph->adv_past[r] += 1;
+            ph->adv_ctx[r] += 1;
+            ph->counters[r] += 1;
+          }
+        }
+        continue;
+      }
+      float u = 0.f;
+      if (ph->do_sample) u = stream_uniform(ph->seeds[r], (unsigned long long)ph->counters[r]);
+      select_row<DF_THREADS>(ph->logits + (long long)r * ph->vocab, ph->vocab, ph->do_sample, ph->temperature, ph->top_k,
+                             ph->top_p, ph->min_p, u, ph->out_ids + r, ph->out_logp + r, sh.sample);
+      __syncthreads();
+      if (tid == 0) {      // the selected id becomes the next step's token; the sequence moves on by one
+        ph->adv_tokens[r] = ph->out_ids[r];
+        ph->adv_positions[r] += 1;
+        ph->adv_past[r] += 1;
+        ph->adv_ctx[r] += 1;
+        ph->counters[r] += 1;
+      }
+    }
+  }
+}
+
 // ---- the kernel --------------------------------------------------------------------------------------------
 // LNQ: rows of up to 768 LNQ channels can be normalised; AI, AT: head sizes up to 32 AI, chunks of 8 AT keys.
 template <int LNQ, int AI, int AT>
@@ -1381,51 +1434,7 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowAr
       sh.ok = ok;
     }
     __syncthreads();
-    const FlowPhase* ph = args.phases + args.n_phases - 1;
-    if (sh.ok) {
-      for (int r = blockIdx.x; r < ph->M; r += gridDim.x) {
-        if (!ph->do_sample && ph->partials) {
-          // greedy: the readout left every block's (max, sum, argmax) of the row; a warp merges them
-          if (warp == 0) {
-            float m = -INFINITY, l = 0.f;
-            int idx = 0x7fffffff;
-            for (int b = lane; b < ph->n_partials; b += 32) {
-              const float4 p = __ldcg(reinterpret_cast<const float4*>(ph->partials + ((long long)r * ph->n_partials + b) * 4));
-              df_track_merge(m, l, idx, p.x, p.y, __float_as_int(p.z));
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-              const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
-              const float l2 = __shfl_xor_sync(0xffffffffu, l, o);
-              const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
-              df_track_merge(m, l, idx, m2, l2, i2);
-            }
-            if (lane == 0) {
-              ph->out_ids[r] = idx;
-              ph->out_logp[r] = -logf(l);
-              ph->adv_tokens[r] = idx;
-              ph->adv_positions[r] += 1;
-              ph->adv_past[r] += 1;
-              ph->adv_ctx[r] += 1;
-              ph->counters[r] += 1;
-            }
-          }
-          continue;
-        }
-        float u = 0.f;
-        if (ph->do_sample) u = stream_uniform(ph->seeds[r], (unsigned long long)ph->counters[r]);
-        select_row<DF_THREADS>(ph->logits + (long long)r * ph->vocab, ph->vocab, ph->do_sample, ph->temperature, ph->top_k,
-                               ph->top_p, ph->min_p, u, ph->out_ids + r, ph->out_logp + r, sh.sample);
-        __syncthreads();
-        if (tid == 0) {      // the selected id becomes the next step's token; the sequence moves on by one
-          ph->adv_tokens[r] = ph->out_ids[r];
-          ph->adv_positions[r] += 1;
-          ph->adv_past[r] += 1;
-          ph->adv_ctx[r] += 1;
-          ph->counters[r] += 1;
-        }
-      }
-    }
+    df_select(args, sh);
   }
 }
 
