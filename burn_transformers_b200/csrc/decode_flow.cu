@@ -169,7 +169,7 @@ __device__ __forceinline__ int df_ld_status(const int* status) {
 struct FlowLayout {
   int w_slots, p_slots, p_slot_bytes;
   int slot_k, w_row, w_slot_bytes;       // k extent of a weight slot, bytes between its 8 rows (16 apart modulo 128: no bank conflicts), its size
-  int panel_rows, panel_stride;          // rows of the panel (8 or 16) and bytes between them
+  int panel_rows, panel_stride;          // rows of the panel (9 or 16) and bytes between them
   long long w_off, p_off, panel_off, rows_off, acc_off, total;
 };
 __host__ __device__ inline int df_kpad(int K) { return (K + 31) / 32 * 32; }
@@ -185,7 +185,7 @@ __host__ __device__ inline FlowLayout df_layout(int rows, int max_k, int max_ln_
   L.w_slots = w_slots;
   L.p_slots = p_slots;
   L.p_slot_bytes = head_dim > 0 ? df_page_slot_bytes(head_dim) : 0;
-  L.panel_rows = rows > 8 ? 16 : 8;
+  L.panel_rows = rows > 8 ? 16 : 9;              // (up to 8 rows: a ninth row of zeros stands for the tile's rows 8 to 15)
   L.panel_stride = df_kpad(max_k) * 2 + 16;
   long long at = 0;
   L.p_off = at;                                  // page slots first: the swizzle pattern wants 1024-byte boundaries
@@ -296,19 +296,23 @@ __device__ __forceinline__ void df_prefetch_l2(const void* p) { asm volatile("pr
 
 // ---- the producers ---------------------------------------------------------------------------------------
 // The weight producer: one warp that walks the phases and, for every linear phase, sends the block's tiles through the
-// ring: tile after tile, slot_k of k at a time, 8 rows (output columns) per slot; lane r copies row r.
-// Returns how many slots it filled.
+// ring: tile after tile, slot_k of k at a time, 8 rows (output columns) per slot.  Four slots are filled at a time: the
+// lanes 8 j .. 8 j + 7 wait for the j-th of them to be handed back and copy its 8 rows (one instruction stream would
+// not keep up with the readout, which takes a slot every few hundred cycles).  Returns how many slots it filled.
 __device__ unsigned df_weight_producer(const FlowArgs& args, int n_phases, const FlowLayout& lay, unsigned char* smem, FlowShared& sh) {
-  const int lane = threadIdx.x & 31;
-  unsigned use = 0;
-  unsigned slot = 0, turn = 0;
+  const int lane = threadIdx.x & 31, grp = lane >> 3, row = lane & 7;
+  const unsigned w_slots = (unsigned)lay.w_slots, w_slot_bytes = (unsigned)lay.w_slot_bytes;
+  const int slot_k = lay.slot_k;
+  const unsigned w_base = ds_smem(smem + lay.w_off) + (unsigned)(row * lay.w_row);
+  int* const status = args.status;
+  unsigned use = 0, base_slot = 0, base_turn = 0;      // of the next slot to fill (slot = use % slots, turn = use / slots)
   for (int pi = 0; pi < n_phases && !sh.failed; ++pi) {
     const FlowPhase* ph = args.phases + pi;
     if (ph->type != FP_LINEAR) continue;
-    const int N = ph->N, K = ph->K;
+    const int K = ph->K, n_chunks = ph->n_chunks;
+    const __nv_bfloat16* const w = ph->w;
     int c0, c1;
     df_columns(ph, c0, c1);
-    const int n_chunks = ph->n_chunks;
     // What the phase's computing warps will read from plain memory, on its way into the L2 cache: the block's bias
     // values, and (one block for all) the norm's parameters.
     if (ph->bias && c0 + lane * 32 < c1) df_prefetch_l2(ph->bias + c0 + lane * 32);
@@ -317,27 +321,46 @@ __device__ unsigned df_weight_producer(const FlowArgs& args, int n_phases, const
         df_prefetch_l2(ph->gamma + k);
         if (ph->beta) df_prefetch_l2(ph->beta + k);
       }
-    for (int t0 = c0; t0 < c1 && !sh.failed; t0 += 8) {
-      const int rows_here = min(8, c1 - t0);
-      const __nv_bfloat16* src = ph->w + (long long)(t0 + lane) * K;
-      for (int c = 0; c < n_chunks; ++c, ++use) {
-        if (turn > 0 && !df_mbar_wait(&sh.wempty[slot], (turn - 1) & 1u, sh, args.status)) return use;
-        const int kc = min(lay.slot_k, K - c * lay.slot_k);
-        const unsigned bytes = (unsigned)kc * 2u;
-        const unsigned dst = ds_smem(smem + lay.w_off) + slot * (unsigned)lay.w_slot_bytes + (unsigned)(lane * lay.w_row);
-        const unsigned bar = ds_smem(&sh.wfull[slot]);
-        if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes * (unsigned)rows_here) : "memory");
-        __syncwarp();
-        if (lane < rows_here)
-          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
-                       "l"(src + (long long)c * lay.slot_k), "r"(bytes), "r"(bar)
+    const int total = ((c1 - c0 + 7) >> 3) * n_chunks;      // slots of this phase
+    int t = 0, c = grp;                                     // this group's tile and piece of k
+    while (c >= n_chunks) {
+      c -= n_chunks;
+      ++t;
+    }
+    for (int f0 = 0; f0 < total && !sh.failed; f0 += 4) {
+      const bool active = f0 + grp < total;
+      unsigned slot = base_slot + (unsigned)grp, turn = base_turn;
+      if (slot >= w_slots) {
+        slot -= w_slots;
+        ++turn;
+      }
+      // (every group goes on as soon as its own slot is free: the first of the four need not wait for the last)
+      bool ok = true;
+      if (active && turn > 0) ok = df_mbar_wait(&sh.wempty[slot], (turn - 1) & 1u, sh, status);
+      if (active && ok) {
+        const int t0 = c0 + 8 * t, rows_here = min(8, c1 - t0), kc = min(slot_k, K - c * slot_k);
+        const unsigned bytes = (unsigned)kc * 2u, bar = ds_smem(&sh.wfull[slot]);
+        if (row == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes * (unsigned)rows_here) : "memory");
+        if (row < rows_here)
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                           w_base + slot * w_slot_bytes),
+                       "l"(w + ((long long)(t0 + row) * K + (long long)c * slot_k)), "r"(bytes), "r"(bar)
                        : "memory");
-        __syncwarp();
-        if (lane == 0) sh.w_issued = use + 1;
-        if (++slot == (unsigned)lay.w_slots) {
-          slot = 0;
-          ++turn;
-        }
+      }
+      if (!__all_sync(0xffffffffu, ok)) return use;
+      const unsigned n_done = (unsigned)min(4, total - f0);
+      use += n_done;
+      base_slot += n_done;
+      if (base_slot >= w_slots) {
+        base_slot -= w_slots;
+        ++base_turn;
+      }
+      __syncwarp();
+      if (lane == 0) sh.w_issued = use;
+      c += 4;
+      while (c >= n_chunks) {
+        c -= n_chunks;
+        ++t;
       }
     }
   }
@@ -801,22 +824,23 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
   if (want == 1) G = 6, n_groups = 1, grp = 0, wg = warp;
   else if (want == 2) G = 3, n_groups = 2, grp = warp / 3, wg = warp - grp * 3;
   else if (want <= 5) G = 2, n_groups = 3, grp = warp >> 1, wg = warp & 1;
-  const bool finisher = wg == 0;
   const unsigned panel = ds_smem(smem + lay.panel_off);
   const int stride = lay.panel_stride;
-  const bool two_rows = lay.panel_rows > 8;
+  const bool two_rows = lay.panel_rows > 9;
   const unsigned tag16 = args.tag16, tag_out = df_tag32(args.epoch, pi);
   FlowTrack trk;
   trk.m[0] = trk.m[1] = -INFINITY;
   trk.l[0] = trk.l[1] = 0.f;
   trk.idx[0] = trk.idx[1] = 0x7fffffff;
   // lane's row and k offset inside a 16 x 16 block of A and an 8 x 32 block of W, as ldmatrix wants the addresses
-  const unsigned a_lane = two_rows ? (unsigned)((((lane >> 3) & 1) * 8 + (lane & 7)) * stride + (lane >> 4) * 16)
-                                   : (unsigned)((lane & 7) * stride + ((lane >> 3) & 1) * 16);
+  // (a panel of up to 8 rows: the lanes that address the tile's rows 8 to 15 all name the panel's row of zeros)
+  const unsigned a_lane = (unsigned)((((lane >> 3) & 1) ? (two_rows ? 8 + (lane & 7) : 8) : (lane & 7)) * stride + (lane >> 4) * 16);
   const unsigned b_lane = (unsigned)((lane & 7) * w_row + (lane >> 3) * 16);
   const unsigned w_base = ds_smem(smem + lay.w_off);
   int round = 0;
-  for (int t = grp; t < T; t += n_groups, ++round) {
+  int fin = 0;                  // which warp of a group finishes its tile: they take turns
+  for (int t = grp; t < T; t += n_groups, ++round, fin = fin + 1 == G ? 0 : fin + 1) {
+    const bool finisher = wg == fin;
     const int tc0 = c0 + t * 8, nc = min(8, c1 - tc0);
     // the finishing warp's bias and residual travel while the products run
     float bias[4] = {0.f, 0.f, 0.f, 0.f};
@@ -859,30 +883,16 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
         unsigned b0[4], b1[4];
         ds_ldmatrix_x4(b0, ws + o0);
         ds_ldmatrix_x4(b1, ws + o1);
-        if (two_rows) {
-          unsigned a00[4], a01[4], a10[4], a11[4];
-          ds_ldmatrix_x4(a00, pa0 + o0);
-          ds_ldmatrix_x4(a01, pa0 + o0 + 32u);
-          ds_ldmatrix_x4(a10, pa0 + o1);
-          ds_ldmatrix_x4(a11, pa0 + o1 + 32u);
-          ds_mma(acc, a00[0], a00[1], a00[2], a00[3], b0[0], b0[1]);
-          ds_mma(acc2, a01[0], a01[1], a01[2], a01[3], b0[2], b0[3]);
-          if (second) {
-            ds_mma(acc, a10[0], a10[1], a10[2], a10[3], b1[0], b1[1]);
-            ds_mma(acc2, a11[0], a11[1], a11[2], a11[3], b1[2], b1[3]);
-          }
-        } else {
-          unsigned a00[2], a01[2], a10[2], a11[2];
-          df_ldmatrix_x2(a00, pa0 + o0);
-          df_ldmatrix_x2(a01, pa0 + o0 + 32u);
-          df_ldmatrix_x2(a10, pa0 + o1);
-          df_ldmatrix_x2(a11, pa0 + o1 + 32u);
-          ds_mma(acc, a00[0], 0u, a00[1], 0u, b0[0], b0[1]);
-          ds_mma(acc2, a01[0], 0u, a01[1], 0u, b0[2], b0[3]);
-          if (second) {
-            ds_mma(acc, a10[0], 0u, a10[1], 0u, b1[0], b1[1]);
-            ds_mma(acc2, a11[0], 0u, a11[1], 0u, b1[2], b1[3]);
-          }
+        unsigned a00[4], a01[4], a10[4], a11[4];
+        ds_ldmatrix_x4(a00, pa0 + o0);
+        ds_ldmatrix_x4(a01, pa0 + o0 + 32u);
+        ds_ldmatrix_x4(a10, pa0 + o1);
+        ds_ldmatrix_x4(a11, pa0 + o1 + 32u);
+        ds_mma(acc, a00[0], a00[1], a00[2], a00[3], b0[0], b0[1]);
+        ds_mma(acc2, a01[0], a01[1], a01[2], a01[3], b0[2], b0[3]);
+        if (second) {
+          ds_mma(acc, a10[0], a10[1], a10[2], a10[3], b1[0], b1[1]);
+          ds_mma(acc2, a11[0], a11[1], a11[2], a11[3], b1[2], b1[3]);
         }
       }
       __syncwarp();
@@ -899,17 +909,19 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
       *reinterpret_cast<float4*>(red[warp][lane]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
       df_bar_group(2 + grp, G * 32);
       if (finisher) {
-        float4 part[DF_CWARPS - 1];
+        // the group's sums in the order of its warps, whoever finishes
+        float4 part[DF_CWARPS];
 #pragma unroll
-        for (int w2 = 1; w2 < DF_CWARPS; ++w2)
-          if (w2 < G) part[w2 - 1] = *reinterpret_cast<const float4*>(red[warp + w2][lane]);
+        for (int w2 = 0; w2 < DF_CWARPS; ++w2)
+          if (w2 < G) part[w2] = *reinterpret_cast<const float4*>(red[warp - wg + w2][lane]);
+        acc[0] = part[0].x, acc[1] = part[0].y, acc[2] = part[0].z, acc[3] = part[0].w;
 #pragma unroll
         for (int w2 = 1; w2 < DF_CWARPS; ++w2)
           if (w2 < G) {
-            acc[0] += part[w2 - 1].x;
-            acc[1] += part[w2 - 1].y;
-            acc[2] += part[w2 - 1].z;
-            acc[3] += part[w2 - 1].w;
+            acc[0] += part[w2].x;
+            acc[1] += part[w2].y;
+            acc[2] += part[w2].z;
+            acc[3] += part[w2].w;
           }
       }
     }
@@ -922,11 +934,11 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
       if (r < M && cc < nc && track_p) {          // columns come to a thread in rising order: the first maximum stays
         float& m = trk.m[i >> 1];
         if (v > m) {
-          trk.l[i >> 1] = trk.l[i >> 1] * expf(m - v) + 1.f;
+          trk.l[i >> 1] = trk.l[i >> 1] * __expf(m - v) + 1.f;
           m = v;
           trk.idx[i >> 1] = tc0 + cc;
         } else if (m != -INFINITY) {
-          trk.l[i >> 1] += expf(v - m);
+          trk.l[i >> 1] += __expf(v - m);
         }
       }
     }
@@ -1090,49 +1102,32 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
   df_bar_consumers();
   const int n_mine = sh.work.n, total = sh.work.start[n_mine];
   {
-    // every item's query and new key and value: tagged words of the projections, four at a time
-    const int quads = hd / 4, kinds = ph.k_off >= 0 ? 3 : 1, n_loads = n_mine * kinds * quads;
-    for (int i0 = 0; i0 < n_loads; i0 += 2 * DF_CONSUMERS) {
-      uint4 v[2];
-      const unsigned* src[2];
-      unsigned pending = 0;
-#pragma unroll
-      for (int b = 0; b < 2; ++b) {
-        const int i = i0 + b * DF_CONSUMERS + tid;
-        src[b] = ph.q;
-        if (i < n_loads) {
-          const int j = i / (kinds * quads), r = (i / quads) % kinds, c = i % quads;
-          const FlowItem it = sh.work.it[j];
-          const int col = r == 0 ? it.head * hd : (r == 1 ? ph.k_off : ph.v_off) + (it.head / group) * hd;
-          src[b] = ph.q + (long long)it.seq * ph.q_stride + col + c * 4;
-          pending |= 1u << b;
+    // Every item's query and new key and value: tagged words of the projections.  A warp takes one of these rows at
+    // a time, a lane four of its dims; a row whose tags are not all there is loaded again.
+    const int quads = hd >> 2, kinds = ph.k_off >= 0 ? 3 : 1, n_rows = n_mine * kinds;
+    const unsigned tags = tag16 << 16;
+    const unsigned* const proj = ph.q;
+    const int q_stride = (int)ph.q_stride, k_off = ph.k_off, v_off = ph.v_off;
+    for (int pair = warp; pair < n_rows; pair += DF_CWARPS) {
+      const int j = kinds == 3 ? pair / 3 : pair, r = pair - j * kinds;
+      const int seq = sh.work.it[j].seq, head = sh.work.it[j].head;
+      const int col = r == 0 ? head * hd : (r == 1 ? k_off : v_off) + (head / group) * hd;
+      if (lane < quads) {
+        const unsigned* src = proj + (unsigned)(seq * q_stride + col + lane * 4);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        for (int tries = 0;; ++tries) {
+          v = df_ld_words4(src);
+          if ((((v.x ^ tags) | (v.y ^ tags) | (v.z ^ tags) | (v.w ^ tags)) >> 16) == 0u) break;
+          if (df_tired(tries, sh, args.status)) {
+            df_give_up(sh, args.status, 3);
+            break;
+          }
         }
+        uint2 packed;
+        packed.x = __byte_perm(v.x, v.y, 0x5410);
+        packed.y = __byte_perm(v.z, v.w, 0x5410);
+        *reinterpret_cast<uint2*>(rows + (j * 3 + r) * hd + lane * 4) = packed;
       }
-      const unsigned mine = pending;
-      for (int tries = 0; pending != 0; ++tries) {
-        if (tries >= DF_SPIN_LIMIT || ((tries & 1023) == 1023 && (sh.failed || (args.status && df_ld_status(args.status) != 0)))) {
-          df_give_up(sh, args.status, 3);
-          break;
-        }
-#pragma unroll
-        for (int b = 0; b < 2; ++b)
-          if (pending & (1u << b)) v[b] = df_ld_words4(src[b]);
-#pragma unroll
-        for (int b = 0; b < 2; ++b)
-          if ((pending & (1u << b)) && (v[b].x >> 16) == tag16 && (v[b].y >> 16) == tag16 && (v[b].z >> 16) == tag16 &&
-              (v[b].w >> 16) == tag16)
-            pending &= ~(1u << b);
-      }
-#pragma unroll
-      for (int b = 0; b < 2; ++b)
-        if (mine & (1u << b)) {
-          const int i = i0 + b * DF_CONSUMERS + tid;
-          const int j = i / (kinds * quads), r = (i / quads) % kinds, c = i % quads;
-          uint2 packed;
-          packed.x = (v[b].x & 0xffffu) | (v[b].y << 16);
-          packed.y = (v[b].z & 0xffffu) | (v[b].w << 16);
-          *reinterpret_cast<uint2*>(rows + (j * 3 + r) * hd + c * 4) = packed;
-        }
     }
   }
   df_bar_consumers();
