@@ -12,22 +12,33 @@
 //     stream, which phase) wrote it: a bfloat16 value travels as a 32-bit word (value | tag << 16), a 32-bit value
 //     as a 64-bit pair (value, tag).  A word or a pair is written and read by one instruction, so a reader sees
 //     either the old tag or the new value with its tag, never a mix.  A consumer simply loads the rows it needs and
-//     looks at the tags; what is not there yet is loaded again (with a limit: see "waits").  No fence, no counter,
-//     no second trip.  Buffers are zeroed before first use and tags are never zero.
+//     looks at the tags; a round of loads in which a tag is missing is loaded again (with a limit: see "waits").  No
+//     fence, no counter, no second trip.  Buffers are zeroed before first use and tags are never zero.
 //   * Weights and cache pages never change during a step.  Two producer warps of every block walk the phase list
 //     on their own, ahead of the computing warps: one streams the block's weight tiles through a ring of slots in
-//     shared memory (bulk copies, one per 8 x 512 piece of W[N, K]), the other the block's pages of keys and values
-//     (tensor-map copies with the 128-byte swizzle).  The rings are the only coupling: a slot is handed back when
-//     its last reader is done.  The weight stream therefore runs through hand-overs and phases without a pause.
-//   * Matrix products: a phase's output columns are dealt out in tiles of 8 to the blocks; the 8 computing warps of
-//     a block split K (32 elements at a time, round-robin), take A from a shared-memory panel of the (at most 16)
-//     rows and B from the ring, both with ldmatrix, and add their partial sums through shared memory in a fixed
-//     order.  The panel is built once per block and phase from tagged rows: copied, or LayerNorm-ed (32-bit
-//     statistics, two passes over registers).
+//     shared memory (bulk copies, one per row of a tile of 8 output columns and up to 1024 of k; four slots are
+//     filled at a time by four groups of lanes), the other the block's pages of keys and values (tensor-map copies
+//     with the 128-byte swizzle).  The rings are the only coupling: a slot is handed back when its last reader is done.
+//     The weight stream therefore runs through hand-overs and phases without a pause.  The weight producer also sends
+//     what the coming phase reads from plain memory (bias values, norm parameters) on its way into the L2 cache.
+//   * Matrix products: every block takes the same share of a phase's output columns (N / blocks or one more), in
+//     tiles of at most 8.  The six computing warps form groups: G = 6, 3, 2 or 1 warps share a tile and split its k
+//     (32 elements at a time, round-robin), so that 6 / G tiles are in work at a time and no block-wide barrier stands
+//     between tiles.  A and B come from shared memory with ldmatrix (A: a panel of the at most 16 rows, built once per
+//     block and phase from tagged rows: copied, or LayerNorm-ed with all warps on every row, 32-bit statistics in two
+//     passes over registers); a group adds its partial sums through shared memory in the order of its warps, and its
+//     warps take turns at finishing a tile (bias, activation, residual, tags).
 //   * Attention is the tensor-core routine of decode_mma.cuh over the pages in the ring.  With several splits per
 //     (sequence, head) every split leaves a tagged partial result and the block of split 0 merges them, in split
 //     order, as soon as their tags show up: the projection after it reads plain rows.
 //   * Nothing is accumulated with atomics and every sum has a fixed order: results do not depend on timing.
+//
+// Registers and code.  Eight warps a block, so that a thread may hold 255 registers, and the kernel is built so that
+// nothing spills: with most of a multiprocessor's memory taken as shared memory there is little cache for spilled
+// registers, and every spilled access would be a trip to the L2 cache.  What runs once a step (token selection) or
+// rarely (the merge of splits, full-precision activations) is kept out of line, so that the code of a layer's phases
+// stays small enough for the instruction cache.  What a phase needs of its description is read into registers once:
+// the description lies in shared memory, and every wait in between would have the compiler read it again.
 //
 // The one place where the step still meets at a grid barrier is before token selection, which reads the plain
 // 32-bit logits (they are also the step's result for the host) or the readout's per-block partials.
@@ -43,8 +54,6 @@
 
 namespace bt {
 
-// Eight warps a block, so that a thread may hold 255 registers: with nearly all of a multiprocessor's memory taken as
-// shared memory there is no cache left for spilled registers, and every spilled access would be a trip to the L2 cache.
 constexpr int DF_CWARPS = 6, DF_CONSUMERS = DF_CWARPS * 32;     // warps that compute
 constexpr int DF_THREADS = DF_CONSUMERS + 64;                   // + the weight producer and the page producer
 constexpr int DF_MAX_SLOT_K = 1024;              // largest k extent of a weight slot
