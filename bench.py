@@ -1,10 +1,14 @@
-"""Decode and prefill throughput of GPT-2 small (random weights, synthetic tokens) on one B200.
+"""Decode and prefill throughput of GPT-2 (random weights, synthetic tokens) on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--points all|small] [--profile]
 
-A step is one decode step of a batch of 8 sequences.  The run prints one JSON line: `value` is decoded
-tokens per second, timed on the device with CUDA events over exactly K steps; `e2e` is the same through the
-public generate entry point with host tokens in and out; `prefill`, `roofline` and `points` explain it.
+A step is one decode step of a batch of 8 sequences of GPT-2 small.  The run prints one JSON line: `value` is decoded
+tokens per second, timed on the device with CUDA events over exactly K steps; `e2e` is the same through the public
+generate entry point with host tokens in and out; `prefill`, `roofline` and `points` explain it.  `points` holds the
+other workloads (GPT-2 small at batch 1 and 64, GPT-2 medium with 8 prompts of unequal lengths, GPT-2 XL at batch 64
+with its cache for 64 x 1,024 positions resident), each measured as 10 repetitions after 3 unmeasured ones, the cache
+state made anew for every repetition, with median, 95th percentile, minimum and maximum and a roofline fraction.
+`--profile` prints, instead, where a prefill and a decode step spend their time, kernel by kernel.
 """
 from __future__ import annotations
 
@@ -23,6 +27,7 @@ sys.path.insert(0, str(ROOT))
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 CONTEXT = 1024
 PREFILL_TOKENS = 2048
+REPETITIONS, WARM_REPETITIONS = 10, 3
 
 
 def peaks():
@@ -77,8 +82,10 @@ class ClockSampler:
                 "samples": len(rows)}
 
 
-def gpt2_small():
-    return dict(model_type="gpt2", n_layer=12, n_embd=768, n_head=12, n_inner=3072, vocab_size=50257,
+def gpt2(size: str) -> dict:
+    sizes = {"small": (12, 768, 12), "medium": (24, 1024, 16), "xl": (48, 1600, 25)}
+    n_layer, n_embd, n_head = sizes[size]
+    return dict(model_type="gpt2", n_layer=n_layer, n_embd=n_embd, n_head=n_head, n_inner=4 * n_embd, vocab_size=50257,
                 n_positions=1024, layer_norm_epsilon=1e-5, activation_function="gelu_new")
 
 
@@ -100,17 +107,22 @@ def prefill_flops(cfg, lengths):
     return gemm + attention + 2 * len(lengths) * d * V
 
 
-def decode_points(engine, cfg, batch, prompt_len, steps, warmup, torch, bt, rng):
-    """`warmup` + `steps` decode steps of `batch` sequences after a prefill of `prompt_len` tokens each: every
-    step is one replay of the recorded forward + greedy selection + advance, the selected tokens being fed
-    forward on the device.  Returns (ms per step on the device, kernels launched in the timed region, mean
-    context of the timed steps)."""
+def make_engine(cfg, bt, torch, *, max_tokens, max_slots, fast_weights=False):
+    """An engine with random weights of `cfg` (written as a model folder and loaded like any other).  The large
+    models draw their weights on the device: the host generator would take minutes."""
+    with tempfile.TemporaryDirectory() as folder:
+        bt.write_random_model(folder, cfg, seed=0, storage="bfloat16", device="cuda" if fast_weights else None)
+        return bt.Engine.from_folder(folder, "bfloat16", max_tokens=max_tokens, max_slots=max_slots)
+
+
+def start_decode(engine, cfg, prompts, new_tokens, bt):
+    """Prefills `prompts` and composes the decode step of the batch; returns (graph, slots)."""
     from burn_transformers_b200.engine.graphs import DecodeSession
     from burn_transformers_b200.sampling.sampler import DeviceSampler
     from burn_transformers_b200.sampling.tracker import SequenceTracker
 
-    config = bt.GenerationConfig(max_new_tokens=steps + warmup + 2)
-    prompts = [rng.integers(0, cfg["vocab_size"], prompt_len).tolist() for _ in range(batch)]
+    batch = len(prompts)
+    config = bt.GenerationConfig(max_new_tokens=new_tokens + 2)
     sampler = DeviceSampler(config, cfg["vocab_size"], engine.device, batch)
     trackers = [SequenceTracker(i, p, config) for i, p in enumerate(prompts)]
     slots = {i: engine.new_sequence() for i in range(batch)}
@@ -119,9 +131,23 @@ def decode_points(engine, cfg, batch, prompt_len, steps, warmup, torch, bt, rng)
         ids, logps = sampler.select(logits, trackers)
         for t, tok, lp in zip(trackers, ids, logps):
             t.push(tok, lp)
-        engine.cache.reserve([(slots[i], prompt_len + steps + warmup + 1) for i in range(batch)])
+        engine.cache.reserve([(slots[i], len(p) + new_tokens + 1) for i, p in enumerate(prompts)])
         session = DecodeSession(engine, config, batch)
-        graph = session._compose(trackers, slots)
+        return session._compose(trackers, slots), slots
+    except BaseException:
+        for s in slots.values():
+            engine.release(s)
+        raise
+
+
+def decode_points(engine, cfg, batch, prompt_len, steps, warmup, torch, bt, rng):
+    """`warmup` + `steps` decode steps of `batch` sequences after a prefill of `prompt_len` tokens each: every
+    step is one replay of the recorded forward + greedy selection + advance, the selected tokens being fed
+    forward on the device.  Returns (ms per step on the device, kernels launched in the timed region, mean
+    context of the timed steps)."""
+    prompts = [rng.integers(0, cfg["vocab_size"], prompt_len).tolist() for _ in range(batch)]
+    graph, slots = start_decode(engine, cfg, prompts, steps + warmup, bt)
+    try:
         for _ in range(warmup):
             graph.run()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -138,6 +164,48 @@ def decode_points(engine, cfg, batch, prompt_len, steps, warmup, torch, bt, rng)
             engine.release(s)
     mean_ctx = prompt_len + warmup + (steps + 1) / 2
     return ms, launches, mean_ctx
+
+
+def spread(samples):
+    """Median, 95th percentile, minimum and maximum of the repetitions."""
+    ordered = sorted(samples)
+    p95 = ordered[min(len(ordered) - 1, int(round(0.95 * (len(ordered) - 1))))]
+    return {"median": statistics.median(ordered), "p95": p95, "min": ordered[0], "max": ordered[-1], "n": len(ordered)}
+
+
+def decode_series(engine, cfg, prompt_lengths, steps, torch, bt, rng, pk):
+    """A decode workload measured as the reference's protocol asks: 3 unmeasured repetitions, then 10 measured
+    ones, each with the cache state made anew (new slots, a new prefill of new random prompts of these lengths) and
+    `steps` decode steps timed on the device.  Returns tokens per second at the median with the spread of ms per
+    step and the fraction of the copy rate: bytes a step has to read (every weight once, the cache of the live
+    requests at the mean context of the timed steps) over its median time."""
+    batch = len(prompt_lengths)
+    samples = []
+    for rep in range(WARM_REPETITIONS + REPETITIONS):
+        prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in prompt_lengths]
+        graph, slots = start_decode(engine, cfg, prompts, steps + 1, bt)
+        try:
+            graph.run()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(steps):
+                graph.run()
+            stop.record()
+            torch.cuda.synchronize()
+            if rep >= WARM_REPETITIONS:
+                samples.append(start.elapsed_time(stop) / steps)
+        finally:
+            for s in slots.values():
+                engine.release(s)
+    stats = spread(samples)
+    mean_ctx = sum(prompt_lengths) / batch + 1 + (steps + 1) / 2
+    step_bytes = weight_bytes(cfg) + batch * mean_ctx * kv_bytes_per_token(cfg)
+    achieved = step_bytes / (stats["median"] * 1e-3) / 1e9
+    return {"tokens_per_s": batch / stats["median"] * 1e3, "ms_per_step": stats, "batch": batch, "steps": steps,
+            "mean_context": mean_ctx,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / pk["hbm_gbs"], "of": pk["source"]}}
 
 
 def e2e_decode(engine, cfg, batch, prompt_len, new_tokens, torch, bt, rng):
@@ -158,6 +226,117 @@ def e2e_decode(engine, cfg, batch, prompt_len, new_tokens, torch, bt, rng):
     return batch * (len(stamps) - 1) / seconds
 
 
+def timed_prefill(engine, prompts, torch, bt):
+    """Median device time (ms) of the prompts' step over 10 repetitions after 3 unmeasured ones (the first two build
+    the kernels' state and record the shape; the rest replay it), slots released and taken anew in between."""
+    times = []
+    for rep in range(WARM_REPETITIONS + REPETITIONS):
+        slots = [engine.new_sequence() for _ in prompts]
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        engine.step([bt.StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        b.record()
+        torch.cuda.synchronize()
+        if rep >= WARM_REPETITIONS:
+            times.append(a.elapsed_time(b))
+        for s in slots:
+            engine.release(s)
+    return spread(times)
+
+
+def run_profile(args, torch, bt, kernels, pk):
+    """Where a prefill of 2 x 1,024 tokens and decode steps at batch 8 and 64 spend their time (GPT-2 small): every
+    kernel between two CUDA events, launched directly (no recorded graph, so gaps between launches are not in the
+    figures), with the rate each kernel class achieved; the fused decode step by its own timeline of block 0."""
+    import numpy as np
+    cfg = gpt2("small")
+    rng = np.random.default_rng(0)
+    engine = make_engine(cfg, bt, torch, max_tokens=64 * CONTEXT, max_slots=64)
+    d, L = cfg["n_embd"], cfg["n_layer"]
+    report = {"profile": True, "peaks": pk}
+
+    def table(rows, attention_flops=0.0, attention_bytes=0.0, steps=1):
+        out = []
+        for row in rows:
+            if row["kernel"].startswith("attention"):
+                row["flops"], row["bytes"] = attention_flops, attention_bytes
+                seconds = row["ms"] * 1e-3
+                row["tflops"] = attention_flops / seconds / 1e12 if attention_flops else None
+                row["gbs"] = attention_bytes / seconds / 1e9 if attention_bytes else None
+            out.append({"kernel": row["kernel"], "launches": row["launches"] // steps, "us": round(row["ms"] * 1e3 / steps, 2),
+                        "share": round(row["share"], 4),
+                        "tflops": None if row["tflops"] is None else round(row["tflops"], 1),
+                        "frac_of_bf16_peak": None if row["tflops"] is None else round(row["tflops"] / pk["bf16_tflops"], 4),
+                        "gbs": None if row["gbs"] is None else round(row["gbs"], 1),
+                        "frac_of_copy_rate": None if row["gbs"] is None else round(row["gbs"] / pk["hbm_gbs"], 4)})
+        return out
+
+    # prefill, launched kernel by kernel (a shape is recorded as a graph from its third occurrence: use new shapes)
+    lengths = [PREFILL_TOKENS // 2] * 2
+    for warm in range(2):
+        prompts = [rng.integers(0, cfg["vocab_size"], n - warm).tolist() for n in lengths]
+        slots = [engine.new_sequence() for _ in prompts]
+        with kernels.KernelProfile() as prof:
+            engine.step([bt.StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        rows = prof.summary()
+        for s in slots:
+            engine.release(s)
+    report["prefill_2x1024"] = table(rows, attention_flops=sum(L * 2 * s * s * d for s in lengths))
+    # decode steps as separate kernels
+    engine.use_fused_step = False
+    for batch in (8, 64):
+        prompts = [rng.integers(0, cfg["vocab_size"], 512).tolist() for _ in range(batch)]
+        graph, slots = start_decode(engine, cfg, prompts, 40, bt)
+        try:
+            for _ in range(3):
+                graph._issue()
+            steps = 8
+            with kernels.KernelProfile() as prof:
+                for _ in range(steps):
+                    graph._issue()
+            rows = prof.summary()
+        finally:
+            for s in slots.values():
+                engine.release(s)
+        kv = batch * 520 * kv_bytes_per_token(cfg) * steps
+        report[f"decode_b{batch}_separate_kernels"] = table(rows, attention_bytes=kv, steps=steps)
+    # the fused decode step: block 0's timeline, by kind of phase
+    engine.use_fused_step = True
+    engine._graphs.clear()
+    prompts = [rng.integers(0, cfg["vocab_size"], 512).tolist() for _ in range(8)]
+    graph, slots = start_decode(engine, cfg, prompts, 40, bt)
+    try:
+        for _ in range(4):
+            graph.run()
+        program = graph.program
+        if program is not None:
+            n = len(program.phases)
+            trace = torch.zeros(8 * n, dtype=torch.int64, device=engine.device)
+            torch.cuda.synchronize()
+            program.launch(trace=trace)
+            torch.cuda.synchronize()
+            t = trace.cpu().numpy().reshape(n, 8)
+            kinds = {0: "embed", 1: "product", 2: "attention", 3: "selection"}
+            groups: dict[str, list[float]] = {}
+            for i, ph in enumerate(program.phases):
+                if t[i, 0] == 0:
+                    continue
+                name = kinds[ph.type] + (f" N={ph.N} K={ph.K}" if ph.type == 1 else "")
+                end_of_previous = t[i - 1, 1] if i > 0 and t[i - 1, 1] else t[i, 0]
+                groups.setdefault(name, []).append((t[i, 1] - end_of_previous) / 1e3)
+            total = (t[n - 2, 1] - t[0, 0]) / 1e3 if n >= 2 else 0.0
+            report["decode_b8_fused_step"] = {
+                "phases": [{"phase": k, "count": len(v), "us_each": round(statistics.median(v), 2),
+                            "us_total": round(sum(v), 1)} for k, v in groups.items()],
+                "us_block0": round(float(total), 1)}
+    finally:
+        for s in slots.values():
+            engine.release(s)
+    print(json.dumps(report))
+    return 0
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -168,17 +347,17 @@ def run_ours(args):
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device: this benchmark has no CPU path"}))
         return 1
-    cfg = gpt2_small()
     pk = peaks()
+    if args.profile:
+        return run_profile(args, torch, bt, kernels, pk)
+    cfg = gpt2("small")
     batch, steps, warmup = 8, args.steps, args.warmup
     if steps + warmup > CONTEXT - 4:
         print(json.dumps({"error": f"steps + warmup must stay below the context of {CONTEXT}"}))
         return 1
     prompt_len = min(512, CONTEXT - steps - warmup - 2)
     rng = np.random.default_rng(0)
-    with tempfile.TemporaryDirectory() as folder:
-        bt.write_random_model(folder, cfg, seed=0, storage="bfloat16")
-        engine = bt.Engine.from_folder(folder, "bfloat16", max_tokens=64 * CONTEXT, max_slots=64)
+    engine = make_engine(cfg, bt, torch, max_tokens=64 * CONTEXT, max_slots=64)
     if args.separate_kernels:
         engine.use_fused_step = False
     before_all = kernels.launch_count()
@@ -190,32 +369,48 @@ def run_ours(args):
     # prefill: 2 sequences x 1,024 tokens
     lengths = [PREFILL_TOKENS // 2] * 2
     prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in lengths]
-    times = []
-    for rep in range(7):
-        slots = [engine.new_sequence() for _ in prompts]
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        a.record()
-        engine.step([bt.StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
-        b.record()
-        torch.cuda.synchronize()
-        times.append(a.elapsed_time(b))
-        for s in slots:
-            engine.release(s)
-    prefill_ms = statistics.median(times[3:])      # the first runs build the kernels' state and record the shape
+    prefill_stats = timed_prefill(engine, prompts, torch, bt)
+    prefill_ms = prefill_stats["median"]
     if args.only == "prefill":
-        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": prefill_ms}))
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": prefill_ms, "spread": prefill_stats}))
         return 0
+    flops = prefill_flops(cfg, lengths)
     prefill = {"value": PREFILL_TOKENS / prefill_ms * 1e3, "tokens": PREFILL_TOKENS, "ms": prefill_ms,
-               "frac": prefill_flops(cfg, lengths) / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
-    # decode at batch 1 and 64 (shorter runs), then the headline at batch 8 under the clock sampler
-    points = {}
+               "frac": flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), "of": "burst",
+               "frac_of_sustained": flops / (prefill_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12),
+               "spread_ms": prefill_stats}
+    # the other workloads: GPT-2 small at batch 1 and 64, then (larger models) medium and XL
+    points, detail = {}, {}
+    series_steps = min(steps, 64)
     for b in (1, 64):
-        ms, _, _ = decode_points(engine, cfg, b, 512, min(steps, 64), max(3, min(warmup, 8)), torch, bt, rng)
-        points[f"decode_b{b}"] = b / ms * 1e3
+        detail[f"decode_b{b}"] = decode_series(engine, cfg, [512] * b, series_steps, torch, bt, rng, pk)
+        points[f"decode_b{b}"] = detail[f"decode_b{b}"]["tokens_per_s"]
     with ClockSampler() as clocks:
         ms, launches, mean_ctx = decode_points(engine, cfg, batch, prompt_len, steps, warmup, torch, bt, rng)
         e2e = e2e_decode(engine, cfg, batch, prompt_len, steps, torch, bt, rng)
+    launches_small = kernels.launch_count() - before_all
+    detail["decode_b8"] = decode_series(engine, cfg, [512] * batch, series_steps, torch, bt, rng, pk)
+    h2d = round(engine.last_session.h2d_bytes / max(1, engine.last_session.steps), 1)
+    d2h = round(engine.last_session.d2h_bytes / max(1, engine.last_session.steps), 1)
+    if args.points == "all":
+        del engine
+        torch.cuda.empty_cache()
+        # GPT-2 medium: 8 prompts with lengths uniform in [16, 900], 128 decode steps
+        medium = gpt2("medium")
+        lengths_m = [int(n) for n in np.random.default_rng(7).integers(16, 901, 8)]
+        eng = make_engine(medium, bt, torch, max_tokens=8 * CONTEXT + 64 * 8, max_slots=8, fast_weights=True)
+        detail["medium_ragged8"] = dict(decode_series(eng, medium, lengths_m, 128, torch, bt, rng, pk), prompt_lengths=lengths_m)
+        points["medium_ragged8"] = detail["medium_ragged8"]["tokens_per_s"]
+        del eng
+        torch.cuda.empty_cache()
+        # GPT-2 XL: batch 64, prompts of 256 tokens, 256 decode steps, the cache for 64 x 1,024 positions resident
+        xl = gpt2("xl")
+        eng = make_engine(xl, bt, torch, max_tokens=64 * CONTEXT, max_slots=64, fast_weights=True)
+        detail["xl_b64"] = decode_series(eng, xl, [256] * 64, 256, torch, bt, rng, pk)
+        detail["xl_b64"]["cache_resident_gb"] = round(64 * CONTEXT * kv_bytes_per_token(xl) / 1e9, 1)
+        points["xl_b64"] = detail["xl_b64"]["tokens_per_s"]
+        del eng
+        torch.cuda.empty_cache()
     value = batch / ms * 1e3
     step_bytes = weight_bytes(cfg) + batch * mean_ctx * kv_bytes_per_token(cfg)
     achieved = step_bytes / (ms * 1e-3) / 1e9
@@ -231,9 +426,7 @@ def run_ours(args):
                    "sampling": "greedy on device", "l2": "working set of a step exceeds L2 (weights 249 MB + cache)",
                    "peaks": pk["source"]},
         "clocks": clocks.summary(),
-        "e2e": {"value": e2e, "unit": "tokens/s",
-                "h2d_bytes_per_step": round(engine.last_session.h2d_bytes / max(1, engine.last_session.steps), 1),
-                "d2h_bytes_per_step": round(engine.last_session.d2h_bytes / max(1, engine.last_session.steps), 1),
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "note": "generate_causal_streaming: prompts as host lists, every step's ids and log-probabilities "
                         "read back to pinned host memory; tokens are fed forward on the device, so a step's own "
                         "input copy is the integers of a recomposed batch only"},
@@ -242,7 +435,8 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "bytes_per_step": step_bytes, "of": pk["source"]},
         "points": points,
-        "launches_total": kernels.launch_count() - before_all,
+        "detail": detail,
+        "launches_total": launches_small,
     }
     print(json.dumps(line))
     return 0
@@ -259,6 +453,10 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8, help="batch of the decode steps under --only decode")
     parser.add_argument("--separate-kernels", action="store_true",
                         help="decode steps as a CUDA graph of separate kernels instead of the fused decode step")
+    parser.add_argument("--points", choices=["all", "small"], default="all",
+                        help="small: leave out the GPT-2 medium and XL workloads (they take about a minute more)")
+    parser.add_argument("--profile", action="store_true",
+                        help="print where a prefill and a decode step spend their time, kernel by kernel, instead")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate (Cargo.toml only): pip "

@@ -35,7 +35,90 @@ def library() -> ctypes.CDLL:
         if lib.bt_abi_version() != 1:
             raise KernelError(f"{path} has an unexpected interface version")
         _LIB = lib
-    return _LIB
+    return _LIB if _PROFILE is None else _Bracketed(_LIB, _PROFILE)
+
+
+class KernelProfile:
+    """Times every launch of the library on the device while it is active (`with KernelProfile() as p: ...`).
+
+    Each launch is bracketed by two CUDA events on the launching stream; `summary()` waits for them and returns, per
+    kernel, the number of launches, the time, and what the wrappers said the launches had to do (floating-point
+    operations and bytes that must move), from which achieved TFLOP/s and GB/s follow.  Launches recorded into a
+    CUDA graph cannot be timed this way: profile steps that run their kernels directly."""
+
+    SKIP = ("bt_last_error", "bt_launch_count", "bt_abi_version", "bt_tensor_map", "bt_decode_flow_plan",
+            "bt_decode_flow_phase_bytes", "bt_attention_decode_scratch_floats")
+
+    def __init__(self):
+        self.records = []          # (name, start event, stop event, flops, bytes)
+        self.pending = (0.0, 0.0)
+
+    def __enter__(self):
+        global _PROFILE
+        _PROFILE = self
+        return self
+
+    def __exit__(self, *exc):
+        global _PROFILE
+        _PROFILE = None
+
+    def summary(self) -> list[dict]:
+        torch.cuda.synchronize()
+        rows: dict[str, dict] = {}
+        for name, start, stop, flops, nbytes in self.records:
+            row = rows.setdefault(name, {"kernel": name, "launches": 0, "ms": 0.0, "flops": 0.0, "bytes": 0.0})
+            row["launches"] += 1
+            row["ms"] += start.elapsed_time(stop)
+            row["flops"] += flops
+            row["bytes"] += nbytes
+        total = sum(r["ms"] for r in rows.values()) or 1.0
+        out = []
+        for row in sorted(rows.values(), key=lambda r: -r["ms"]):
+            seconds = row["ms"] * 1e-3
+            row["share"] = row["ms"] / total
+            row["tflops"] = row["flops"] / seconds / 1e12 if seconds > 0 and row["flops"] else None
+            row["gbs"] = row["bytes"] / seconds / 1e9 if seconds > 0 and row["bytes"] else None
+            out.append(row)
+        return out
+
+
+class _Bracketed:
+    """The library as the wrappers see it while a profile is active: every launch between two events."""
+
+    def __init__(self, lib, profile):
+        self._lib, self._profile = lib, profile
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+        if name.endswith("_supports") or name.startswith(KernelProfile.SKIP):
+            return fn
+        profile = self._profile
+
+        def launch(*args):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            code = fn(*args)
+            stop.record()
+            flops, nbytes = profile.pending
+            profile.pending = (0.0, 0.0)
+            profile.records.append((name[3:] if name.startswith("bt_") else name, start, stop, flops, nbytes))
+            return code
+        return launch
+
+
+_PROFILE: KernelProfile | None = None
+
+
+def _work(flops: float = 0.0, nbytes: float = 0.0) -> None:
+    """What the next launch has to do (for a profile; costs nothing otherwise)."""
+    if _PROFILE is not None:
+        _PROFILE.pending = (float(flops), float(nbytes))
+
+
+def _linear_work(m, n, k, a, w, out) -> None:
+    if _PROFILE is not None:
+        _work(2.0 * m * n * k, m * k * (a.element_size() if hasattr(a, "element_size") else 4) + n * k * w.element_size()
+              + m * n * out.element_size())
 
 
 def launch_count() -> int:
@@ -101,6 +184,7 @@ def embed(tokens, positions, wte, wpe, out, status=None):
         n_pos = wpe.shape[0]
     if out.shape[0] < n:
         raise ShapeError(f"out: {out.shape[0]} rows for {n} tokens")
+    _work(0.0, n * width * (wte.element_size() * (2 if wpe is not None else 1) + 4))
     _check(library().bt_embed(_ptr(tokens), _ptr(positions if wpe is not None else None), _ptr(wte), _ptr(wpe), _ptr(out),
                               c_int(n), c_int(width), c_int(vocab), c_int(n_pos), c_int(_code(wte.dtype)),
                               _ptr(status), _stream()))
@@ -119,6 +203,7 @@ def layernorm(x, gamma, beta, out, eps: float, rows=None, n_rows=None):
     _need(out, "out", (torch.float32, torch.bfloat16), (None, width))
     if out.shape[0] < n:
         raise ShapeError(f"out: {out.shape[0]} rows for {n} rows")
+    _work(0.0, n * width * (4 + out.element_size()))
     _check(library().bt_layernorm(_ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), c_int(n), c_int(width),
                                   c_float(eps), c_int(_code(out.dtype)), _stream()))
 
@@ -143,6 +228,7 @@ def linear_simt(a, w, bias, out, *, m=None, w_is_nk=False, activation=None, resi
         raise ShapeError(f"linear: {m} rows asked of a[{a.shape[0]}] and out[{out.shape[0]}]")
     if activation not in ACTIVATIONS:
         raise ShapeError(f"linear: unknown activation {activation!r}")
+    _linear_work(m, n, k, a, w, out)
     _check(library().bt_linear_simt(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), c_int(m), c_int(n), c_int(k),
                                     c_int(1 if w_is_nk else 0), c_int(ACTIVATIONS[activation]), c_int(_code(a.dtype)),
                                     c_int(_code(out.dtype)), _stream()))
@@ -185,6 +271,7 @@ def linear_skinny(a, w, bias, out, *, m, w_is_nk=False, activation=None, residua
         _need(a, "a", torch.bfloat16, (None, k))
         if a.shape[0] < m:
             raise ShapeError(f"linear_skinny: {m} rows asked of a[{a.shape[0]}]")
+    _linear_work(m, n, k, w, w, out)
     _check(library().bt_linear_skinny(_ptr(a if norm is None else None), _ptr(x32), _ptr(rows), _ptr(gamma), _ptr(beta),
                                       c_float(eps), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), c_int(m), c_int(n),
                                       c_int(k), c_int(1 if w_is_nk else 0), c_int(ACTIVATIONS[activation]),
@@ -207,6 +294,7 @@ def linear_mid(a, w, bias, out, *, m, activation=None, residual=None, split=0):
         _need(residual, "residual", torch.float32, (None, n))
     if activation not in ACTIVATIONS:
         raise ShapeError(f"linear_mid: unknown activation {activation!r}")
+    _linear_work(m, n, k, a, w, out)
     _check(library().bt_linear_mid(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), _ptr(kernel_status(a.device)),
                                    c_int(m), c_int(n), c_int(k), c_int(ACTIVATIONS[activation]),
                                    c_int(1 if out.dtype == torch.float32 else 0), c_int(split), _stream()))
@@ -247,6 +335,7 @@ def linear_tcgen05(a, w, bias, out, *, m, activation=None, residual=None):
         _need(residual, "residual", torch.float32, (None, n))
     if activation not in ACTIVATIONS:
         raise ShapeError(f"linear_tcgen05: unknown activation {activation!r}")
+    _linear_work(m, n, k, a, w, out)
     _check(library().bt_linear_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out),
                                        _ptr(kernel_status(a.device)), c_int(m), c_int(n), c_int(k),
                                        c_int(ACTIVATIONS[activation]), c_int(1 if out.dtype == torch.float32 else 0),
@@ -289,6 +378,7 @@ def linear_stream(a, w, bias, out, *, m, activation=None, residual=None, norm=No
         _need(a, "a", torch.bfloat16, (None, k))
         if a.shape[0] < m:
             raise ShapeError(f"linear_stream: {m} rows asked of a[{a.shape[0]}]")
+    _linear_work(m, n, k, w, w, out)
     _check(library().bt_linear_stream(_ptr(a if norm is None else None), _ptr(x32), _ptr(rows), _ptr(gamma), _ptr(beta),
                                       c_float(eps), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), c_int(m), c_int(n),
                                       c_int(k), c_int(ACTIVATIONS[activation]),
@@ -302,6 +392,7 @@ def kv_append(proj, k_offset, v_offset, positions, token_seq, ctx_len, table, ta
     _need(k_pool, "k_pool", proj.dtype)
     _need(v_pool, "v_pool", proj.dtype)
     _need(table, "table", torch.int32)
+    _work(0.0, 4.0 * n_tokens * n_kv_heads * head_dim * proj.element_size())
     _check(library().bt_kv_append(_ptr(proj), c_longlong(proj.shape[1]), c_int(k_offset), c_int(v_offset),
                                   _ptr(positions), _ptr(token_seq), _ptr(ctx_len), _ptr(table), c_int(table.shape[1]),
                                   c_int(table_len), c_int(PAGE_SIZE), _ptr(k_pool), _ptr(v_pool), c_int(n_tokens),
