@@ -357,7 +357,9 @@ def run_ours(args):
         return 1
     prompt_len = min(512, CONTEXT - steps - warmup - 2)
     rng = np.random.default_rng(0)
-    engine = make_engine(cfg, bt, torch, max_tokens=64 * CONTEXT, max_slots=64)
+    # (a run of one workload, for a profiler, holds only the cache that workload needs)
+    cache_rows = max(args.batch, 2) if args.only != "all" else 64
+    engine = make_engine(cfg, bt, torch, max_tokens=cache_rows * CONTEXT, max_slots=64)
     if args.separate_kernels:
         engine.use_fused_step = False
     before_all = kernels.launch_count()
