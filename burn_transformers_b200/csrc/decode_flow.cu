@@ -64,13 +64,13 @@ constexpr int DF_SPIN_LIMIT = 1 << 21;           // tries of any wait before a b
 constexpr int DF_TRACE_SLOTS = 8;
 
 enum { FP_EMBED = 0, FP_LINEAR = 1, FP_ATTENTION = 2, FP_SAMPLE = 3 };
-enum { FA_ROWS = 0, FA_LAYERNORM = 1 };
+enum { FA_ROWS = 0, FA_LAYERNORM = 1, FA_RMSNORM = 2 };
 enum { FO_WORDS = 0, FO_PAIRS = 1, FO_PLAIN = 2 };
 
 struct FlowPhase {
   int type, M;
   // ---- linear: out[M, N] = act(A @ w^T + bias) (+ residual) ----
-  int a_kind;                    // FA_ROWS: tagged bfloat16 words [M][K]; FA_LAYERNORM: LayerNorm of tagged 32-bit pairs [.][K]
+  int a_kind;                    // FA_ROWS: tagged bfloat16 words [M][K]; FA_LAYERNORM, FA_RMSNORM: that norm of tagged 32-bit pairs [.][K]
   int N, K, act;
   int out_kind;                  // FO_WORDS: tagged bfloat16 words; FO_PAIRS: tagged 32-bit pairs (the residual stream, added to);
                                  // FO_PLAIN: plain 32-bit (the logits)
@@ -325,7 +325,7 @@ __device__ unsigned df_weight_producer(const FlowArgs& args, int n_phases, const
     // What the phase's computing warps will read from plain memory, on its way into the L2 cache: the block's bias
     // values, and (one block for all) the norm's parameters.
     if (ph->bias && c0 + lane * 32 < c1) df_prefetch_l2(ph->bias + c0 + lane * 32);
-    if (ph->a_kind == FA_LAYERNORM && pi % (int)gridDim.x == (int)blockIdx.x)
+    if (ph->a_kind != FA_ROWS && pi % (int)gridDim.x == (int)blockIdx.x)
       for (int k = lane * 32; k < K; k += 32 * 32) {
         df_prefetch_l2(ph->gamma + k);
         if (ph->beta) df_prefetch_l2(ph->beta + k);
@@ -537,7 +537,7 @@ __device__ __forceinline__ void df_sum_warps(const float (*part)[8], float (&out
 // channels) [w qpw, (w + 1) qpw) of each row, a lane Q of them (K <= 768 Q).  Rows go in passes of RP (as many as keep
 // the loads of a pass in 64 registers): loaded until every tag is the expected one, then each warp's sum per row, the
 // mean from the warps' sums in warp order, each warp's squared deviations, the variance, and the normalised rows go
-// into the panel as bfloat16, 8 bytes a lane at a time.
+// into the panel as bfloat16, 8 bytes a lane at a time.  An RMS norm (FA_RMSNORM) is the same with the mean left at zero.
 template <int Q>
 __device__ __forceinline__ void df_layernorm_rows(const FlowPhase& ph, const FlowArgs& args, unsigned char* panel, int stride,
                                                   FlowShared& sh, int tid) {
@@ -546,6 +546,7 @@ __device__ __forceinline__ void df_layernorm_rows(const FlowPhase& ph, const Flo
   const int K = ph.K, M = ph.M, quads = K >> 2, qpw = (quads + DF_CWARPS - 1) / DF_CWARPS;
   const unsigned tag = df_tag32(args.epoch, ph.a_src);
   const float inv_k = 1.f / (float)K;
+  const bool rms = ph.a_kind == FA_RMSNORM;      // no mean is taken off: the rows are scaled by their root mean square
   int qd[Q];
   unsigned has = 0;
   float4 g4[Q], b4[Q];
@@ -624,7 +625,7 @@ __device__ __forceinline__ void df_layernorm_rows(const FlowPhase& ph, const Flo
     float mean[RP];
     df_sum_warps<RP>(sh.ln[0], mean);
 #pragma unroll
-    for (int r = 0; r < RP; ++r) mean[r] *= inv_k;
+    for (int r = 0; r < RP; ++r) mean[r] = rms ? 0.f : mean[r] * inv_k;
 #pragma unroll
     for (int r = 0; r < RP; ++r) {
       float t = 0.f;
@@ -747,7 +748,7 @@ __device__ void df_build_panel(const FlowPhase& ph, const FlowArgs& args, const 
       const int r = i / (KP - K), c = K + i % (KP - K);
       reinterpret_cast<__nv_bfloat16*>(panel + (size_t)r * stride)[c] = __float2bfloat16_rn(0.f);
     }
-  if (ph.a_kind == FA_LAYERNORM) {
+  if (ph.a_kind != FA_ROWS) {
     df_layernorm_rows<LNQ>(ph, args, panel, stride, sh, tid);
   } else {
     df_panel_from_words(ph, args, panel, stride, sh, tid);
@@ -1480,7 +1481,7 @@ extern "C" int bt_decode_flow_plan(void* phases_host, int n_phases, int rows, lo
     if (ph[i].type == FP_LINEAR) {
       BT_CHECK(ph[i].K % 8 == 0 && ph[i].K >= 8, "decode_flow: K=%d is no multiple of 8", ph[i].K);
       if (ph[i].K > max_k) max_k = ph[i].K;
-      if (ph[i].a_kind == FA_LAYERNORM) {
+      if (ph[i].a_kind != FA_ROWS) {
         BT_CHECK(ph[i].K <= 3 * 768, "decode_flow: a LayerNorm over %d channels exceeds the 2304 the step holds", ph[i].K);
         if (ph[i].K > max_ln_k) max_ln_k = ph[i].K;
       }

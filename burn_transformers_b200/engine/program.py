@@ -26,7 +26,7 @@ from .. import kernels
 from ..cache.spec import PAGE_SIZE
 
 PH_EMBED, PH_LINEAR, PH_ATTENTION, PH_SAMPLE = 0, 1, 2, 3
-A_ROWS, A_LAYERNORM = 0, 1
+A_ROWS, A_LAYERNORM, A_RMSNORM = 0, 1, 2
 OUT_WORDS, OUT_PAIRS, OUT_PLAIN = 0, 1, 2
 MAX_ITEMS = 8          # DF_MAX_ITEMS of csrc/decode_flow.cu
 MAX_ROWS = 16
@@ -127,12 +127,13 @@ class DecodeProgram:
         ph = Phase(type=PH_LINEAR, M=m, N=n, K=k, act=kernels.ACTIVATIONS[activation], w=_p(w), bias=_p(bias),
                    a_src=-1, res_src=-1)
         if isinstance(a, LazyNorm):
-            if not getattr(a.norm, "fusable", False):
+            kind = {"layernorm": A_LAYERNORM, "rmsnorm": A_RMSNORM}.get(getattr(a.norm, "fused_kind", None))
+            if kind is None:
                 raise ProgramUnsupported("this norm cannot be applied inside a product")
             source = a.x32.data_ptr()
-            if source not in self.pairs or k > 2048:
+            if source not in self.pairs or k > 2304:
                 raise ProgramUnsupported("the rows to normalise were not written by a phase of this step")
-            ph.a_kind, ph.a, ph.rows, ph.a_src = A_LAYERNORM, _p(self.pairs[source]), _p(a.rows), self.writer[source]
+            ph.a_kind, ph.a, ph.rows, ph.a_src = kind, _p(self.pairs[source]), _p(a.rows), self.writer[source]
             ph.gamma, ph.beta, ph.eps = _p(a.norm.t_weight), _p(a.norm.t_bias if a.norm.has_bias else None), a.norm.eps
             if (ph.gamma or 0) % 16 or (ph.beta or 0) % 16:
                 raise ProgramUnsupported("the norm's parameters must lie on 16-byte boundaries")

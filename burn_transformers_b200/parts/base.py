@@ -48,7 +48,12 @@ class Part:
 
 
 class Norm(Part):
+    # A norm that the weight-streaming products can apply to their rows on the way in (LayerNorm semantics: tensors
+    # `t_weight`, `t_bias` if `has_bias`, `eps`) sets `fusable`.  `fused_kind` names what the fused decode step may do
+    # in its place: "layernorm" or "rmsnorm" (rows scaled by the root of their mean square plus `eps`, times `t_weight`,
+    # plus `t_bias` if `has_bias`); None: the norm runs as its own kernels and the step as separate kernels.
     fusable = False
+    fused_kind: str | None = None
 
     def forward(self, ctx, x32, out_dtype, rows=None, n_rows=None, lazy=False):
         """`lazy` allows (never obliges) the norm to return a handle that the consumer's first matrix product

@@ -23,6 +23,7 @@ class LayerNorm(Norm):
         return specs
 
     fusable = True      # linear kernels know how to apply this norm to their rows on the way in
+    fused_kind = "layernorm"
 
     def forward(self, ctx, x32, out_dtype, rows=None, n_rows=None, lazy=False):
         """Normalised rows; with `lazy` (and bfloat16 output, few rows) a handle that the next matrix product

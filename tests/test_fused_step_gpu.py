@@ -174,3 +174,130 @@ def test_fused_step_at_long_contexts_with_loud_weights(splits, monkeypatch, tmp_
     both = replay.batches(engine, seqs, [[0, 1]], [len(s) - 6 for s in seqs])
     err, where = replay.worst_error(both, ref)
     assert err < TOL_BF16, f"fused batch, loud, splits {splits}: {err:.3e} at {where}"
+
+
+# ---- another norm inside the fused step: a toy architecture with an RMS norm that is defined here ----
+
+import dataclasses
+from typing import ClassVar
+
+from burn_transformers_b200.config import Architecture, ModelConfig, register_architecture, unregister_architecture
+from burn_transformers_b200.config.base import field
+from burn_transformers_b200.engine import LayerCall, ModelPlan
+from burn_transformers_b200.parts import (CausalSelfAttention, DenseFeedForward, LearnedPositions, PreNormBlock, TiedReadout,
+                                          TokenEmbedding)
+from burn_transformers_b200.parts.base import Norm
+from burn_transformers_b200.parts.linear import LazyNorm
+from burn_transformers_b200.weights import TensorSpec
+from burn_transformers_b200.weights.spec import VECTOR
+
+
+class ToyRmsNorm(Norm):
+    """x / sqrt(mean(x^2) + eps) * weight, written with torch operations.  It names the fused decode step's RMS kind,
+    so decode steps of few sequences run as one kernel without this class being known to the library."""
+    fused_kind = "rmsnorm"
+    has_bias = False
+
+    def __init__(self, width, eps):
+        self.width, self.eps = width, eps
+
+    def specs(self):
+        return {"weight": TensorSpec((self.width,), VECTOR, ("ones",))}
+
+    def forward(self, ctx, x32, out_dtype, rows=None, n_rows=None, lazy=False):
+        n = n_rows if n_rows is not None else ctx.n_tokens
+        if lazy and out_dtype == torch.bfloat16 and n <= 16:
+            return LazyNorm(self, x32, rows, n)
+        return self.apply(ctx, x32, out_dtype, rows, n)
+
+    def apply(self, ctx, x32, out_dtype, rows, n):
+        x = x32[:n] if rows is None else x32[rows[:n].long()]
+        y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps) * self.t_weight
+        out = ctx.ws.take((n, self.width), out_dtype)
+        out[:n] = y.to(out_dtype)
+        return out
+
+
+@dataclasses.dataclass
+class ToyRmsConfig(ModelConfig):
+    FAMILY: ClassVar[str] = "toy_rms"
+    MODEL_TYPES: ClassVar[tuple] = ("toy_rms",)
+    model_type: str = field("toy_rms")
+    vocab: int = field(300)
+    width: int = field(160)
+    layers: int = field(2)
+    heads: int = field(5)
+    max_len: int = field(256)
+
+    def validate(self):
+        self._check_model_type(self.model_type)
+        self._check_extents(("vocab", "width", "layers", "heads", "max_len"))
+
+
+def build_toy_rms(config: ToyRmsConfig) -> ModelPlan:
+    emb = TokenEmbedding(config.vocab, config.width, 0.5)
+    pos = LearnedPositions(config.max_len, config.width, 0.5)
+    final = ToyRmsNorm(config.width, 1e-6)
+    names = {"embed.weight": (emb, "weight"), "pos.weight": (pos, "weight"), "final.weight": (final, "weight")}
+    blocks = []
+    for i in range(config.layers):
+        n1, n2 = ToyRmsNorm(config.width, 1e-6), ToyRmsNorm(config.width, 1e-6)
+        mixer = CausalSelfAttention(config.width, config.heads, config.heads, config.width // config.heads, 0.25, bias=False)
+        ffn = DenseFeedForward(config.width, 3 * config.width, "gelu_new", bias=False)
+        blocks.append(PreNormBlock(n1, mixer, n2, ffn))
+        for part_name, part in (("n1", n1), ("mixer", mixer), ("n2", n2), ("ffn", ffn)):
+            for local in part.specs():
+                names[f"layers.{i}.{part_name}.{local}"] = (part, local)
+    return ModelPlan(config=config, embedding=emb, positions=pos, blocks=blocks,
+                     schedule=[LayerCall(i) for i in range(config.layers)], final_norm=final, readout=TiedReadout(emb),
+                     names=names, vocab=config.vocab, width=config.width, max_context=config.max_len)
+
+
+def plain_toy_rms(config, w, seq):
+    """The toy model on a whole sequence in float64, written from its definition."""
+    s, d, heads = len(seq), config.width, config.heads
+    hd = d // heads
+    rms = lambda t, p: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6) * w[p + ".weight"]
+    gelu = lambda t: 0.5 * t * (1 + torch.tanh(0.7978845608028654 * (t + 0.044715 * t ** 3)))
+    x = w["embed.weight"][seq] + w["pos.weight"][:s]
+    hidden = torch.arange(s)[None, :] > torch.arange(s)[:, None]
+    for layer in range(config.layers):
+        p = f"layers.{layer}."
+        proj = rms(x, p + "n1") @ w[p + "mixer.qkv.weight"]
+        q, k, v = (proj[:, i * d:(i + 1) * d].view(s, heads, hd) for i in range(3))
+        out = torch.zeros(s, heads, hd, dtype=torch.float64)
+        for h in range(heads):
+            out[:, h] = torch.softmax((q[:, h] @ k[:, h].T * 0.25).masked_fill(hidden, -float("inf")), -1) @ v[:, h]
+        x = x + out.reshape(s, d) @ w[p + "mixer.out.weight"]
+        x = x + gelu(rms(x, p + "n2") @ w[p + "ffn.up.weight"]) @ w[p + "ffn.down.weight"]
+    return rms(x, "final") @ w["embed.weight"].T
+
+
+def test_a_toy_architecture_with_an_rms_norm_decodes_through_the_fused_step(tmp_path):
+    """The norm is defined in this file; it only names the kind of norm the fused step may apply in its place."""
+    register_architecture(Architecture("toy_rms", ("toy_rms",), ToyRmsConfig, build_toy_rms), replace=True)
+    try:
+        config = ToyRmsConfig()
+        folder = bt.write_random_model(tmp_path, config, seed=11, storage="bfloat16")
+        w = {k: torch.from_numpy(v).double() for k, v in plain.read_safetensors(folder / "model.safetensors").items()}
+        rng = np.random.default_rng(4)
+        seqs = [rng.integers(0, config.vocab, n).tolist() for n in (90, 33, 140)]
+        want = [plain_toy_rms(config, w, s).numpy() for s in seqs]
+        results = {}
+        for fused in (True, False):
+            engine = Engine.from_folder(folder, "bfloat16", max_tokens=64 * 8)
+            engine.use_fused_step = fused
+            results[fused] = replay.tail_one_by_one(engine, seqs, tail=24)
+            assert bool(fused_programs(engine)) == fused, "the fused step ran (or did not) against the switch"
+        # the fused step against the same model as separate kernels (bfloat16 both, rounding in the same places) ...
+        separate = {r: np.stack([results[False][(r, p)] for p in range(len(s))]) for r, s in enumerate(seqs)}
+        err, where = replay.worst_error(results[True], separate)
+        assert err < TOL_BF16, f"rms norm, fused against separate kernels: {err:.3e} at {where}"
+        # ... and both against the model in 64-bit (which rounds nothing): the direction of every row of logits
+        for fused, got in results.items():
+            for (r, p), row in got.items():
+                ref = want[r][p]
+                cosine = float(row @ ref / (np.linalg.norm(row) * np.linalg.norm(ref)))
+                assert cosine > 0.999, f"rms norm, fused={fused}: cosine {cosine:.5f} at {(r, p)}"
+    finally:
+        unregister_architecture("toy_rms")
