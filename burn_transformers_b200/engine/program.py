@@ -170,17 +170,20 @@ class DecodeProgram:
         span = ctx.ctx_bound if not window else min(ctx.ctx_bound, window)
         pages = max(1, -(-span // PAGE_SIZE)) + (1 if window else 0)
         units = ctx.n_seqs * n_heads
-        # the splits that leave the busiest block the fewest pages (a block takes every n_blocks-th item)
+        # The splits that leave the busiest block the fewest pages (a block takes every n_blocks-th item), among those
+        # that give a block at most two items if there are any: an item costs a block a hand-over between its warps
+        # and, when it is small, a wait for pages that its ring of slots could not hold ahead (measured: 9 splits
+        # of one page each, 8 items a block, took 23.6 us where one item of 9 pages takes 6).
         splits, best = 1, None
         for s in range(1, min(pages, 16) + 1):
             per_block = -(-units * s // self.n_blocks)
             if per_block > MAX_ITEMS:
                 break
-            load = per_block * -(-pages // s)
+            load = (per_block > 2, per_block * -(-pages // s))
             if best is None or load < best:
                 splits, best = s, load
         if SPLITS_OVERRIDE is not None and -(-units * SPLITS_OVERRIDE // self.n_blocks) <= MAX_ITEMS:
-            splits, best = max(1, min(int(SPLITS_OVERRIDE), pages)), 0
+            splits, best = max(1, min(int(SPLITS_OVERRIDE), pages)), (False, 0)
         if best is None:
             raise ProgramUnsupported(f"{units} attention units are too many for the fused step")
         mixed = ctx.ws.take((ctx.n_seqs, n_heads * head_dim), torch.bfloat16)       # the name of the phase's result
