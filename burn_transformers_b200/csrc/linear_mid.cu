@@ -29,7 +29,7 @@ constexpr int LM_THREADS = (LM_WARPS + 1) * 32;
 constexpr int LM_BM = 64, LM_BK = 64;                 // rows and k of one stage; its columns BN are 16 or 64
 constexpr int LM_MAX_STAGES = 8;
 constexpr int LM_A_BYTES = LM_BM * LM_BK * 2;
-constexpr int lm_stages(int bn) { return bn == 16 ? 8 : 6; }
+constexpr int lm_stages(int bn) { return bn <= 32 ? 8 : 6; }
 constexpr int LM_WAIT_LIMIT = 1 << 20;
 
 struct MidParams {
@@ -228,35 +228,47 @@ extern "C" int bt_linear_mid(const void* a, const void* w, const float* bias, co
   BT_CHECK(bt_linear_mid_supports(M, N, K), "linear_mid: sizes M=%d N=%d K=%d are not supported", M, N, K);
   BT_CHECK(act >= 0 && act <= 2, "linear_mid: unknown activation %d", act);
   BT_CHECK(!(residual && !out_is_f32), "linear_mid: a residual needs a 32-bit output");
-  // wide outputs (a readout) take 64 columns a block, so that the rows are read from L2 a quarter as often
-  const int bn = N >= 8192 ? 64 : 16;
+  const int k_blocks = (K + LM_BK - 1) / LM_BK;
+  if (split <= 0) {
+    split = 1;
+    while (split < 8 && (k_blocks + split - 1) / split > 16) split *= 2;
+  }
+  // Every block reads all rows of A (from L2) for its columns of W: the wider a block's share of columns, the less
+  // often the rows are read.  So: the widest of 64, 32 and 16 columns that still leaves a block (or more) for
+  // every multiprocessor; a readout (N >= 8192) takes 64 in any case.
+  const int want_blocks = sm_count();
+  int bn = 16;
+  if (N >= 8192) bn = 64;
+  else
+    for (int cand = 64; cand > 16; cand /= 2)
+      if (((N + cand - 1) / cand) * split >= want_blocks) {
+        bn = cand;
+        break;
+      }
   const int n_tiles = (N + bn - 1) / bn;
   const int rows16 = (M + 15) / 16 * 16;
   CUtensorMap ma, mw;
   if (int rc = tensor_map_2d_bf16(&ma, a, (unsigned long long)M, (unsigned long long)K, (unsigned long long)K, rows16)) return rc;
   if (int rc = tensor_map_2d_bf16(&mw, w, (unsigned long long)N, (unsigned long long)K, (unsigned long long)K, bn)) return rc;
-  const int k_blocks = (K + LM_BK - 1) / LM_BK;
-  if (split <= 0) {
-    split = 1;
-    while (split < 8 && (k_blocks + split - 1) / split > 16) split *= 2;
-    if (split == 1 && k_blocks >= 8 && 2 * n_tiles <= sm_count()) split = 2;      // too few blocks to fill the device
-  }
+  if (split == 1 && k_blocks >= 8 && 2 * n_tiles <= sm_count()) split = 2;      // too few blocks to fill the device
   BT_CHECK(split == 1 || split == 2 || split == 4 || split == 8, "linear_mid: split %d is not 1, 2, 4 or 8", split);
   const int k_slice = (k_blocks + split - 1) / split * LM_BK;
   MidParams p{bias, residual, out, status, M, N, K, k_slice, act, out_is_f32, rows16};
   BT_CHECK(n_tiles <= 65535, "linear_mid: N=%d needs too many column tiles", N);
   auto launch = [&](auto kernel, int bn_) -> int {
     const size_t smem = (size_t)lm_stages(bn_) * (LM_A_BYTES + bn_ * LM_BK * 2) + 1024 + (split > 1 ? (size_t)LM_BM * bn_ * 4 : 0);
-    static bool configured[2] = {false, false};
-    if (!configured[bn_ == 64]) {
+    static bool configured[3] = {false, false, false};
+    const int which = bn_ == 64 ? 2 : (bn_ == 32 ? 1 : 0);
+    if (!configured[which]) {
       const size_t most = (size_t)lm_stages(bn_) * (LM_A_BYTES + bn_ * LM_BK * 2) + 1024 + (size_t)LM_BM * bn_ * 4;
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
       BT_CHECK(e == cudaSuccess, "linear_mid: cannot reserve %zu bytes of shared memory: %s", most, cudaGetErrorString(e));
-      configured[bn_ == 64] = true;
+      configured[which] = true;
     }
     BT_PDL_OK("linear_mid", launch_pdl(kernel, dim3(split, n_tiles), dim3(LM_THREADS), smem, stream, split, ma, mw, p));
     return 0;
   };
   if (bn == 64) return launch(linear_mid_kernel<64>, 64);
+  if (bn == 32) return launch(linear_mid_kernel<32>, 32);
   return launch(linear_mid_kernel<16>, 16);
 }
