@@ -97,6 +97,8 @@ class ModelPlan:
         for index, call in enumerate(self.schedule):
             entry, owns = self.cache_entry(index)
             self.blocks[call.block].forward(ctx, residual, entry, owns)
+        if getattr(ctx, "side", None) is not None:
+            ctx.side.join()       # (what parts ran beside the step must be done before the step's scratch is used again)
         if ctx.n_want == 0:
             return None
         h = self.final_norm.forward(ctx, residual, ctx.dtype, rows=ctx.want_rows, n_rows=ctx.n_want,

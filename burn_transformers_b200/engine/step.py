@@ -79,8 +79,39 @@ class StepContext:
         self.want_rows = want_rows
         self.tables = tables            # per cache group: [n_seqs, table_width] page ids
         self.program = None             # set while a fused decode step is recorded (engine.program.DecodeProgram)
+        self.side = None                # a SideWork: a second stream for work nothing later in the step waits for
         # the same facts as Python lists, for parts that plan on the host
         self.host_slots, self.host_seq_start, self.host_past_len = host_slots, host_seq_start, host_past_len
+
+
+class SideWork:
+    """A second stream beside the step's own, for kernels whose results nothing later in the same step reads (filing
+    a prompt's keys and values in the pages while attention runs on the step's own projections).
+
+    `fork()` makes the side stream wait for what the step's stream has been given so far; work launched inside
+    `with side.stream_context():` then runs beside the step; `join()` makes the step's stream wait for it.  A part
+    calls `fork` and the context; the model's forward calls `join` once at the end of the step, before the step's
+    scratch memory may be used again.  Inside a stream capture the same calls become a branch of the graph."""
+
+    def __init__(self, device):
+        self.stream = torch.cuda.Stream(device=device)
+        self.pending = False
+
+    def fork(self):
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream())
+        self.stream.wait_event(event)
+
+    def stream_context(self):
+        self.pending = True
+        return torch.cuda.stream(self.stream)
+
+    def join(self):
+        if self.pending:
+            event = torch.cuda.Event()
+            event.record(self.stream)
+            torch.cuda.current_stream().wait_event(event)
+            self.pending = False
 
 
 def _align4(n: int) -> int:
@@ -131,6 +162,7 @@ class StepBuilder:
         self._host = None
         self._dev = None
         self.h2d_bytes_last = 0
+        self._side = None         # the steps' second stream (made at the first step on a CUDA device)
 
     def build(self, entries: list[StepEntry]) -> StepContext:
         cache = self.cache
@@ -176,9 +208,14 @@ class StepBuilder:
         view = lambda i: dev[offsets[i]:offsets[i] + max(1, sizes[i])]
         tables = [view(8 + g).view(n_seqs, width) for g in range(len(cache.groups))]
         tokens = range(n_tokens)
-        return StepContext(
+        ctx = StepContext(
             dtype=self.dtype, cache=cache, ws=self.ws, n_tokens=len(tokens), n_seqs=n_seqs, n_want=len(want_rows),
             max_new=max(news), is_decode=all(n == 1 for n in news), fresh=all(p == 0 for p in pasts),
             ctx_bound=max(ctx_len), tokens=view(0), positions=view(1), token_seq=view(2), seq_start=view(3),
             past_len=view(4), ctx_len=view(5), slots=view(6), want_rows=view(7), tables=tables, host_slots=slots,
             host_seq_start=seq_start, host_past_len=pasts)
+        if self.device.type == "cuda":
+            if self._side is None:
+                self._side = SideWork(self.device)
+            ctx.side = self._side
+        return ctx

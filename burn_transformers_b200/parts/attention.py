@@ -91,8 +91,17 @@ class CausalSelfAttention(Mixer):
         table = ctx.tables[g]
         window = self.window or 0
         if owns_cache and not ctx.is_decode:
-            kernels.kv_append(proj, self.q_width, self.q_width + self.kv_width, ctx.positions, ctx.token_seq,
-                              ctx.ctx_len, table, group.table_len, k_pool, v_pool, n, self.n_kv_heads, self.head_dim)
+            side = getattr(ctx, "side", None) if ctx.fresh else None
+            if side is not None:
+                # fresh sequences attend over the step's own projections: nothing in this step reads the pages, so
+                # the keys and values are filed beside the attention, on the step's second stream
+                side.fork()
+                with side.stream_context():
+                    kernels.kv_append(proj, self.q_width, self.q_width + self.kv_width, ctx.positions, ctx.token_seq,
+                                      ctx.ctx_len, table, group.table_len, k_pool, v_pool, n, self.n_kv_heads, self.head_dim)
+            else:
+                kernels.kv_append(proj, self.q_width, self.q_width + self.kv_width, ctx.positions, ctx.token_seq,
+                                  ctx.ctx_len, table, group.table_len, k_pool, v_pool, n, self.n_kv_heads, self.head_dim)
         if program is not None and ctx.is_decode:
             # recorded as a phase of the fused step; its partial results are merged by the output projection
             mixed = program.add_attention(ctx, proj, k_pool, v_pool, table, group.table_len, n_heads=self.n_heads,
