@@ -246,15 +246,15 @@ def timed_prefill(engine, prompts, torch, bt):
 
 
 def run_profile(args, torch, bt, kernels, pk):
-    """Where a prefill of 2 x 1,024 tokens and decode steps at batch 8 and 64 spend their time (GPT-2 small): every
+    """Where a prefill of 2 x 1,024 tokens and decode steps at batch 8 and 64 spend their time (--model): every
     kernel between two CUDA events, launched directly (no recorded graph, so gaps between launches are not in the
     figures), with the rate each kernel class achieved; the fused decode step by its own timeline of block 0."""
     import numpy as np
-    cfg = gpt2("small")
+    cfg = gpt2(args.model)
     rng = np.random.default_rng(0)
-    engine = make_engine(cfg, bt, torch, max_tokens=64 * CONTEXT, max_slots=64)
+    engine = make_engine(cfg, bt, torch, max_tokens=64 * CONTEXT, max_slots=64, fast_weights=args.model != "small")
     d, L = cfg["n_embd"], cfg["n_layer"]
-    report = {"profile": True, "peaks": pk}
+    report = {"profile": True, "model": args.model, "peaks": pk}
 
     def table(rows, attention_flops=0.0, attention_bytes=0.0, steps=1):
         out = []
@@ -459,6 +459,7 @@ def main() -> int:
                         help="small: leave out the GPT-2 medium and XL workloads (they take about a minute more)")
     parser.add_argument("--profile", action="store_true",
                         help="print where a prefill and a decode step spend their time, kernel by kernel, instead")
+    parser.add_argument("--model", choices=["small", "medium", "xl"], default="small", help="the model --profile looks at")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate (Cargo.toml only): pip "
