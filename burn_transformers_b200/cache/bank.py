@@ -10,15 +10,19 @@ NoahIsCool/burn-transformers) with pages in place of its dense [batch, heads, ti
 
 Lengths advance only when a step is committed; a step that fails leaves them unchanged
 (src/cache/tensor/state/step.rs:1-56).  Releasing a slot returns its pages and zeroes its state.
+
+The tensors live here; the books (which slot and page is in use, each sequence's page list and length) are kept by the
+host library, csrc/host/page_book.cpp, in C++.
 """
 from __future__ import annotations
 
+import ctypes
 import dataclasses
 
 import torch
 
 from ..errors import CacheError
-from .slots import FreeList
+from . import native
 from .spec import PAGE_SIZE, CacheConfig, CacheNeed, KvSpec
 
 
@@ -26,15 +30,48 @@ def pages_for(tokens: int) -> int:
     return (tokens + PAGE_SIZE - 1) // PAGE_SIZE
 
 
+class _SlotBooks:
+    """The slots of a bank as the host library keeps them: how many are free or held, whether one is held."""
+
+    def __init__(self, bank):
+        self._bank = bank
+        self.count = bank.config.max_slots
+
+    @property
+    def free(self) -> int:
+        return self._bank._lib.bth_book_free_slots(self._bank._book)
+
+    @property
+    def held(self) -> int:
+        return self.count - self.free
+
+    def is_held(self, slot: int) -> bool:
+        return bool(self._bank._lib.bth_book_slot_is_held(self._bank._book, int(slot)))
+
+
+class _PageBooks:
+    """The page pool of one group as the host library keeps it."""
+
+    def __init__(self, bank, group: int, count: int):
+        self._bank, self._group, self.count = bank, group, count
+
+    @property
+    def free(self) -> int:
+        return self._bank._lib.bth_book_free_pages(self._bank._book, self._group)
+
+    @property
+    def held(self) -> int:
+        return self.count - self.free
+
+
 @dataclasses.dataclass
 class KvGroup:
     spec: KvSpec
     entries: list[int]            # cache entry ids, in layer order inside the group
     table_len: int                # pages a sequence may hold (all keys) or cycles through (window)
-    pool: FreeList
+    pool: _PageBooks
     k: torch.Tensor               # [layers, pages, kv_heads, PAGE_SIZE, head_dim]
     v: torch.Tensor
-    pages: dict[int, list[int]]   # slot -> page ids in logical order
 
     @property
     def is_ring(self) -> bool:
@@ -42,16 +79,19 @@ class KvGroup:
 
 
 class CacheBank:
+    """The tensors of the cache (pages of keys and values per group, fixed-size states) and, through the host
+    library (csrc/host/page_book.cpp), its books: slots, pages, page lists and lengths."""
+
     def __init__(self, needs: list[CacheNeed], config: CacheConfig, kv_dtype: torch.dtype, device):
         self.config = config
         self.device = torch.device(device)
         self.kv_dtype = kv_dtype
-        self.slots = FreeList(config.max_slots, "slot")
-        self.lengths = [0] * config.max_slots
         self.table_width = pages_for(config.max_context)
         self.groups: list[KvGroup] = []
         self._entry_group: dict[int, tuple[int, int]] = {}
         self.states: dict[tuple[int, str], torch.Tensor] = {}
+        self._lib = native.library()
+        self._book = None
         budget_pages = pages_for(config.max_tokens)
         by_spec: dict[KvSpec, list[int]] = {}
         for entry, need in enumerate(needs):
@@ -60,6 +100,7 @@ class CacheBank:
             for state in need.states:
                 self.states[(entry, state.name)] = torch.zeros((config.max_slots, *state.shape), dtype=state.dtype,
                                                                device=self.device)
+        table_lens, pool_sizes = [], []
         for spec, entries in by_spec.items():
             if spec.window is None:
                 table_len, n_pages = self.table_width, budget_pages
@@ -67,12 +108,27 @@ class CacheBank:
                 table_len = min(self.table_width, pages_for(spec.window))
                 n_pages = min(budget_pages, config.max_slots * table_len)
             shape = (len(entries), n_pages, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
-            group = KvGroup(spec, entries, table_len, FreeList(n_pages, "cache page"),
+            group = KvGroup(spec, entries, table_len, _PageBooks(self, len(self.groups), n_pages),
                             torch.zeros(shape, dtype=kv_dtype, device=self.device),
-                            torch.zeros(shape, dtype=kv_dtype, device=self.device), {})
+                            torch.zeros(shape, dtype=kv_dtype, device=self.device))
             for layer, entry in enumerate(entries):
                 self._entry_group[entry] = (len(self.groups), layer)
             self.groups.append(group)
+            table_lens.append(table_len)
+            pool_sizes.append(n_pages)
+        n = len(self.groups)
+        self._book = self._lib.bth_book_create(config.max_slots, config.max_context, config.max_tokens, n,
+                                               (ctypes.c_int * max(1, n))(*table_lens),
+                                               (ctypes.c_int * max(1, n))(*pool_sizes))
+        if not self._book:
+            raise native.error()
+        self.slots = _SlotBooks(self)
+        self._row = (ctypes.c_int * max(1, self.table_width))()
+
+    def __del__(self):
+        book, self._book = getattr(self, "_book", None), None
+        if book:
+            self._lib.bth_book_destroy(book)
 
     @property
     def max_continued_run(self) -> int | None:
@@ -86,60 +142,41 @@ class CacheBank:
 
     # ---- slots -------------------------------------------------------------------------
     def acquire(self) -> int:
-        slot = self.slots.take()
-        self.lengths[slot] = 0
-        for group in self.groups:
-            group.pages[slot] = []
+        slot = self._lib.bth_book_acquire(self._book)
+        if slot < 0:
+            raise native.error()
         return slot
 
     def release(self, slot: int) -> None:
-        if not self.slots.is_held(slot):
-            raise CacheError(f"slot {slot} is not in use (released twice?)")
-        for group in self.groups:
-            for page in group.pages.pop(slot, []):
-                group.pool.give_back(page)
+        if self._lib.bth_book_release(self._book, int(slot)) < 0:
+            raise native.error()
         for state in self.states.values():
             state[slot].zero_()
-        self.lengths[slot] = 0
-        self.slots.give_back(slot)
 
     def length(self, slot: int) -> int:
-        self._held(slot)
-        return self.lengths[slot]
-
-    def _held(self, slot: int) -> None:
-        if not self.slots.is_held(slot):
-            raise CacheError(f"slot {slot} is not in use")
+        n = self._lib.bth_book_length(self._book, int(slot))
+        if n < 0:
+            raise native.error()
+        return n
 
     # ---- pages -------------------------------------------------------------------------
-    def _pages_wanted(self, group: KvGroup, new_len: int) -> int:
-        return min(pages_for(new_len), group.table_len)
-
     def reserve(self, wanted: list[tuple[int, int]]) -> None:
         """Gives every (slot, new_length) the pages it needs, or raises and changes nothing."""
-        for slot, new_len in wanted:
-            self._held(slot)
-            if new_len > self.config.max_context:
-                raise CacheError(f"slot {slot}: {new_len} tokens exceed the longest sequence of "
-                                 f"{self.config.max_context}")
-            if new_len < self.lengths[slot]:
-                raise CacheError(f"slot {slot}: cannot shrink from {self.lengths[slot]} to {new_len} tokens")
-        for group in self.groups:
-            extra = sum(max(0, self._pages_wanted(group, n) - len(group.pages[s])) for s, n in wanted)
-            if extra > group.pool.free:
-                raise CacheError(f"the cache is full: {extra} more pages needed, {group.pool.free} of "
-                                 f"{group.pool.count} free (max_tokens={self.config.max_tokens})")
-        for group in self.groups:
-            for slot, new_len in wanted:
-                held = group.pages[slot]
-                held.extend(group.pool.take_many(max(0, self._pages_wanted(group, new_len) - len(held))))
+        n = len(wanted)
+        slots = (ctypes.c_int * max(1, n))(*[int(s) for s, _ in wanted])
+        lens = (ctypes.c_int * max(1, n))(*[int(m) for _, m in wanted])
+        if self._lib.bth_book_reserve(self._book, n, slots, lens) < 0:
+            raise native.error()
 
     def commit(self, slot: int, new_len: int) -> None:
-        self._held(slot)
-        self.lengths[slot] = new_len
+        if self._lib.bth_book_commit(self._book, int(slot), int(new_len)) < 0:
+            raise native.error()
 
     def table_row(self, group_index: int, slot: int) -> list[int]:
-        return self.groups[group_index].pages[slot]
+        n = self._lib.bth_book_table_row(self._book, int(group_index), int(slot), self._row, self.table_width)
+        if n < 0:
+            raise native.error()
+        return list(self._row[:n])
 
     def entry_group(self, entry: int) -> tuple[int, int]:
         """(group index, layer index inside the group) of a cache entry that holds keys and values."""
@@ -156,17 +193,9 @@ class CacheBank:
     # ---- checks ------------------------------------------------------------------------
     def tokens_held(self) -> int:
         """Tokens the live sequences hold, each rounded up to a whole page."""
-        return sum(pages_for(self.lengths[s]) * PAGE_SIZE for s in range(self.config.max_slots) if self.slots.is_held(s))
+        return int(self._lib.bth_book_tokens_held(self._book))
 
     def check(self) -> None:
         """No slot or page lost, held twice or freed twice."""
-        self.slots.check()
-        for group in self.groups:
-            group.pool.check()
-            held = [p for pages in group.pages.values() for p in pages]
-            if len(held) != len(set(held)):
-                raise CacheError("a cache page is held by two sequences")
-            if len(held) != group.pool.held:
-                raise CacheError("cache pages are lost: held pages and page lists differ")
-            if any(not self.slots.is_held(s) for s in group.pages):
-                raise CacheError("a free slot still holds pages")
+        if self._lib.bth_book_check(self._book) < 0:
+            raise native.error()

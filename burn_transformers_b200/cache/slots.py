@@ -1,7 +1,9 @@
-"""Host-side bookkeeping of slots and pages.  No tensor lives here, so it runs anywhere."""
+"""Pools of integer handles (slots, pages).  The books are kept by the host library (csrc/host/page_book.cpp);
+no tensor lives here, so it runs anywhere."""
 from __future__ import annotations
 
 from ..errors import CacheError
+from . import native
 
 
 class FreeList:
@@ -10,41 +12,43 @@ class FreeList:
     def __init__(self, count: int, what: str):
         self.what = what
         self.count = count
-        self._free = list(range(count - 1, -1, -1))   # pop() hands out 0 first
-        self._held = [False] * count
+        self._lib = native.library()
+        self._pool = self._lib.bth_pool_create(count, what.encode())
+        if not self._pool:
+            raise native.error()
+
+    def __del__(self):
+        pool, self._pool = getattr(self, "_pool", None), None
+        if pool:
+            self._lib.bth_pool_destroy(pool)
 
     @property
     def free(self) -> int:
-        return len(self._free)
+        return self._lib.bth_pool_free(self._pool)
 
     @property
     def held(self) -> int:
-        return self.count - len(self._free)
+        return self.count - self.free
 
     def take(self) -> int:
-        if not self._free:
-            raise CacheError(f"no free {self.what}: all {self.count} are in use")
-        handle = self._free.pop()
-        self._held[handle] = True
+        handle = self._lib.bth_pool_take(self._pool)
+        if handle < 0:
+            raise native.error()
         return handle
 
     def take_many(self, n: int) -> list[int]:
-        if n > len(self._free):
-            raise CacheError(f"{n} {self.what}s needed, {len(self._free)} of {self.count} free")
+        if n > self.free:
+            raise CacheError(f"{n} {self.what}s needed, {self.free} of {self.count} free")
         return [self.take() for _ in range(n)]
 
     def give_back(self, handle: int) -> None:
-        if not (0 <= handle < self.count):
-            raise CacheError(f"{self.what} {handle} does not exist")
-        if not self._held[handle]:
-            raise CacheError(f"{self.what} {handle} is not in use (freed twice?)")
-        self._held[handle] = False
-        self._free.append(handle)
+        if self._lib.bth_pool_give_back(self._pool, int(handle)) < 0:
+            raise native.error()
 
     def is_held(self, handle: int) -> bool:
-        return 0 <= handle < self.count and self._held[handle]
+        return bool(self._lib.bth_pool_is_held(self._pool, int(handle)))
 
     def check(self) -> None:
         """Every handle is either free or held, none twice."""
-        if sorted(self._free + [h for h in range(self.count) if self._held[h]]) != list(range(self.count)):
-            raise CacheError(f"{self.what} bookkeeping is corrupt")
+        if self._lib.bth_pool_check(self._pool) < 0:
+            raise native.error()

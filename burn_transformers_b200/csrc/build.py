@@ -129,5 +129,47 @@ def build(verbose: bool = True) -> Path:
     return lib
 
 
+HOST_LIB_NAME = "libbt_host.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared"]
+
+
+def host_sources() -> list[Path]:
+    return sorted((CSRC / "host").glob("*.cpp"))
+
+
+def build_host(verbose: bool = True) -> Path:
+    """Compiles the host-side library (the cache's books and the packing of a step's integers: plain C++, no CUDA)
+    with the system's C++ compiler and returns its path.  It needs no GPU and no nvcc, so everything that does not
+    launch kernels (configuration, weights, the cache's bookkeeping, the generation loop's decisions) runs anywhere."""
+    files = host_sources()
+    out_dir = _build_dir()
+    lib = out_dir / HOST_LIB_NAME
+    stamp_file = out_dir / "host_stamp.txt"
+    h = hashlib.sha256()
+    for path in files:
+        h.update(path.name.encode())
+        h.update(path.read_bytes())
+    h.update(" ".join(HOST_FLAGS).encode())
+    stamp = h.hexdigest()
+    if lib.is_file() and stamp_file.is_file() and stamp_file.read_text() == stamp:
+        return lib
+    compiler = next((c for c in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++"))
+                     if c and Path(c).is_file()), None)
+    if compiler is None:
+        raise KernelError("no C++ compiler was found (looked at $CXX, g++, c++, clang++); the host library of this "
+                          "package cannot be built")
+    started = time.time()
+    tmp = out_dir / f".{HOST_LIB_NAME}.{os.getpid()}"
+    result = subprocess.run([compiler, *HOST_FLAGS, "-o", str(tmp), *map(str, files)], capture_output=True, text=True)
+    if result.returncode != 0:
+        raise KernelError(f"compiling {HOST_LIB_NAME} failed:\n{result.stdout}\n{result.stderr}")
+    os.replace(tmp, lib)
+    stamp_file.write_text(stamp)
+    if verbose:
+        _say(f"built {lib.name} in {time.time() - started:.0f} s")
+    return lib
+
+
 if __name__ == "__main__":
+    print(build_host())
     print(build())

@@ -189,19 +189,20 @@ class StepBuilder:
             self._host = PinnedStaging(cap, pinned=self.device.type == "cuda")
             self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         _, h = self._host.next_buffer()
-        for i, e in enumerate(entries):
-            lo, hi = seq_start[i], seq_start[i + 1]
-            h[offsets[0] + lo:offsets[0] + hi] = e.tokens
-            h[offsets[1] + lo:offsets[1] + hi] = np.arange(pasts[i], pasts[i] + news[i], dtype=np.int32)
-            h[offsets[2] + lo:offsets[2] + hi] = i
-        for section, values in ((3, seq_start), (4, pasts), (5, ctx_len), (6, slots), (7, want_rows)):
-            h[offsets[section]:offsets[section] + len(values)] = values
-        for g in range(len(cache.groups)):
-            base = offsets[8 + g]
-            h[base:base + n_seqs * width] = 0
-            for i, e in enumerate(entries):
-                row = cache.table_row(g, e.slot)
-                h[base + i * width:base + i * width + len(row)] = row
+        # the host library fills the buffer (csrc/host/page_book.cpp: positions from the lengths in its books, the
+        # page tables from its page lists)
+        flat_tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int32, count=n_tokens)
+        flat_wants = np.fromiter((int(w) for e in entries for w in e.want), dtype=np.int32, count=len(want_rows))
+        counts = np.asarray(news, dtype=np.int32)
+        want_counts = np.asarray([len(e.want) for e in entries], dtype=np.int32)
+        slot_ids = np.asarray(slots, dtype=np.int32)
+        offs = np.asarray(offsets, dtype=np.int64)
+        summary = np.zeros(6, dtype=np.int32)
+        if cache._lib.bth_book_pack_step(cache._book, n_seqs, slot_ids.ctypes.data, counts.ctypes.data,
+                                         flat_tokens.ctypes.data, want_counts.ctypes.data, flat_wants.ctypes.data, width,
+                                         offs.ctypes.data, h.ctypes.data, summary.ctypes.data) < 0:
+            from ..cache import native
+            raise native.error()
         self._host.copy_to(self._dev, total)
         self.h2d_bytes_last = total * 4
         dev = self._dev
