@@ -1041,7 +1041,7 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
 
 // ---- attention: merging the splits ----
 // The block of split 0 merges the splits of its (sequence, head), in split order, as their tags show up: thread d takes
-// dim d.  Two splits' worth of loads are in flight together.  (A function of its own, not inlined: what it holds in
+// dim d.  Four splits' worth of loads are in flight together.  (A function of its own, not inlined: what it holds in
 // registers is then no burden on the loop over the keys.)
 __device__ __noinline__ void df_attention_merge(const FlowPhase& ph, int pi, const FlowArgs& args, FlowShared& sh) {
   const int tid = threadIdx.x, hd = ph.head_dim, S = ph.n_splits, H = ph.n_heads, n_mine = sh.work.n;
@@ -1052,11 +1052,11 @@ __device__ __noinline__ void df_attention_merge(const FlowPhase& ph, int pi, con
     const long long unit = (long long)it.seq * H + it.head;
     const uint2* src = ph.part + unit * S * (hd + 2);
     float Mx = -INFINITY, Lall = 0.f, o = 0.f;
-    for (int s0 = 0; s0 < S; s0 += 2) {
-      uint2 po[2], pm[2], pl[2];
+    for (int s0 = 0; s0 < S; s0 += 4) {
+      uint2 po[4], pm[4], pl[4];
       unsigned pending = 0;
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+      for (int j = 0; j < 4; ++j)
         if (s0 + j < S) pending |= 1u << j;
       const unsigned have = pending;
       for (int tries = 0; pending != 0; ++tries) {
@@ -1065,7 +1065,7 @@ __device__ __noinline__ void df_attention_merge(const FlowPhase& ph, int pi, con
           break;
         }
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < 4; ++j)
           if (pending & (1u << j)) {
             const uint2* one = src + (long long)(s0 + j) * (hd + 2);
             po[j] = df_ld_pair(one + tid);
@@ -1073,11 +1073,11 @@ __device__ __noinline__ void df_attention_merge(const FlowPhase& ph, int pi, con
             pl[j] = df_ld_pair(one + hd + 1);
           }
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < 4; ++j)
           if ((pending & (1u << j)) && po[j].y == tag_part && pm[j].y == tag_part && pl[j].y == tag_part) pending &= ~(1u << j);
       }
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+      for (int j = 0; j < 4; ++j)
         if (have & (1u << j)) {
           const float ms = __uint_as_float(pm[j].x);
           if (ms == -INFINITY) continue;
