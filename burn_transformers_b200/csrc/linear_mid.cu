@@ -133,6 +133,24 @@ linear_mid_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // W: blocks (columns 0-7: k 0-7, k 8-15; columns 8-15: k 0-7, k 8-15).
     const int blk = lane >> 3, r8 = lane & 7;
     const int my_blocks = warp * 16 < p.M ? k_blocks : 0;      // a warp without rows takes no part in the ring
+    const int g = lane >> 2, q = lane & 3;
+    // what the epilogue adds travels while the products run (a block that sums over a cluster reads it there)
+    float pre_bias[LM_BN / 8][2], pre_res[LM_BN / 8][4];
+    if (split == 1) {
+#pragma unroll
+      for (int j = 0; j < LM_BN / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int col = n0 + j * 8 + 2 * q + e;
+          pre_bias[j][e] = (p.bias && col < p.N) ? __ldg(p.bias + col) : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = warp * 16 + g + (e >> 1) * 8, col = n0 + j * 8 + 2 * q + (e & 1);
+          pre_res[j][e] = (p.residual && r < p.M && col < p.N) ? p.residual[(long long)r * p.N + col] : 0.f;
+        }
+      }
+    }
     bool ok = true;
     for (int kb = 0; kb < my_blocks && ok; ++kb) {
       const int s = kb % LM_STAGES;
@@ -157,7 +175,6 @@ linear_mid_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(lm_smem(&empty[s])) : "memory");
     }
     if (!ok) failed = 1;
-    const int g = lane >> 2, q = lane & 3;
     if (split > 1) {
       // (a block that failed leaves NaN, which its peers' sums keep)
 #pragma unroll
@@ -173,8 +190,7 @@ linear_mid_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const int r = warp * 16 + g + (e >> 1) * 8, col = n0 + j * 8 + 2 * q + (e & 1);
           if (r < p.M && col < p.N) {
             const long long o = (long long)r * p.N + col;
-            float x = apply_activation(acc[j][e] + (p.bias ? p.bias[col] : 0.f), p.act);
-            if (p.residual) x += p.residual[o];
+            const float x = apply_activation(acc[j][e] + pre_bias[j][e & 1], p.act) + pre_res[j][e];
             if (p.out_is_f32)
               reinterpret_cast<float*>(p.out)[o] = x;
             else
