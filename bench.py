@@ -55,7 +55,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.file,
+                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=self.file,
                                          stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -392,6 +392,11 @@ def run_ours(args):
         e2e = e2e_decode(engine, cfg, batch, prompt_len, steps, torch, bt, rng)
     launches_small = kernels.launch_count() - before_all
     detail["decode_b8"] = decode_series(engine, cfg, [512] * batch, series_steps, torch, bt, rng, pk)
+    # the same batch at a short and at a long context (the cache's share of a step's bytes goes from 10 % to 55 %)
+    for prompt in (128, 900):
+        key = f"decode_b8_ctx{prompt}"
+        detail[key] = decode_series(engine, cfg, [prompt] * batch, series_steps, torch, bt, rng, pk)
+        points[key] = detail[key]["tokens_per_s"]
     h2d = round(engine.last_session.h2d_bytes / max(1, engine.last_session.steps), 1)
     d2h = round(engine.last_session.d2h_bytes / max(1, engine.last_session.steps), 1)
     if args.points == "all":
