@@ -1361,6 +1361,7 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowAr
   }
   static_assert(sizeof(FlowPhase) % 16 == 0, "phases are copied 16 bytes at a time");
   constexpr int PHASE_VECS = (int)(sizeof(FlowPhase) / 16);
+  static_assert(PHASE_VECS <= 64, "two warps copy a phase's description");
   if (tid < PHASE_VECS) reinterpret_cast<uint4*>(&sh.phase[0])[tid] = reinterpret_cast<const uint4*>(args.phases)[tid];
   __syncthreads();
   // token selection comes last (if at all) and is the work of the whole block after the grid barrier
@@ -1386,9 +1387,12 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode_flow_kernel(const FlowAr
       if (sh.failed) break;    // (uniform: written before the barrier)
       const FlowPhase& ph = sh.phase[pi & 1];
       // the next phase's description travels meanwhile
-      if (pi + 1 < args.n_phases && tid < PHASE_VECS)
-        df_cp16(reinterpret_cast<uint4*>(&sh.phase[(pi + 1) & 1]) + tid, reinterpret_cast<const uint4*>(args.phases + pi + 1) + tid);
-      if (tid == 0) sh.trace = (args.trace && blockIdx.x == 0) ? args.trace + DF_TRACE_SLOTS * pi : nullptr;
+      // (asked for by the last warps: right after a phase's stores a copy may wait a few hundred nanoseconds for the
+      // load/store path, and these warps' share of the next rows is the least likely to be waited for)
+      if (pi + 1 < args.n_phases && tid >= DF_CONSUMERS - 64 && tid - (DF_CONSUMERS - 64) < PHASE_VECS)
+        df_cp16(reinterpret_cast<uint4*>(&sh.phase[(pi + 1) & 1]) + (tid - (DF_CONSUMERS - 64)),
+                reinterpret_cast<const uint4*>(args.phases + pi + 1) + (tid - (DF_CONSUMERS - 64)));
+      if (args.trace && tid == 0) sh.trace = blockIdx.x == 0 ? args.trace + DF_TRACE_SLOTS * pi : nullptr;
       df_stamp(sh, 0);
       if (ph.type == FP_EMBED) {
         const unsigned tag = df_tag32(args.epoch, pi);
