@@ -214,6 +214,7 @@ __host__ __device__ inline FlowLayout df_layout(int rows, int max_k, int max_ln_
 
 struct FlowItem {
   int seq, head, split, L, lo, pg_first, pg_end;   // pages [pg_first, pg_end)
+  int kv_head;                                     // the key/value head the query head reads
 };
 struct FlowWork {
   FlowItem it[DF_MAX_ITEMS];
@@ -406,6 +407,7 @@ __device__ __forceinline__ FlowItem df_item(const FlowPhase* ph, const FlowShare
   const int unit = item / S;
   it.head = unit % ph->n_heads;
   it.seq = unit / ph->n_heads;
+  it.kv_head = it.head / (ph->n_heads / ph->n_kv_heads);
   it.L = df_ctx_len(ph, sh, it.seq);
   it.lo = ph->window > 0 ? max(0, it.L - ph->window) : 0;
   // (a sequence without keys, L <= 0, owns no page, files nothing and yields zeros)
@@ -456,7 +458,6 @@ __device__ unsigned df_page_producer(const FlowArgs& args, int n_phases, const F
     df_plan(ph, sh, sh.pwork);
     const int total = sh.pwork.start[sh.pwork.n];
     const int cbs = df_col_blocks(ph->head_dim);
-    const int group = ph->n_heads / ph->n_kv_heads;
     for (int base = 0; base < total && !sh.failed; base += 32) {
       // every lane looks up one page of the stream
       const int k = base + lane;
@@ -467,7 +468,7 @@ __device__ unsigned df_page_producer(const FlowArgs& args, int n_phases, const F
         const FlowItem it = sh.pwork.it[j];
         const int pg = it.pg_first + (k - sh.pwork.start[j]);
         const int page = df_table_entry(ph, sh, it.seq, pg % ph->table_len);
-        row = (page * ph->n_kv_heads + it.head / group) * DS_PAGE;
+        row = (page * ph->n_kv_heads + it.kv_head) * DS_PAGE;
       }
       const int n = min(32, total - base);
       for (int j = 0; j < n; ++j, ++use) {
@@ -1121,7 +1122,7 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
     for (int pair = warp; pair < n_rows; pair += DF_CWARPS) {
       const int j = kinds == 3 ? pair / 3 : pair, r = pair - j * kinds;
       const int seq = sh.work.it[j].seq, head = sh.work.it[j].head;
-      const int col = r == 0 ? head * hd : (r == 1 ? k_off : v_off) + (head / group) * hd;
+      const int col = r == 0 ? head * hd : (r == 1 ? k_off : v_off) + sh.work.it[j].kv_head * hd;
       if (lane < quads) {
         const unsigned* src = proj + (unsigned)(seq * q_stride + col + lane * 4);
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -1152,7 +1153,7 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
     const FlowItem it = sh.work.it[mine];
     const __nv_bfloat16* my_rows = rows + mine * 3 * hd;
     const int k0 = sh.work.start[mine], n_pages = sh.work.start[mine + 1] - k0;
-    const int kv_head = it.head / group;
+    const int kv_head = it.kv_head;
     const int lo = max(it.lo, it.pg_first * DS_PAGE), hi = min(it.L, it.pg_end * DS_PAGE);
     // the query in the layout of the keys' loads; only row 0 of the tile (lanes with g = 0) is a query
     unsigned qa[I * 4];          // per 16 dims: dims 2q, 2q + 1 and 8 + 2q, 9 + 2q
