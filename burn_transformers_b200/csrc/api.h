@@ -69,6 +69,11 @@ int bt_advance(const int* ids, int* tokens, int* positions, int* past_len, int* 
 int bt_linear_tcgen05_supports(int M, int N, int K);
 int bt_linear_tcgen05(const void* a, const void* w, const float* bias, const float* residual, void* out, int* status,
                       int M, int N, int K, int act, int out_is_f32, cudaStream_t stream);
+// out[M, N] = act(x[M, K] @ w[N, K]^T + bias) (+ residual) for at most 128 bfloat16 rows over large weights, on the
+// tcgen05 tensor cores with the weights on their M side; split: blocks per cluster along K (0: chosen from the shape).
+int bt_linear_few_tcgen05_supports(int M, int N, int K);
+int bt_linear_few_tcgen05(const void* x, const void* w, const float* bias, const float* residual, void* out, int* status,
+                          int M, int N, int K, int act, int out_is_f32, int split, cudaStream_t stream);
 int bt_linear_stream_supports(int M, int N, int K, int fuse_ln);
 int bt_linear_stream(const void* a, const float* x32, const int* rows, const float* gamma, const float* beta, float eps,
                      const void* w, const float* bias, const float* residual, void* out, int M, int N, int K, int act,

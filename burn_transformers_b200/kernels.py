@@ -342,6 +342,33 @@ def linear_tcgen05(a, w, bias, out, *, m, activation=None, residual=None):
                                        _stream()))
 
 
+def linear_few_tcgen05_supports(m, n, k) -> bool:
+    return _supports("bt_linear_few_tcgen05_supports", m, n, k)
+
+
+def linear_few_tcgen05(a, w, bias, out, *, m, activation=None, residual=None, split=0):
+    """out[:m] = act(a[:m] @ w^T + bias) (+ residual) for at most 128 bfloat16 rows and weights stored [N, K], on the
+    tcgen05 tensor cores with the weights on their M side: the product for few rows over large weights (a block per
+    128 columns and slice of K, the slices of a cluster summed through distributed shared memory)."""
+    n, k = w.shape
+    _need(a, "a", torch.bfloat16, (None, k))
+    _need(w, "w", torch.bfloat16, (n, k))
+    _need(out, "out", (torch.float32, torch.bfloat16), (None, n))
+    if a.shape[0] < m or out.shape[0] < m:
+        raise ShapeError(f"linear_few_tcgen05: {m} rows asked of a[{a.shape[0]}] and out[{out.shape[0]}]")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (n,))
+    if residual is not None:
+        _need(residual, "residual", torch.float32, (None, n))
+    if activation not in ACTIVATIONS:
+        raise ShapeError(f"linear_few_tcgen05: unknown activation {activation!r}")
+    _linear_work(m, n, k, a, w, out)
+    _check(library().bt_linear_few_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out),
+                                           _ptr(kernel_status(a.device)), c_int(m), c_int(n), c_int(k),
+                                           c_int(ACTIVATIONS[activation]), c_int(1 if out.dtype == torch.float32 else 0),
+                                           c_int(split), _stream()))
+
+
 def linear_stream_supports(m, n, k, fuse_ln) -> bool:
     return _supports("bt_linear_stream_supports", m, n, k, 1 if fuse_ln else 0)
 

@@ -251,6 +251,75 @@ def test_linear_mid_refuses_what_it_cannot_do():
                            split=3)
 
 
+@pytest.mark.parametrize("m", [1, 17, 64, 100, 128])
+@pytest.mark.parametrize("n, k", [(256, 128), (768, 3072), (200, 72), (130, 64), (1000, 520), (1604, 6400), (2304, 776)])
+def test_linear_few_tcgen05(m, n, k):
+    """The tcgen05 product with the weights on the tensor cores' M side: column tiles that end inside a tile, rows
+    that are no multiple of 16, K that ends inside a stage and is longer than the ring, the split the library
+    chooses."""
+    a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    bias, res = torch.randn(n, device=DEV), torch.randn(m, n, device=DEV)
+    assert kernels.linear_few_tcgen05_supports(m, n, k)
+    product = a.double() @ w.double().T
+    out = torch.full((m + 2, n), 3.0, device=DEV)
+    out[:m] = res
+    kernels.linear_few_tcgen05(a, w, bias, out, m=m, activation="gelu_new", residual=out)
+    want = torch.nn.functional.gelu(product + bias.double(), approximate="tanh") + res.double()
+    assert rel(out[:m], want) < 4 * math.sqrt(k) * 2.0 ** -24 + 1e-6 and float((out[m:] - 3.0).abs().max()) == 0.0
+    low = torch.full((m + 2, n), 3.0, device=DEV, dtype=torch.bfloat16)
+    kernels.linear_few_tcgen05(a, w, None, low, m=m)
+    assert rel(low[:m], product) < 4e-3 and float((low[m:].float() - 3.0).abs().max()) == 0.0
+    low = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    kernels.linear_few_tcgen05(a, w, bias, low, m=m, activation="gelu")
+    assert rel(low, torch.nn.functional.gelu(product + bias.double())) < 4e-3
+    # the same rows give the same result whatever else is in the call
+    alone = torch.empty(1, n, device=DEV)
+    both = torch.empty(m, n, device=DEV)
+    kernels.linear_few_tcgen05(a[m - 1:].contiguous(), w, bias, alone, m=1)
+    kernels.linear_few_tcgen05(a, w, bias, both, m=m)
+    assert torch.equal(alone[0], both[m - 1])
+    assert int(kernels.kernel_status(a.device)) == 0
+
+
+@pytest.mark.parametrize("split", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("n, k", [(768, 3072), (300, 520), (52, 1608)])
+def test_linear_few_tcgen05_split_over_a_cluster(n, k, split):
+    """K cut over the blocks of a cluster (slices that end inside a stage) gives the whole sum, the same at every
+    call; a split that would leave a block without any k is refused."""
+    m = 41
+    a = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    bias, res = torch.randn(n, device=DEV), torch.randn(m, n, device=DEV)
+    k_blocks = -(-k // 64)
+    if (split - 1) * -(-k_blocks // split) >= k_blocks:
+        with pytest.raises(KernelError, match="without any of K"):
+            kernels.linear_few_tcgen05(a, w, bias, res.clone(), m=m, split=split)
+        return
+    want = torch.nn.functional.gelu(a.double() @ w.double().T + bias.double(), approximate="tanh") + res.double()
+    outs = []
+    for _ in range(2):
+        out = res.clone()
+        kernels.linear_few_tcgen05(a, w, bias, out, m=m, activation="gelu_new", residual=out, split=split)
+        outs.append(out)
+    assert rel(outs[0], want) < 4 * math.sqrt(k) * 2.0 ** -24 + 1e-6
+    assert torch.equal(outs[0], outs[1])
+    assert int(kernels.kernel_status(a.device)) == 0
+
+
+def test_linear_few_tcgen05_refuses_what_it_cannot_do():
+    assert not kernels.linear_few_tcgen05_supports(129, 64, 64)
+    assert not kernels.linear_few_tcgen05_supports(20, 64, 100)          # rows of 100 bfloat16 are not 16-byte chunks
+    with pytest.raises(KernelError, match="not supported"):
+        kernels.linear_few_tcgen05(torch.zeros(20, 100, device=DEV, dtype=torch.bfloat16),
+                                   torch.zeros(64, 100, device=DEV, dtype=torch.bfloat16), None, torch.zeros(20, 64, device=DEV),
+                                   m=20)
+    with pytest.raises(KernelError, match="split"):
+        kernels.linear_few_tcgen05(torch.zeros(20, 64, device=DEV, dtype=torch.bfloat16),
+                                   torch.zeros(64, 64, device=DEV, dtype=torch.bfloat16), None, torch.zeros(20, 64, device=DEV),
+                                   m=20, split=9)
+
+
 def test_linear_skinny_refuses_what_it_cannot_do():
     assert not kernels.linear_skinny_supports(65, 64, 64, False, False)
     assert not kernels.linear_skinny_supports(4, 100, 64, False, False)     # [K,N] rows of 100 are not 16-byte chunks
