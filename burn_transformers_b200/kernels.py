@@ -535,7 +535,8 @@ _STATUS_TEXT = {1: "decode attention gave up waiting for a copy of cache pages",
                 4: "the fused decode step met a token id or position outside its table",
                 5: "the matrix product for 17 to 64 rows gave up waiting for a stage of its pipeline",
                 6: "the tcgen05 prefill attention gave up waiting for a stage of its pipeline (or found its shared memory "
-                   "misaligned)"}
+                   "misaligned)",
+                7: "the tcgen05 matrix product for few rows gave up waiting for a stage of its pipeline"}
 
 
 def check_status(device) -> None:
