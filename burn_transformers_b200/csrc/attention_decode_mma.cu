@@ -5,11 +5,12 @@
 // memory accelerator for them (a 64 x 64 box per tile, 128-byte swizzle), the first ones before the kernel waits
 // for its predecessor (old keys and values do not change during a step), each further one when the warps that read
 // the slot have handed it back.  Each computing warp takes 32- or 16-key chunks of the landed pages by itself
-// (scores and weighted values with mma.sync, the query as row 0 of the 16-row tile, softmax in 32-bit); no
-// barrier of the whole block stands between pages.  The warps are merged through shared memory and the splits of a
-// (sequence, head) through distributed shared memory inside a thread-block cluster (at most 8 splits) or through
-// scratch memory, where the block that takes the last ticket merges.  Blocks are small (a few pages) so that many
-// are resident on an SM: a block is a chain of latencies, and it is the other blocks that hide them.
+// (scores and weighted values with mma.sync, the keys on the tiles' 16 rows and the query as the 8-column operand,
+// softmax in 32-bit); no barrier of the whole block stands between pages.  The warps are merged through shared
+// memory and the splits of a (sequence, head) through distributed shared memory inside a thread-block cluster (at
+// most 8 splits) or through scratch memory, where the block that takes the last ticket merges.  Blocks are small (a
+// few pages) so that many are resident on an SM: a block is a chain of latencies, and it is the other blocks that
+// hide them.
 // The block of split 0 files the new token's key and value in the page (one block per key head does).
 // Every wait for a copy is bounded; a wait that runs out sets the status word and makes the result NaN.
 #include <cooperative_groups.h>
@@ -132,16 +133,18 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       *reinterpret_cast<uint4*>(p.v_pool + off + c * 8) = *reinterpret_cast<const uint4*>(rows + 2 * hd + c * 8);
     }
   }
-  unsigned qa[I * 4];          // per 16 dims: dims 2q, 2q + 1 and 8 + 2q, 9 + 2q of the query (row 0 of the tile)
+  unsigned qa[I * 4];          // per 16 dims: dims 2q, 2q + 1 and 8 + 2q, 9 + 2q of the query (every column of the operand)
 #pragma unroll
   for (int j = 0; j < I * 4; ++j) {
     const int d = 16 * (j >> 1) + 8 * (j & 1) + 2 * q;
-    qa[j] = (g == 0 && d < hd) ? *reinterpret_cast<const unsigned*>(rows + d) : 0u;
+    qa[j] = d < hd ? *reinterpret_cast<const unsigned*>(rows + d) : 0u;
   }
+  unsigned k_lane[2 * I], v_lane[2 * I];
+  ds_lane_offsets<I>(lane, k_lane, v_lane);
   float m = -INFINITY, l = 0.f;
-  float acc[I * 4][4];
+  float acc[I * 2][4];
 #pragma unroll
-  for (int n = 0; n < I * 4; ++n)
+  for (int n = 0; n < I * 2; ++n)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
   if (warp == DM_WARPS) {
@@ -202,7 +205,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         }
         __syncwarp();
       }
-      ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, p.scale_log2, m, l, acc, lane);
+      ds_attn_chunk_kt<I, T / 2>(qa, k_lane, v_lane, Ks, Vs, hd, h * CK, key0, lo, hi, p.scale_log2, m, l, acc, lane);
     }
     if (i + p.slots < n_pages) {      // the slot's next page may come
       __syncwarp();
@@ -210,16 +213,21 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
   }
   if (!ok) s_flag = 1;
-  // the four lanes of a row each summed their own keys' weights; lane q of row 0 holds dims 8 n + 2 q + {0, 1}
-  l += __shfl_xor_sync(0xffffffffu, l, 1);
-  l += __shfl_xor_sync(0xffffffffu, l, 2);
-  if (g == 0 && warp < DM_WARPS) {
+  // a lane summed the weights of its own keys (the quad g's, the same in its four lanes); the lanes of a quad hold
+  // dims 16 n + g and 16 n + g + 8 of the weighted values
+  l += __shfl_xor_sync(0xffffffffu, l, 4);
+  l += __shfl_xor_sync(0xffffffffu, l, 8);
+  l += __shfl_xor_sync(0xffffffffu, l, 16);
+  if (q == 0 && warp < DM_WARPS) {
 #pragma unroll
-    for (int n = 0; n < I * 4; ++n) {
-      const int d = 8 * n + 2 * q;
-      if (d < hd) *reinterpret_cast<float2*>(s_acc + warp * hd + d) = make_float2(acc[n][0], acc[n][1]);
+    for (int n = 0; n < I * 2; ++n) {
+      const int d = 16 * n + g;
+      if (d < hd) {
+        s_acc[warp * hd + d] = acc[n][0];
+        s_acc[warp * hd + d + 8] = acc[n][2];
+      }
     }
-    if (q == 0) {
+    if (g == 0) {
       s_ml[warp][0] = m;
       s_ml[warp][1] = l;
     }
@@ -325,6 +333,11 @@ static int launch_decode_mma(const CUtensorMap& km, const CUtensorMap& vm, Decod
   const int share = (pages_total + n_splits - 1) / n_splits;
   int fit = DM_SMEM_BUDGET / slot_bytes;
   if (fit > 16) fit = 16;
+  // A ring that pages go round more than once has an even number of slots.  With 32-key chunks two warps take the even
+  // pages and two the odd ones, so a pair meets a slot again 2 k pages later: with an even count that is the slot's very
+  // next use, whose barrier phase the pair cannot mistake; with an odd count the other pair's use would lie in between,
+  // and a pair that ran ahead would take the phase before it for its own.
+  if (fit > 2) fit &= ~1;
   BT_CHECK(fit >= 1, "attention_decode: one page of head_dim %d does not fit in shared memory", p.head_dim);
   p.slots = share < fit ? (share < 1 ? 1 : share) : fit;
   const size_t smem = 1024 + (size_t)p.slots * slot_bytes + sizeof(float) * (size_t)(DM_WARPS + 1) * p.head_dim + 3 * (size_t)p.head_dim * 2 + 64;

@@ -1149,18 +1149,20 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
   const bool files = ph.k_off >= 0;
   unsigned slot = puse % p_slots, turn = puse / p_slots;
   puse += (unsigned)total;
+  unsigned k_lane[2 * I], v_lane[2 * I];
+  ds_lane_offsets<I>(lane, k_lane, v_lane);
   for (int mine = 0; mine < n_mine; ++mine) {
     const FlowItem it = sh.work.it[mine];
     const __nv_bfloat16* my_rows = rows + mine * 3 * hd;
     const int k0 = sh.work.start[mine], n_pages = sh.work.start[mine + 1] - k0;
     const int kv_head = it.kv_head;
     const int lo = max(it.lo, it.pg_first * DS_PAGE), hi = min(it.L, it.pg_end * DS_PAGE);
-    // the query in the layout of the keys' loads; only row 0 of the tile (lanes with g = 0) is a query
+    // the query as the products' 8-column operand (every column the query)
     unsigned qa[I * 4];          // per 16 dims: dims 2q, 2q + 1 and 8 + 2q, 9 + 2q
 #pragma unroll
     for (int j = 0; j < I * 4; ++j) {
       const int d = 16 * (j >> 1) + 8 * (j & 1) + 2 * q;
-      qa[j] = (g == 0 && d < hd) ? *reinterpret_cast<const unsigned*>(my_rows + d) : 0u;
+      qa[j] = d < hd ? *reinterpret_cast<const unsigned*>(my_rows + d) : 0u;
     }
     if (ph.k_off >= 0 && it.L > 0 && it.split == 0 && it.head == kv_head * group) {
       // this block also files the new token's key and value in the sequence's page (for the steps to come)
@@ -1173,9 +1175,9 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
       }
     }
     float m = -INFINITY, l = 0.f;
-    float acc[I * 4][4];
+    float acc[I * 2][4];
 #pragma unroll
-    for (int n = 0; n < I * 4; ++n)
+    for (int n = 0; n < I * 2; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
     for (int p = 0; p < n_pages; ++p) {
@@ -1201,7 +1203,7 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
           }
           __syncwarp();
         }
-        ds_attn_chunk<I, T>(qa, Ks, Vs, hd, h * CK, key0, lo, hi, scale_log2, m, l, acc, lane);
+        ds_attn_chunk_kt<I, T / 2>(qa, k_lane, v_lane, Ks, Vs, hd, h * CK, key0, lo, hi, scale_log2, m, l, acc, lane);
       }
       __syncwarp();
       if (lane == 0) df_mbar_arrive(&sh.pempty[slot]);      // (every warp, once per page)
@@ -1211,20 +1213,24 @@ __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& 
       }
     }
     df_stamp(sh, 2 + min(mine, 5));
-    // the four lanes of a row each summed their own keys' weights
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    // lane q of row 0 holds dims 8 n + 2 q + {0, 1} of value tile n.  (Two sets of the warps' results, used in
-    // turn: the block-wide hand-over of the next item orders this item's reads before the item after that writes.)
+    // a lane summed the weights of its own keys (its quad's: the same in the quad's four lanes)
+    l += __shfl_xor_sync(0xffffffffu, l, 4);
+    l += __shfl_xor_sync(0xffffffffu, l, 8);
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+    // the lanes of quad g hold dims 16 n + g and 16 n + g + 8 of value tile n.  (Two sets of the warps' results, used
+    // in turn: the block-wide hand-over of the next item orders this item's reads before the item after that writes.)
     float* my_acc = s_acc + (mine & 1) * DF_CWARPS * hd;
     float (*my_ml)[2] = sh.ml[mine & 1];
-    if (g == 0) {
+    if (q == 0) {
 #pragma unroll
-      for (int n = 0; n < I * 4; ++n) {
-        const int d = 8 * n + 2 * q;
-        if (d < hd) *reinterpret_cast<float2*>(my_acc + warp * hd + d) = make_float2(acc[n][0], acc[n][1]);
+      for (int n = 0; n < I * 2; ++n) {
+        const int d = 16 * n + g;
+        if (d < hd) {
+          my_acc[warp * hd + d] = acc[n][0];
+          my_acc[warp * hd + d + 8] = acc[n][2];
+        }
       }
-      if (q == 0) {
+      if (g == 0) {
         my_ml[warp][0] = m;
         my_ml[warp][1] = l;
       }

@@ -103,4 +103,96 @@ __device__ __forceinline__ void ds_attn_chunk(const unsigned (&qa)[I * 4], unsig
     }
 }
 
+// The same chunk with the keys on the tiles' 16 rows and the query as the 8-column operand (every column the
+// query, so every lane of a quad holds the same numbers): S^T = K q^T and O^T = V^T P^T.  A product then covers
+// 16 keys x 16 dims instead of 8 x 16, and a lane holds the scores of keys g and g + 8 of each 16-key tile: half the
+// products and half the softmax arithmetic of the form above, for callers with registers to spare for the lane's
+// byte offsets.
+//   qb: the query for every lane: per 16 dims the dims 2q, 2q + 1 and 8 + 2q, 9 + 2q (two registers);
+//   k_lane[j] / v_lane[j]: byte offset, inside a 16-key tile, of what this lane names for ldmatrix at the j-th 16 dims
+//   (ds_lane_offsets); T2: 16-key tiles of the chunk; row0: the chunk's first row in the page (a multiple of 8).
+// acc[j][0], acc[j][2]: dims 16 j + g and 16 j + g + 8 (the same in the four lanes of a quad); l: the lane's own keys'
+// weights, to be summed over g (lanes 4 apart) at the end.
+template <int I>
+__device__ __forceinline__ void ds_lane_offsets(int lane, unsigned (&k_lane)[2 * I], unsigned (&v_lane)[2 * I]) {
+  const int blk = lane >> 3, r = lane & 7;
+#pragma unroll
+  for (int j = 0; j < 2 * I; ++j) {
+    const int kc = 2 * j + (blk >> 1), vc = 2 * j + (blk & 1);      // 16-byte chunks of the row
+    k_lane[j] = (unsigned)((kc >> 3) * DS_PAGE * 128 + ((blk & 1) * 8 + r) * 128 + (((kc & 7) ^ r) << 4));
+    v_lane[j] = (unsigned)((vc >> 3) * DS_PAGE * 128 + ((blk >> 1) * 8 + r) * 128 + (((vc & 7) ^ r) << 4));
+  }
+}
+
+template <int I, int T2>
+__device__ __forceinline__ void ds_attn_chunk_kt(const unsigned (&qb)[I * 4], const unsigned (&k_lane)[2 * I],
+                                                 const unsigned (&v_lane)[2 * I], unsigned Ks, unsigned Vs, int hd, int row0, int key0,
+                                                 int lo, int hi, float scale_log2, float& m, float& l, float (&acc)[I * 2][4],
+                                                 int lane) {
+  const int g = lane >> 2, q = lane & 3;
+  const unsigned kb = Ks + (unsigned)row0 * 128u, vb = Vs + (unsigned)row0 * 128u;
+  float s[T2][4];
+#pragma unroll
+  for (int t = 0; t < T2; ++t)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[t][e] = 0.f;
+#pragma unroll
+  for (int j = 0; j < 2 * I; ++j) {
+    if (16 * j < hd) {
+#pragma unroll
+      for (int t = 0; t < T2; ++t) {
+        unsigned kf[4];
+        ds_ldmatrix_x4(kf, kb + (unsigned)(t * 16 * 128) + k_lane[j]);
+        ds_mma(s[t], kf[0], kf[1], kf[2], kf[3], qb[2 * j], qb[2 * j + 1]);
+      }
+    }
+  }
+  // a lane's scores: keys key0 + 16 t + g (s[t][0]) and + 8 (s[t][2])
+  float mx = -INFINITY;
+#pragma unroll
+  for (int t = 0; t < T2; ++t)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int key = key0 + 16 * t + 8 * e + g;
+      const float v = (key >= lo && key < hi) ? s[t][2 * e] * scale_log2 : -INFINITY;
+      s[t][2 * e] = v;
+      mx = fmaxf(mx, v);
+    }
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+  const float m_new = fmaxf(m, mx);
+  const float corr = m_new == -INFINITY ? 1.f : ds_exp2(m - m_new);
+  float psum = 0.f;
+  unsigned pb[T2][2];
+#pragma unroll
+  for (int t = 0; t < T2; ++t) {
+    const float p0 = s[t][0] == -INFINITY ? 0.f : ds_exp2(s[t][0] - m_new);      // key 16 t + g
+    const float p1 = s[t][2] == -INFINITY ? 0.f : ds_exp2(s[t][2] - m_new);      // key 16 t + g + 8
+    psum += p0 + p1;
+    // the 8-column operand wants keys 2q, 2q + 1 (and + 8) in one lane: they sit in the quads g = 2q and 2q + 1
+    const float a0 = __shfl_sync(0xffffffffu, p0, 8 * q), a1 = __shfl_sync(0xffffffffu, p0, 8 * q + 4);
+    const float b0 = __shfl_sync(0xffffffffu, p1, 8 * q), b1 = __shfl_sync(0xffffffffu, p1, 8 * q + 4);
+    pb[t][0] = ds_pack(a0, a1);
+    pb[t][1] = ds_pack(b0, b1);
+  }
+  l = l * corr + psum;
+  m = m_new;
+#pragma unroll
+  for (int j = 0; j < I * 2; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[j][e] *= corr;
+#pragma unroll
+  for (int j = 0; j < 2 * I; ++j) {
+    if (16 * j < hd) {
+#pragma unroll
+      for (int t = 0; t < T2; ++t) {
+        unsigned vf[4];
+        ds_ldmatrix_x4_trans(vf, vb + (unsigned)(t * 16 * 128) + v_lane[j]);
+        ds_mma(acc[j], vf[0], vf[1], vf[2], vf[3], pb[t][0], pb[t][1]);
+      }
+    }
+  }
+}
+
 }  // namespace bt
