@@ -68,9 +68,14 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   unsigned char* ring = dm_smem_raw + ((1024u - (ds_smem(dm_smem_raw) & 1023u)) & 1023u);
   float* s_acc = reinterpret_cast<float*>(ring + (size_t)p.slots * slot_bytes);     // [DM_WARPS][hd]
   float* c_acc = s_acc + DM_WARPS * hd;                                             // [hd], read by the cluster peers
-  __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(c_acc + hd);               // query, new key, new value
 
   // lengths and page tables were written before the previous kernel started: safe to read before the wait
+  const int* table = p.table + (long long)seq * p.table_stride;
+  // (without a window or splits the block's run starts at the sequence's first page whatever its length: the
+  // producer's lanes ask for their table entries together with the length, not after it)
+  const bool from_first = p.window == 0 && gridDim.x == 1;
+  int early_page = 0;
+  if (warp == DM_WARPS && from_first) early_page = table[lane % p.table_len];
   const int L = p.ctx_len[seq];                     // keys 0..L-1; the query sits at L-1
   const int lo_all = p.window > 0 ? max(0, L - p.window) : 0;
   // (a sequence without keys, L <= 0, owns no page, files nothing and yields zeros)
@@ -79,7 +84,6 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   const int pg_first = first + split * per, pg_end = min(last + 1, pg_first + per);
   const int n_pages = pg_end > pg_first ? pg_end - pg_first : 0;
   const int lo = max(lo_all, pg_first * DS_PAGE), hi = min(L, pg_end * DS_PAGE);
-  const int* table = p.table + (long long)seq * p.table_stride;
 
   if (tid == 0) {
     for (int i = 0; i < p.slots; ++i) {
@@ -109,35 +113,30 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
   };
   // the first pages at once, before the wait for the predecessor: old keys and values do not change during a step
-  if (warp == DM_WARPS && lane < min(n_pages, p.slots)) ask(lane, table[(pg_first + lane) % p.table_len]);
+  if (warp == DM_WARPS && lane < min(n_pages, p.slots)) ask(lane, from_first ? early_page : table[(pg_first + lane) % p.table_len]);
 
   pdl_wait();     // the projections of this step are complete from here on
-  // the query and the new key and value come into shared memory
-  {
-    const int vecs = hd / 8, kinds = p.new_k ? 3 : 1;
-    for (int i = tid; i < kinds * vecs; i += DM_THREADS) {
-      const int r = i / vecs, c = i - r * vecs;
-      const __nv_bfloat16* src = r == 0 ? p.q + (long long)seq * p.q_stride + head * hd
-                                        : (r == 1 ? p.new_k : p.new_v) + (long long)seq * p.q_stride + kv_head * hd;
-      *reinterpret_cast<uint4*>(rows + r * hd + c * 8) = *reinterpret_cast<const uint4*>(src + c * 8);
-    }
+  // The query goes straight into the registers that multiply it, and the new key and value straight to where they are
+  // needed (the page in memory; the page's copy in shared memory for the one chunk that holds their position): no
+  // staging and no barrier of the block between the wait and the first chunk.
+  const __nv_bfloat16* const q_row = p.q + (long long)seq * p.q_stride + head * hd;
+  const __nv_bfloat16* const new_k = p.new_k ? p.new_k + (long long)seq * p.q_stride + kv_head * hd : nullptr;
+  const __nv_bfloat16* const new_v = p.new_k ? p.new_v + (long long)seq * p.q_stride + kv_head * hd : nullptr;
+  unsigned qa[I * 4];          // per 16 dims: dims 2q, 2q + 1 and 8 + 2q, 9 + 2q of the query (every column of the operand)
+#pragma unroll
+  for (int j = 0; j < I * 4; ++j) {
+    const int d = 16 * (j >> 1) + 8 * (j & 1) + 2 * q;
+    qa[j] = d < hd ? *reinterpret_cast<const unsigned*>(q_row + d) : 0u;
   }
-  __syncthreads();
-  if (p.new_k && L > 0 && split == 0 && head == kv_head * (p.n_heads / p.n_kv_heads)) {
+  if (new_k && L > 0 && split == 0 && head == kv_head * (p.n_heads / p.n_kv_heads)) {
     // this block also files the new token's key and value in the sequence's page
     const int pos = L - 1;
     const long long page = table[(pos / DS_PAGE) % p.table_len];
     const long long off = (page * p.n_kv_heads + kv_head) * (long long)(DS_PAGE * hd) + (long long)(pos % DS_PAGE) * hd;
     for (int c = tid; c < hd / 8; c += DM_THREADS) {
-      *reinterpret_cast<uint4*>(p.k_pool + off + c * 8) = *reinterpret_cast<const uint4*>(rows + hd + c * 8);
-      *reinterpret_cast<uint4*>(p.v_pool + off + c * 8) = *reinterpret_cast<const uint4*>(rows + 2 * hd + c * 8);
+      *reinterpret_cast<uint4*>(p.k_pool + off + c * 8) = *reinterpret_cast<const uint4*>(new_k + c * 8);
+      *reinterpret_cast<uint4*>(p.v_pool + off + c * 8) = *reinterpret_cast<const uint4*>(new_v + c * 8);
     }
-  }
-  unsigned qa[I * 4];          // per 16 dims: dims 2q, 2q + 1 and 8 + 2q, 9 + 2q of the query (every column of the operand)
-#pragma unroll
-  for (int j = 0; j < I * 4; ++j) {
-    const int d = 16 * (j >> 1) + 8 * (j & 1) + 2 * q;
-    qa[j] = d < hd ? *reinterpret_cast<const unsigned*>(rows + d) : 0u;
   }
   unsigned k_lane[2 * I], v_lane[2 * I];
   ds_lane_offsets<I>(lane, k_lane, v_lane);
@@ -194,14 +193,14 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
     if (!landed) ok = false;
     if (key0 < hi && key0 + CK > lo) {
-      if (p.new_k && L - 1 >= key0 && L - 1 < key0 + CK) {
+      if (new_k && L - 1 >= key0 && L - 1 < key0 + CK) {
         // the newest key and value are not in their page yet (or only just): they come from the projections.
         // (No other warp touches this chunk's rows; the rows beyond are masked and hold old, finite numbers.)
         const int row = (L - 1) % DS_PAGE;
         for (int ch = lane; ch < hd / 8; ch += 32) {
           const unsigned off = (unsigned)((ch >> 3) * DS_PAGE * 128 + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
-          *reinterpret_cast<uint4*>(Kt + off) = *reinterpret_cast<const uint4*>(rows + hd + ch * 8);
-          *reinterpret_cast<uint4*>(Kt + cbs * DS_PAGE * 128 + off) = *reinterpret_cast<const uint4*>(rows + 2 * hd + ch * 8);
+          *reinterpret_cast<uint4*>(Kt + off) = *reinterpret_cast<const uint4*>(new_k + ch * 8);
+          *reinterpret_cast<uint4*>(Kt + cbs * DS_PAGE * 128 + off) = *reinterpret_cast<const uint4*>(new_v + ch * 8);
         }
         __syncwarp();
       }
@@ -340,7 +339,7 @@ static int launch_decode_mma(const CUtensorMap& km, const CUtensorMap& vm, Decod
   if (fit > 2) fit &= ~1;
   BT_CHECK(fit >= 1, "attention_decode: one page of head_dim %d does not fit in shared memory", p.head_dim);
   p.slots = share < fit ? (share < 1 ? 1 : share) : fit;
-  const size_t smem = 1024 + (size_t)p.slots * slot_bytes + sizeof(float) * (size_t)(DM_WARPS + 1) * p.head_dim + 3 * (size_t)p.head_dim * 2 + 64;
+  const size_t smem = 1024 + (size_t)p.slots * slot_bytes + sizeof(float) * (size_t)(DM_WARPS + 1) * p.head_dim + 64;
   auto kern = attention_decode_mma_kernel<I, T>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   BT_CHECK(e == cudaSuccess, "attention_decode: cannot reserve %zu bytes of shared memory", smem);
