@@ -1094,10 +1094,10 @@ __device__ __noinline__ void df_attention_merge(const FlowPhase& ph, int pi, con
 }
 
 // ---- attention ---------------------------------------------------------------------------------------------
-// One query per (sequence, head) is row 0 of a 16-row tile (decode_mma.cuh); the pages of the block's items arrive
-// through the ring of page slots in the order of the block's stream of pages.  A warp takes chunks of 8 T keys
-// (the c-th chunk of the stream belongs to warp c % 8) and hands every page back when it is done with it, whether
-// it had a chunk in it or not.  `puse`: how many page slots the block has consumed so far in the launch.
+// One query per (sequence, head) is the 8-column operand of products whose rows are keys (decode_mma.cuh); the pages
+// of the block's items arrive through the ring of page slots in the order of the block's stream of pages.  A warp
+// takes chunks of 8 T keys (the c-th chunk of the stream belongs to warp c % 6) and hands every page back when it is
+// done with it, whether it had a chunk in it or not.  `puse`: how many page slots the block has consumed so far in the launch.
 template <int I, int T>
 __device__ void df_attention_items(const FlowPhase& ph, int pi, const FlowArgs& args, const FlowLayout& lay, unsigned char* smem,
                                    FlowShared& sh, unsigned& puse) {

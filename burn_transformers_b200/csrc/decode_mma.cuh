@@ -1,7 +1,8 @@
 // Decode attention on tensor cores: the pieces that the fused decode step and the stand-alone decode attention share.
-// One query per (sequence, head) is row 0 of a 16-row tile; keys and values lie in shared memory as the tensor
-// memory accelerator leaves them with the 128-byte swizzle (tiles of 64 rows x 128 bytes; the 16-byte chunk c of
-// row r lies at chunk c ^ (r & 7)), so that the 8 x 8 blocks ldmatrix reads fall into different banks.
+// The keys of a chunk are the 16 rows of the products' tiles and the one query per (sequence, head) their 8-column
+// operand; keys and values lie in shared memory as the tensor memory accelerator leaves them with the 128-byte swizzle
+// (tiles of 64 rows x 128 bytes; the 16-byte chunk c of row r lies at chunk c ^ (r & 7)), so that the 8 x 8 blocks
+// ldmatrix reads fall into different banks.
 #pragma once
 #include "common.cuh"
 
@@ -36,78 +37,12 @@ __device__ __forceinline__ unsigned ds_swizzled(unsigned tiles, int row, int chu
   return tiles + (unsigned)((chunk >> 3) * DS_PAGE * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-// One chunk of 8 T keys (rows row0.. of the page whose keys lie at Ks and values at Vs, shared-memory addresses):
-// scores, the running softmax (32-bit), the weighted values.  `qa`: the query's fragments (row 0 of the tile),
-// two registers per 16 dims.  `lane`: the caller's lane (a caller may pass a number the compiler cannot see through, so
-// that the addresses derived from it are not kept in registers from one call to the next).
-template <int I, int T>
-__device__ __forceinline__ void ds_attn_chunk(const unsigned (&qa)[I * 4], unsigned Ks, unsigned Vs, int hd, int row0, int key0, int lo,
-                                              int hi, float scale_log2, float& m, float& l, float (&acc)[I * 4][4], int lane) {
-  const int q = lane & 3;
-  const int blk = lane >> 3, r = lane & 7;       // this lane gives the address of row r of block blk of a load of four
-  float s[T][4];
-#pragma unroll
-  for (int t = 0; t < T; ++t) {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) s[t][e] = 0.f;
-#pragma unroll
-    for (int i = 0; i < I; ++i) {
-      if (32 * i < hd) {           // four chunks = 32 dims = two products
-        unsigned kf[4];
-        ds_ldmatrix_x4(kf, ds_swizzled(Ks, row0 + 8 * t + r, 4 * i + blk));
-        ds_mma(s[t], qa[4 * i], 0u, qa[4 * i + 1], 0u, kf[0], kf[1]);
-        ds_mma(s[t], qa[4 * i + 2], 0u, qa[4 * i + 3], 0u, kf[2], kf[3]);
-      }
-    }
-  }
-  float mx = -INFINITY;
-#pragma unroll
-  for (int t = 0; t < T; ++t)
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int key = key0 + 8 * t + 2 * q + e;
-      s[t][e] = (key >= lo && key < hi) ? s[t][e] * scale_log2 : -INFINITY;
-      mx = fmaxf(mx, s[t][e]);
-    }
-  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-  const float m_new = fmaxf(m, mx);
-  const float corr = m_new == -INFINITY ? 1.f : ds_exp2(m - m_new);
-  float psum = 0.f;
-  unsigned pa[T];
-#pragma unroll
-  for (int t = 0; t < T; ++t) {
-    const float p0 = s[t][0] == -INFINITY ? 0.f : ds_exp2(s[t][0] - m_new);
-    const float p1 = s[t][1] == -INFINITY ? 0.f : ds_exp2(s[t][1] - m_new);
-    psum += p0 + p1;
-    pa[t] = ds_pack(p0, p1);
-  }
-  l = l * corr + psum;
-  m = m_new;
-#pragma unroll
-  for (int n = 0; n < I * 4; ++n) {
-    acc[n][0] *= corr;
-    acc[n][1] *= corr;
-  }
-  // values: blocks (keys 16 b (+ 8), dims 16 n (+ 8)) read transposed
-#pragma unroll
-  for (int b = 0; b < T / 2; ++b)
-#pragma unroll
-    for (int n = 0; n < I * 2; ++n) {
-      if (16 * n < hd) {
-        unsigned v[4];
-        ds_ldmatrix_x4_trans(v, ds_swizzled(Vs, row0 + 16 * b + (blk & 1) * 8 + r, 2 * n + (blk >> 1)));
-        ds_mma(acc[2 * n], pa[2 * b], 0u, pa[2 * b + 1], 0u, v[0], v[1]);
-        ds_mma(acc[2 * n + 1], pa[2 * b], 0u, pa[2 * b + 1], 0u, v[2], v[3]);
-      }
-    }
-}
-
-// The same chunk with the keys on the tiles' 16 rows and the query as the 8-column operand (every column the
-// query, so every lane of a quad holds the same numbers): S^T = K q^T and O^T = V^T P^T.  A product then covers
-// 16 keys x 16 dims instead of 8 x 16, and a lane holds the scores of keys g and g + 8 of each 16-key tile: half the
-// products and half the softmax arithmetic of the form above, for callers with registers to spare for the lane's
-// byte offsets.
+// One chunk of 16 T2 keys (rows row0.. of the page whose keys lie at Ks and values at Vs, shared-memory addresses):
+// scores, the running softmax (32-bit), the weighted values, as S^T = K q^T and O^T = V^T P^T with every column of the
+// 8-column operand the query (so the four lanes of a quad hold the same numbers).  A product covers 16 keys x 16 dims,
+// and a lane holds the scores of keys g and g + 8 of each 16-key tile.  (With the query as row 0 of a 16-row tile
+// instead, a product covers 8 keys x 16 dims and a lane 8 scores of a 32-key chunk: twice the products and the
+// softmax arithmetic.)
 //   qb: the query for every lane: per 16 dims the dims 2q, 2q + 1 and 8 + 2q, 9 + 2q (two registers);
 //   k_lane[j] / v_lane[j]: byte offset, inside a 16-key tile, of what this lane names for ldmatrix at the j-th 16 dims
 //   (ds_lane_offsets); T2: 16-key tiles of the chunk; row0: the chunk's first row in the page (a multiple of 8).
