@@ -123,6 +123,12 @@ class DecodeProgram:
         n, k = w.shape
         if k % 8 or m > MAX_ROWS or w.data_ptr() % 16:
             raise ProgramUnsupported(f"a product of {m} rows and K={k} has no phase")
+        if m >= 6 and n < 8192 and n * k >= 5_500_000:
+            # Layers this large with this many rows are faster as separate kernels: the rows' panel takes the shared
+            # memory the weights' ring needs.  Measured a step, fused against separate: width 1280 at 8 rows 2.04
+            # against 1.67 ms (at 4 rows 1.53 against 1.75); width 1600 at 8 rows 3.78 against 3.20, at 6 rows 3.51
+            # against 3.08, at 5 rows 3.04 against 3.06, at 1 row 2.31 against 2.88; width 1024 at 8 rows 0.97 against 1.02.
+            raise ProgramUnsupported(f"a product of {m} rows over {n} x {k} weights is faster outside the fused step")
         index = len(self.phases)
         ph = Phase(type=PH_LINEAR, M=m, N=n, K=k, act=kernels.ACTIVATIONS[activation], w=_p(w), bias=_p(bias),
                    a_src=-1, res_src=-1)

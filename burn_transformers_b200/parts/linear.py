@@ -25,8 +25,9 @@ def linear(ctx, a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=
     32-bit operands always take the plain fused-multiply-add kernel: the 32-bit path has no reduced-precision
     matrix mode.  bfloat16 products of at most 16 rows take a weight-streaming kernel, which can also normalise
     its rows on the way in; 17 to 64 rows ([N, K] weights) take the kernel that is fed by tensor-map copies (large
-    weights with a short K the tcgen05 product for many rows; up to 128 rows over a large weight with a long K the
-    tcgen05 product with the weights on the M side); with more rows they run on the tcgen05 tensor cores."""
+    weights with a short K the tcgen05 product for many rows); up to 128 rows over a large weight (any K at up to 16
+    rows, a long K above) take the tcgen05 product with the weights on the M side; with more rows they run on the
+    tcgen05 tensor cores."""
     program = getattr(ctx, "program", None)
     if program is not None:      # a fused decode step is being recorded: this product becomes one of its phases
         program.add_linear(a, w, bias, out, m=m, w_is_nk=w_is_nk, activation=activation, residual=residual)
@@ -34,11 +35,15 @@ def linear(ctx, a, w, bias, out, *, m, w_is_nk=False, activation=None, residual=
     lazy = isinstance(a, LazyNorm)
     n = w.shape[0] if w_is_nk else w.shape[1]
     k = w.shape[1] if w_is_nk else w.shape[0]
-    if (w.dtype == torch.bfloat16 and w_is_nk and 16 < m <= 128 and k >= 4096 and n * k >= (6_000_000 if m <= 64 else 3_000_000)
-            and kernels.linear_few_tcgen05_supports(m, n, k)):
-        # a long K over a large weight: the tcgen05 product with the weights on the tensor cores' M side and K cut over
-        # a cluster (measured at 64 rows: 1600 x 6400 in 15.4 us against 21.9 us for the kernel below; at 128 rows 21.0
-        # against 32.5 us for the product for many rows, 1024 x 4096 in 17.9 against 22.1)
+    if (w.dtype == torch.bfloat16 and w_is_nk and n < 8192 and kernels.linear_few_tcgen05_supports(m, n, k)
+            and ((m <= 16 and n * k >= 7_000_000) or (16 < m <= 64 and k >= 4096 and n * k >= 6_000_000)
+                 or (64 < m <= 128 and k >= 4096 and n * k >= 3_000_000))):
+        # a large weight: the tcgen05 product with the weights on the tensor cores' M side and K cut over a cluster.
+        # Measured in a graph with weights that rotate through more than L2 holds, against the kernel that would take
+        # the shape otherwise: 64 rows, 1600 x 6400: 15.4 against 21.9 us; 128 rows: 21.0 against 32.5 us, 1024 x 4096:
+        # 17.9 against 22.1; 8 rows, 4800 x 1600: 9.5 against 11.6 us, 6400 x 1600: 10.4 against 12.6, and the decode step
+        # of GPT-2 XL outside the fused step at 16 rows 3.36 against 4.94 ms (below 7 M weights the kernels for few
+        # rows win: 5120 x 1280 at 8 rows 6.9 against 8.8 us)
         if lazy:
             a = a.materialize(ctx)
         kernels.linear_few_tcgen05(a, w, bias, out, m=m, activation=activation, residual=residual)
