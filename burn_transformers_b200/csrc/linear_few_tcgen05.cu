@@ -40,7 +40,8 @@ constexpr int TF_THREADS = 10 * 32;       // producer, issuer, eight epilogue wa
 constexpr int TF_MAX_STAGES = 8;
 constexpr int TF_MAX_ROWS = 128;
 constexpr unsigned TF_W_BYTES = TF_BN * TC_BK * 2;
-constexpr size_t TF_RING_BUDGET = 200 * 1024;
+constexpr size_t TF_RING_BUDGET = 200 * 1024;    // the ring of stages, one block on a multiprocessor
+constexpr size_t TF_RING_PAIRED = 104 * 1024;    // the ring when two blocks share one
 
 struct FewParams {
   const float* bias;           // [N] or null
@@ -254,16 +255,16 @@ linear_few_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
 }
 
 // The split of K over a cluster for a shape: the one with the shortest estimated time, from
-// (waves of blocks over the multiprocessors) x (a block's k-blocks x the time of one + what a block costs at all);
+// (waves of blocks over the places for a block) x (a block's k-blocks x the time of one + what a block costs at all);
 // every block of a cluster has some of K.
-static int tf_choose_split(int n_tiles, int k_blocks, int sms) {
+static int tf_choose_split(int n_tiles, int k_blocks, int places) {
   int best = 1;
   double best_cost = -1.0;
   for (int s = 1; s <= 8; ++s) {
     const int per = (k_blocks + s - 1) / s;
     if ((s - 1) * per >= k_blocks) continue;          // a rank would be left without k
     const long long blocks = (long long)n_tiles * s;
-    const long long waves = (blocks + sms - 1) / sms;
+    const long long waves = (blocks + places - 1) / places;
     const double cost = (double)waves * (per * 0.25 + 2.0 + 0.15 * (s > 1 ? s : 0));
     if (best_cost < 0 || cost < best_cost - 1e-9) {
       best_cost = cost;
@@ -294,12 +295,17 @@ extern "C" int bt_linear_few_tcgen05(const void* x, const void* w, const float* 
   const int k_blocks = (K + TC_BK - 1) / TC_BK;
   const int n_tiles = (N + TF_BN - 1) / TF_BN;
   BT_CHECK(n_tiles <= 65535, "linear_few_tcgen05: N=%d needs too many column tiles", N);
-  if (split == 0) split = tf_choose_split(n_tiles, k_blocks, sms);
+  // With at most 16 rows a stage is 18 KB: a ring of 104 KB holds what a block needs, two blocks share a multiprocessor,
+  // and the next product of a step streams its weights while this one sums and finishes (measured at 8 rows, 4800 x
+  // 1600: 7.5 against 9.5 us a launch in a graph).  More rows take the whole of shared memory for a long K's stages.
+  const int rows16 = (M + 15) / 16 * 16;
+  const bool paired = rows16 <= 16;
+  const size_t budget = paired ? TF_RING_PAIRED : TF_RING_BUDGET;
+  if (split == 0) split = tf_choose_split(n_tiles, k_blocks, paired ? 2 * sms : sms);
   const int per = (k_blocks + split - 1) / split;
   BT_CHECK((split - 1) * per < k_blocks, "linear_few_tcgen05: split %d leaves a block without any of K=%d", split, K);
-  const int rows16 = (M + 15) / 16 * 16;
   const size_t stage_bytes = TF_W_BYTES + (size_t)rows16 * TC_BK * 2;
-  int stages = (int)(TF_RING_BUDGET / stage_bytes);
+  int stages = (int)(budget / stage_bytes);
   if (stages > TF_MAX_STAGES) stages = TF_MAX_STAGES;
   if (stages > per) stages = per;
   size_t ring = (size_t)stages * stage_bytes;
