@@ -83,7 +83,8 @@ class KernelProfile:
 
 
 class _Bracketed:
-    """The library as the wrappers see it while a profile is active: every launch between two events."""
+    """The library as the wrappers see it while a profile is active: every launch between two events and inside
+    an NVTX range of the kernel's name."""
 
     def __init__(self, lib, profile):
         self._lib, self._profile = lib, profile
@@ -96,9 +97,11 @@ class _Bracketed:
 
         def launch(*args):
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.nvtx.range_push(name)      # (a timeline tool shows the same brackets by name)
             start.record()
             code = fn(*args)
             stop.record()
+            torch.cuda.nvtx.range_pop()
             flops, nbytes = profile.pending
             profile.pending = (0.0, 0.0)
             profile.records.append((name[3:] if name.startswith("bt_") else name, start, stop, flops, nbytes))
