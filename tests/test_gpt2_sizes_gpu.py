@@ -61,3 +61,28 @@ def test_a_request_in_true_32_bit(case):
     got = replay.tail_one_by_one(engine, [seqs[1]], tail=4)
     err, where = replay.worst_error(got, ref32)
     assert err < 1e-4, f"float32: {err:.3e} at {where}"
+
+
+def test_six_requests_over_wide_layers_decode_as_separate_kernels(case):
+    """Six and more rows over layers of 5.5 M weights and more are not recorded as a fused step: the decode steps run
+    as a graph of separate kernels (with the tcgen05 product for few rows over the large weights), and give the same
+    logits; smaller batches of the same model still take the fused step."""
+    cfg, folder, _, _, _ = case
+    if cfg["n_embd"] < 1600:
+        pytest.skip("the layers of this size stay inside the fused step at every batch")
+    pcfg, pw = plain.load_model(folder)
+    rounded = {k: (plain.round_to_bf16(v) if v.ndim == 2 else v) for k, v in pw.items()}
+    lengths = [20, 35, 50, 28, 41, 33]
+    seqs = random_prompts(cfg, lengths, seed=9)
+    ref = [plain.logits(pcfg, rounded, s, quant=plain.round_to_bf16) for s in seqs]
+    engine = Engine.from_folder(folder, "bfloat16", max_tokens=64 * 6)
+    got = replay.batches(engine, seqs, [[0, 1, 2, 3, 4, 5]], [n - 6 for n in lengths])
+    err, where = replay.worst_error(got, ref)
+    assert err < 3e-2, f"batch of six: {err:.3e} at {where}"
+    graphs = {g.n: g for g in engine._graphs.values()}
+    assert graphs[6].program is None, "six rows over these layers were recorded as a fused step"
+    got = replay.batches(engine, seqs[:3], [[0, 1, 2]], [n - 4 for n in lengths[:3]])
+    err, where = replay.worst_error(got, ref[:3])
+    assert err < 3e-2, f"batch of three: {err:.3e} at {where}"
+    graphs = {g.n: g for g in engine._graphs.values()}
+    assert graphs[3].program is not None, "three rows of this model did not run as a fused step"
