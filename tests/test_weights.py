@@ -213,3 +213,24 @@ def test_split_reads_pieces_of_one_stored_tensor():
         bad.stored()
     with pytest.raises(ValueError, match="cannot make"):
         WeightPlan({"a": TensorSpec((4, 7))}, sources={"a": Concat((Stored("p"), Stored("q")), 1)}).stored()
+
+
+def test_the_random_model_program_writes_the_folder_the_library_writes(tmp_path):
+    """bin/random_model: the same configuration and seed give the file `write_random_model` gives; a configuration
+    that cannot be built ends with one line on standard error and a non-zero exit, not a traceback."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    program = Path(__file__).resolve().parent.parent / "bin" / "random_model"
+    config = dict(TINY_A)
+    (tmp_path / "c.json").write_text(json.dumps(config))
+    done = subprocess.run([sys.executable, str(program), str(tmp_path / "c.json"), str(tmp_path / "a"), "--seed", "5", "--loud"],
+                          capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stderr
+    assert done.stdout.strip() == str(tmp_path / "a")
+    bt.write_random_model(tmp_path / "b", config, 5, loud=True)
+    assert (tmp_path / "a" / "model.safetensors").read_bytes() == (tmp_path / "b" / "model.safetensors").read_bytes()
+    assert json.loads((tmp_path / "a" / "config.json").read_text()) == json.loads((tmp_path / "b" / "config.json").read_text())
+    bad = subprocess.run([sys.executable, str(program), json.dumps(dict(config, n_head=5)), str(tmp_path / "c")],
+                         capture_output=True, text=True, timeout=300)
+    assert bad.returncode == 1 and bad.stderr.startswith("random_model: gpt2.n_head") and "Traceback" not in bad.stderr
