@@ -115,8 +115,9 @@ def make_engine(cfg, bt, torch, *, max_tokens, max_slots, fast_weights=False):
         return bt.Engine.from_folder(folder, "bfloat16", max_tokens=max_tokens, max_slots=max_slots)
 
 
-def start_decode(engine, cfg, prompts, new_tokens, bt):
-    """Prefills `prompts` and composes the decode step of the batch; returns (graph, slots)."""
+def start_decode(engine, cfg, prompts, new_tokens, bt, events=None):
+    """Prefills `prompts` and composes the decode step of the batch; returns (graph, slots).  `events`: a pair of CUDA
+    events recorded before and after the prompts' step."""
     from burn_transformers_b200.engine.graphs import DecodeSession
     from burn_transformers_b200.sampling.sampler import DeviceSampler
     from burn_transformers_b200.sampling.tracker import SequenceTracker
@@ -127,7 +128,11 @@ def start_decode(engine, cfg, prompts, new_tokens, bt):
     trackers = [SequenceTracker(i, p, config) for i, p in enumerate(prompts)]
     slots = {i: engine.new_sequence() for i in range(batch)}
     try:
+        if events is not None:
+            events[0].record()
         logits = engine.step([bt.StepEntry(slots[i], p, [len(p) - 1]) for i, p in enumerate(prompts)])
+        if events is not None:
+            events[1].record()
         ids, logps = sampler.select(logits, trackers)
         for t, tok, lp in zip(trackers, ids, logps):
             t.push(tok, lp)
@@ -180,10 +185,11 @@ def decode_series(engine, cfg, prompt_lengths, steps, torch, bt, rng, pk):
     step and the fraction of the copy rate: bytes a step has to read (every weight once, the cache of the live
     requests at the mean context of the timed steps) over its median time."""
     batch = len(prompt_lengths)
-    samples = []
+    samples, prompt_samples = [], []
     for rep in range(WARM_REPETITIONS + REPETITIONS):
         prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in prompt_lengths]
-        graph, slots = start_decode(engine, cfg, prompts, steps + 1, bt)
+        around_prompts = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        graph, slots = start_decode(engine, cfg, prompts, steps + 1, bt, around_prompts)
         try:
             graph.run()
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -195,6 +201,7 @@ def decode_series(engine, cfg, prompt_lengths, steps, torch, bt, rng, pk):
             torch.cuda.synchronize()
             if rep >= WARM_REPETITIONS:
                 samples.append(start.elapsed_time(stop) / steps)
+                prompt_samples.append(around_prompts[0].elapsed_time(around_prompts[1]))
         finally:
             for s in slots.values():
                 engine.release(s)
@@ -202,8 +209,14 @@ def decode_series(engine, cfg, prompt_lengths, steps, torch, bt, rng, pk):
     mean_ctx = sum(prompt_lengths) / batch + 1 + (steps + 1) / 2
     step_bytes = weight_bytes(cfg) + batch * mean_ctx * kv_bytes_per_token(cfg)
     achieved = step_bytes / (stats["median"] * 1e-3) / 1e9
+    # the prompts' own step (all prompts of the batch in one step; a recorded shape replayed from the third repetition)
+    prompt_stats = spread(prompt_samples)
+    prompt_flops = prefill_flops(cfg, prompt_lengths)
+    prompt_step = {"tokens": int(sum(prompt_lengths)), "ms": prompt_stats,
+                   "tokens_per_s": sum(prompt_lengths) / prompt_stats["median"] * 1e3,
+                   "frac": prompt_flops / (prompt_stats["median"] * 1e-3) / (pk["bf16_tflops"] * 1e12), "of": "burst"}
     return {"tokens_per_s": batch / stats["median"] * 1e3, "ms_per_step": stats, "batch": batch, "steps": steps,
-            "mean_context": mean_ctx,
+            "mean_context": mean_ctx, "prompt_step": prompt_step,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / pk["hbm_gbs"], "of": pk["source"]}}
 
