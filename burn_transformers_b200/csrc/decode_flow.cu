@@ -178,7 +178,7 @@ __device__ __forceinline__ int df_ld_status(const int* status) {
 struct FlowLayout {
   int w_slots, p_slots, p_slot_bytes;
   int slot_k, w_row, w_slot_bytes;       // k extent of a weight slot, bytes between its 8 rows (16 apart modulo 128: no bank conflicts), its size
-  int panel_rows, panel_stride;          // rows of the panel (9 or 16) and bytes between them
+  int panel_rows, panel_stride;          // rows of the panel (the step's rows and one of zeros, or 16) and bytes between them
   long long w_off, p_off, panel_off, rows_off, acc_off, total;
 };
 __host__ __device__ inline int df_kpad(int K) { return (K + 31) / 32 * 32; }
@@ -194,7 +194,7 @@ __host__ __device__ inline FlowLayout df_layout(int rows, int max_k, int max_ln_
   L.w_slots = w_slots;
   L.p_slots = p_slots;
   L.p_slot_bytes = head_dim > 0 ? df_page_slot_bytes(head_dim) : 0;
-  L.panel_rows = rows > 8 ? 16 : 9;              // (up to 8 rows: a ninth row of zeros stands for the tile's rows 8 to 15)
+  L.panel_rows = rows > 8 ? 16 : rows + 1;       // (up to 8 rows: a row of zeros behind them stands for all other rows of the tile)
   L.panel_stride = df_kpad(max_k) * 2 + 16;
   long long at = 0;
   L.p_off = at;                                  // page slots first: the swizzle pattern wants 1024-byte boundaries
@@ -837,15 +837,19 @@ __device__ void df_linear_phase(const FlowPhase& ph, int pi, const FlowArgs& arg
   else if (want <= 5) G = 2, n_groups = 3, grp = warp >> 1, wg = warp & 1;
   const unsigned panel = ds_smem(smem + lay.panel_off);
   const int stride = lay.panel_stride;
-  const bool two_rows = lay.panel_rows > 9;
+  const bool two_rows = lay.panel_rows == 16;
   const unsigned tag16 = args.tag16, tag_out = df_tag32(args.epoch, pi);
   FlowTrack trk;
   trk.m[0] = trk.m[1] = -INFINITY;
   trk.l[0] = trk.l[1] = 0.f;
   trk.idx[0] = trk.idx[1] = 0x7fffffff;
   // lane's row and k offset inside a 16 x 16 block of A and an 8 x 32 block of W, as ldmatrix wants the addresses
-  // (a panel of up to 8 rows: the lanes that address the tile's rows 8 to 15 all name the panel's row of zeros)
-  const unsigned a_lane = (unsigned)((((lane >> 3) & 1) ? (two_rows ? 8 + (lane & 7) : 8) : (lane & 7)) * stride + (lane >> 4) * 16);
+  // (a panel of up to 8 rows: the lanes that address a row of the tile that the step does not have, rows 8 to 15
+  // among them, all name the panel's row of zeros, which lies behind the step's rows)
+  const int zero_row = lay.panel_rows - 1;
+  const unsigned a_lane =
+      (unsigned)((((lane >> 3) & 1) ? (two_rows ? 8 + (lane & 7) : zero_row) : (two_rows ? (lane & 7) : min(lane & 7, zero_row))) * stride +
+                 (lane >> 4) * 16);
   const unsigned b_lane = (unsigned)((lane & 7) * w_row + (lane >> 3) * 16);
   const unsigned w_base = ds_smem(smem + lay.w_off);
   int round = 0;
