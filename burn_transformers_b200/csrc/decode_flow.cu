@@ -24,8 +24,8 @@
 //   * Matrix products: every block takes the same share of a phase's output columns (N / blocks or one more), in
 //     tiles of at most 8.  The six computing warps form groups: G = 6, 3, 2 or 1 warps share a tile and split its k
 //     (32 elements at a time, round-robin), so that 6 / G tiles are in work at a time and no block-wide barrier stands
-//     between tiles.  A and B come from shared memory with ldmatrix (A: a panel of the at most 16 rows, built once per
-//     block and phase from tagged rows: copied, or LayerNorm-ed with all warps on every row, 32-bit statistics in two
+//     between tiles.  A and B come from shared memory with ldmatrix (A: a panel of the step's rows and a row of zeros
+//     for the rows it does not have, or 16 rows for more than 8, built once per block and phase from tagged rows: copied, or LayerNorm-ed with all warps on every row, 32-bit statistics in two
 //     passes over registers); a group adds its partial sums through shared memory in the order of its warps, and its
 //     warps take turns at finishing a tile (bias, activation, residual, tags).
 //   * Attention is the tensor-core routine of decode_mma.cuh over the pages in the ring.  With several splits per
