@@ -56,7 +56,7 @@ namespace bt {
 
 constexpr int DF_CWARPS = 6, DF_CONSUMERS = DF_CWARPS * 32;     // warps that compute
 constexpr int DF_THREADS = DF_CONSUMERS + 64;                   // + the weight producer and the page producer
-constexpr int DF_MAX_SLOT_K = 1024;              // largest k extent of a weight slot
+constexpr int DF_MAX_SLOT_K = 1664;              // largest k extent of a weight slot
 constexpr int DF_MAX_WSLOTS = 32, DF_MAX_PSLOTS = 16;
 constexpr int DF_MAX_ITEMS = 8;                  // (sequence, head, split) items of an attention phase a block takes, at most
 constexpr int DF_TABLE_CACHE = 64;               // page-table entries per sequence kept in shared memory
