@@ -1507,38 +1507,13 @@ extern "C" int bt_decode_flow_plan(void* phases_host, int n_phases, int rows, lo
       head_dim = ph[i].head_dim;
     }
   }
-  // The k extent of a weight slot (a multiple of 32, at most 1024; a slot holds one piece of one tile's k): the one
-  // that leaves the least of the ring unused; of equals the largest.
-  int slot_k = 32;
-  long long best = -1;
-  for (int c = 32; c <= DF_MAX_SLOT_K; c += 32) {
-    long long cost = 0;
-    for (int i = 0; i < n_phases; ++i)
-      if (ph[i].type == FP_LINEAR) cost += (long long)ph[i].N * ((ph[i].K + c - 1) / c) * c;
-    if (best < 0 || cost <= best) {
-      best = cost;
-      slot_k = c;
-    }
-  }
-  // what the kernel would otherwise divide out in every phase
   const int n_blocks = sm_count();
   BT_CHECK(n_blocks > 0, "decode_flow: cannot read the number of multiprocessors of the current device");
-  for (int i = 0; i < n_phases; ++i)
-    if (ph[i].type == FP_LINEAR) {
-      ph[i].col_q = ph[i].N / n_blocks;
-      ph[i].col_r = ph[i].N % n_blocks;
-      ph[i].n_chunks = (ph[i].K + slot_k - 1) / slot_k;
-    }
   int variant = 0;
   FlowKernel kernel = df_variant(max_ln_k, head_dim, &variant);
   cudaFuncAttributes attr;
   cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
   BT_CHECK(e == cudaSuccess, "decode_flow: cannot read the kernel's attributes: %s", cudaGetErrorString(e));
-  // Two sizes of shared memory are tried.  195 KB leaves the multiprocessor some 60 KB of first-level cache, where the
-  // few registers the compiler spills stay close; if that leaves the weights' ring fewer than 5 slots, everything the
-  // block may have (227 KB) is taken, and spilled registers live in the second-level cache.
-  // page slots: about 48 KB of them (at least 2, at most 8); weight slots: what is left (at least 4)
-  int p_slots = 0, w_slots = 0;
   // (a model whose layers give a block 64 KB of weights and more a phase is the better for every slot: GPT-2 XL at one
   // row 1.75 against 1.85 ms a step with all of shared memory, GPT-2 large at four rows 1.48 against 1.51; GPT-2 small
   // at eight rows is the other way round, 0.404 against 0.400 ms)
@@ -1546,23 +1521,52 @@ extern "C" int bt_decode_flow_plan(void* phases_host, int n_phases, int rows, lo
   for (int i = 0; i < n_phases; ++i)
     if (ph[i].type == FP_LINEAR && ph[i].N < 8192 && (long long)ph[i].N * ph[i].K > widest) widest = (long long)ph[i].N * ph[i].K;
   const int kb0 = widest * 2 / n_blocks >= 64 * 1024 ? 227 : 195;
-  for (int kb = kb0; kb <= 227; kb += 32) {
-    const long long budget = (long long)kb * 1024 - (long long)attr.sharedSizeBytes - 1024 - 64;
-    p_slots = 0;
-    if (head_dim > 0) {
-      p_slots = 48 * 1024 / df_page_slot_bytes(head_dim);
-      p_slots = p_slots < 2 ? 2 : (p_slots > 8 ? 8 : p_slots);
+  int slot_k = 32, p_slots = 0, w_slots = 0;
+  // The k extent of a weight slot (a multiple of 32; a slot holds one piece of one tile's k): the one that leaves the
+  // least of the ring unused; of equals the largest.  Slots of up to 1,664 of k take a wide model's rows of K in one
+  // piece (half the hand-overs between the producer and the warps: GPT-2 XL at one row 1.57 against 1.75 ms a step); if
+  // such slots leave the ring fewer than 4 of them, slots of at most 1,024 are taken.
+  for (int limit : {DF_MAX_SLOT_K, 1024}) {
+    long long best = -1;
+    for (int c = 32; c <= limit; c += 32) {
+      long long cost = 0;
+      for (int i = 0; i < n_phases; ++i)
+        if (ph[i].type == FP_LINEAR) cost += (long long)ph[i].N * ((ph[i].K + c - 1) / c) * c;
+      if (best < 0 || cost <= best) {
+        best = cost;
+        slot_k = c;
+      }
     }
-    for (;;) {
-      const FlowLayout fixed = df_layout(rows, max_k, max_ln_k, head_dim, 0, p_slots, slot_k);
-      w_slots = (int)((budget - fixed.total) / fixed.w_slot_bytes);
-      if (w_slots >= 4 || p_slots <= 2) break;
-      --p_slots;
+    // Two sizes of shared memory are tried.  195 KB leaves the multiprocessor some 60 KB of first-level cache, where the
+    // few registers the compiler spills stay close; if that leaves the weights' ring fewer than 5 slots, everything the
+    // block may have (227 KB) is taken, and spilled registers live in the second-level cache.
+    // page slots: about 48 KB of them (at least 2, at most 8); weight slots: what is left (at least 4)
+    for (int kb = kb0; kb <= 227; kb += 32) {
+      const long long budget = (long long)kb * 1024 - (long long)attr.sharedSizeBytes - 1024 - 64;
+      p_slots = 0;
+      if (head_dim > 0) {
+        p_slots = 48 * 1024 / df_page_slot_bytes(head_dim);
+        p_slots = p_slots < 2 ? 2 : (p_slots > 8 ? 8 : p_slots);
+      }
+      for (;;) {
+        const FlowLayout fixed = df_layout(rows, max_k, max_ln_k, head_dim, 0, p_slots, slot_k);
+        w_slots = (int)((budget - fixed.total) / fixed.w_slot_bytes);
+        if (w_slots >= 4 || p_slots <= 2) break;
+        --p_slots;
+      }
+      if (w_slots >= 5) break;
     }
-    if (w_slots >= 5) break;
+    if (w_slots >= 4 || slot_k <= 1024) break;
   }
   BT_CHECK(w_slots >= 4, "decode_flow: %d rows of K=%d leave no room for the weights' ring in shared memory", rows, max_k);
   if (w_slots > DF_MAX_WSLOTS) w_slots = DF_MAX_WSLOTS;
+  // what the kernel would otherwise divide out in every phase
+  for (int i = 0; i < n_phases; ++i)
+    if (ph[i].type == FP_LINEAR) {
+      ph[i].col_q = ph[i].N / n_blocks;
+      ph[i].col_r = ph[i].N % n_blocks;
+      ph[i].n_chunks = (ph[i].K + slot_k - 1) / slot_k;
+    }
   const FlowLayout lay = df_layout(rows, max_k, max_ln_k, head_dim, w_slots, p_slots, slot_k);
   out[0] = max_k;
   out[1] = max_ln_k;
