@@ -35,6 +35,10 @@ MAX_ROWS = 16
 SPLITS_OVERRIDE = None
 
 
+# More rows than WIDE_ROWS over layers of WIDE_WEIGHTS weights and more are left to separate kernels (see add_linear).
+WIDE_ROWS, WIDE_WEIGHTS = 5, 5_500_000
+
+
 class ProgramUnsupported(Exception):
     """Something in the step has no phase; the step runs as separate kernels."""
 
@@ -123,11 +127,12 @@ class DecodeProgram:
         n, k = w.shape
         if k % 8 or m > MAX_ROWS or w.data_ptr() % 16:
             raise ProgramUnsupported(f"a product of {m} rows and K={k} has no phase")
-        if m >= 6 and n < 8192 and n * k >= 5_500_000:
+        if m > WIDE_ROWS and n < 8192 and n * k >= WIDE_WEIGHTS:
             # Layers this large with this many rows are faster as separate kernels: the rows' panel takes the shared
-            # memory the weights' ring needs.  Measured a step, fused against separate: width 1280 at 8 rows 2.04
-            # against 1.67 ms (at 4 rows 1.53 against 1.75); width 1600 at 8 rows 3.78 against 3.20, at 6 rows 3.51
-            # against 3.08, at 5 rows 3.04 against 3.06, at 1 row 2.31 against 2.88; width 1024 at 8 rows 0.97 against 1.02.
+            # memory the weights' ring needs.  Measured a step, fused against separate: width 1280 at 8 rows 2.02
+            # against 1.67 ms, at 6 rows 1.62 against 1.58, at 5 rows 1.59 against 1.58, at 4 rows 1.34 against 1.75;
+            # width 1600 at 8 rows 3.79 against 3.05, at 5 rows 2.55 against 3.06, at 1 row 1.57 against 2.88; width
+            # 1024 at 8 rows 0.97 against 1.02.
             raise ProgramUnsupported(f"a product of {m} rows over {n} x {k} weights is faster outside the fused step")
         index = len(self.phases)
         ph = Phase(type=PH_LINEAR, M=m, N=n, K=k, act=kernels.ACTIVATIONS[activation], w=_p(w), bias=_p(bias),
